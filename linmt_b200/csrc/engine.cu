@@ -1,0 +1,651 @@
+// engine.cu -- decoding engine: weight packing, device state, encoder, step loop, C ABI.
+//
+// Host code launches kernels on one stream and never waits inside the step loop: beam
+// state, back-pointers, finished hypotheses and alignment records all stay on the device
+// (the reference copies V x k probabilities to the host and walks heaps there every step,
+// src/decoder.h:1396-1436, 355-480).
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <numeric>
+
+#include "gemm_simt.cuh"
+#include "step_kernels.cuh"
+
+namespace linmt {
+
+#define CK(call)                                                                              \
+  do {                                                                                        \
+    cudaError_t e_ = (call);                                                                  \
+    if (e_ != cudaSuccess) {                                                                  \
+      char b_[512];                                                                           \
+      snprintf(b_, sizeof b_, "CUDA error %s at %s:%d: %s", cudaGetErrorName(e_), __FILE__, __LINE__, cudaGetErrorString(e_)); \
+      return fail(LINMT_ECUDA, b_);                                                           \
+    }                                                                                         \
+  } while (0)
+
+#define LAUNCHED() (++stats.kernel_launches)
+
+template <class T>
+int Engine::dalloc(T** p, size_t count) {
+  void* q = nullptr;
+  cudaError_t e = cudaMalloc(&q, std::max<size_t>(count, 1) * sizeof(T));
+  if (e != cudaSuccess) {
+    err = std::string("cudaMalloc failed: ") + cudaGetErrorString(e);
+    return LINMT_ENOMEM;
+  }
+  allocs_.push_back(q);
+  *p = static_cast<T*>(q);
+  return LINMT_OK;
+}
+#define DA(p, n)                                  \
+  do {                                            \
+    int rc_ = dalloc(&(p), (n));                  \
+    if (rc_ != LINMT_OK) return rc_;              \
+  } while (0)
+
+Engine::~Engine() {
+  if (stream) cudaStreamSynchronize(stream);
+  for (void* p : allocs_) cudaFree(p);
+  for (void* p : trace_allocs_) cudaFree(p);
+  if (h_meta_) cudaFreeHost(h_meta_);
+  if (ev0_) cudaEventDestroy(ev0_);
+  if (ev1_) cudaEventDestroy(ev1_);
+  for (auto e : gemm_ev_) cudaEventDestroy(e);
+  if (stream) cudaStreamDestroy(stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Host-side packing.  A reference weight "out x in" sits column-major, i.e. [in][out]
+// (src/utility_cu.h:37).  Packed gate matrix row 4j+g = gate g of hidden unit j, columns =
+// the K-concatenation of the segments, each padded to Hp.
+void pack_gate_weights(const float* const* mats, int nseg, int H, int Hp, float* out) {
+  const size_t K = (size_t)nseg * Hp;
+  std::memset(out, 0, sizeof(float) * 4 * (size_t)Hp * K);
+#pragma omp parallel for schedule(static)
+  for (int j = 0; j < H; ++j)
+    for (int g = 0; g < 4; ++g) {
+      float* row = out + ((size_t)4 * j + g) * K;
+      for (int s = 0; s < nseg; ++s) {
+        const float* m = mats[s * 4 + g];
+        float* dst = row + (size_t)s * Hp;
+        for (int kx = 0; kx < H; ++kx) dst[kx] = m[(size_t)kx * H + j];
+      }
+    }
+}
+
+namespace {
+struct BlobView {
+  struct Lstm {
+    const float *Whi, *bi, *Whf, *bf, *Whc, *bc, *Who, *bo, *emb, *Mi, *Mf, *Mo, *Mc, *Qi, *Qf, *Qo, *Qc;
+  };
+  std::vector<Lstm> src, tgt;
+  const float *Wa, *Wp, *vp, *bout, *Wc1, *Wc2, *D, *bd;
+};
+// Matrix order of a model file: src/layer_input_to_hidden.h:1378-1423,
+// src/layer_hidden_to_hidden.h:953-979, src/layer_attention.h:1246-1260,
+// src/layer_loss.h:1191-1196, sequence src/deep_rnn.h:1878-1969.
+BlobView view_blob(const linmt_model_desc& d, const float* p) {
+  BlobView v;
+  const size_t H = d.hidden, hh = H * H;
+  auto take = [&](size_t n) { const float* q = p; p += n; return q; };
+  auto lstm = [&](BlobView::Lstm& w, bool first, size_t vocab, bool feed) {
+    w.Whi = take(hh); w.bi = take(H); w.Whf = take(hh); w.bf = take(H);
+    w.Whc = take(hh); w.bc = take(H); w.Who = take(hh); w.bo = take(H);
+    w.emb = first ? take(H * vocab) : nullptr;
+    w.Mi = take(hh); w.Mf = take(hh); w.Mo = take(hh); w.Mc = take(hh);
+    w.Qi = w.Qf = w.Qo = w.Qc = nullptr;
+    if (feed) { w.Qi = take(hh); w.Qf = take(hh); w.Qo = take(hh); w.Qc = take(hh); }
+  };
+  v.src.resize(d.layers); v.tgt.resize(d.layers);
+  for (int l = 0; l < d.layers; ++l) lstm(v.src[l], l == 0, d.vocab_src, false);
+  for (int l = 0; l < d.layers; ++l) lstm(v.tgt[l], l == 0, d.vocab_tgt, l == 0 && d.feed_input);
+  v.Wa = take(hh); v.Wp = take(hh); v.vp = take(H); v.bout = take(H); v.Wc1 = take(hh); v.Wc2 = take(hh);
+  v.D = take((size_t)d.vocab_tgt * H); v.bd = take(d.vocab_tgt);
+  return v;
+}
+}  // namespace
+
+int Engine::pack_model(const float* blob, DevModel& m) {
+  const BlobView bv = view_blob(desc, blob);
+  std::vector<float> host;
+  auto upload = [&](float** dst, size_t n) -> int {
+    DA(*dst, n);
+    cudaError_t e = cudaMemcpy(*dst, host.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(LINMT_ECUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    return LINMT_OK;
+  };
+  auto pack_emb = [&](const float* emb, int vocab, float** dst) -> int {
+    host.assign((size_t)vocab * Hp, 0.f);
+#pragma omp parallel for schedule(static)
+    for (int v = 0; v < vocab; ++v) std::memcpy(&host[(size_t)v * Hp], emb + (size_t)v * H, sizeof(float) * H);
+    return upload(dst, host.size());
+  };
+  auto pack_bias4 = [&](const BlobView::Lstm& w, float** dst) -> int {
+    host.assign((size_t)4 * Hp, 0.f);
+    const float* bs[4] = {w.bi, w.bf, w.bc, w.bo};
+    for (int j = 0; j < H; ++j)
+      for (int g = 0; g < 4; ++g) host[(size_t)4 * j + g] = bs[g][j];
+    return upload(dst, host.size());
+  };
+  auto pack_lstm = [&](const BlobView::Lstm& w, bool feed, float** wdst, float** bdst, int* ldw) -> int {
+    const int nseg = feed ? 3 : 2;
+    const float* mats[12] = {w.Mi, w.Mf, w.Mc, w.Mo, w.Whi, w.Whf, w.Whc, w.Who, w.Qi, w.Qf, w.Qc, w.Qo};
+    host.resize((size_t)4 * Hp * nseg * Hp);
+    pack_gate_weights(mats, nseg, H, Hp, host.data());
+    *ldw = nseg * Hp;
+    int rc = upload(wdst, host.size());
+    if (rc) return rc;
+    return pack_bias4(w, bdst);
+  };
+  int rc;
+  if ((rc = pack_emb(bv.src[0].emb, desc.vocab_src, &m.emb_src))) return rc;
+  if ((rc = pack_emb(bv.tgt[0].emb, desc.vocab_tgt, &m.emb_tgt))) return rc;
+  m.enc_w.resize(L); m.enc_b.resize(L); m.dec_w.resize(L); m.dec_b.resize(L); m.dec_ldw.resize(L);
+  for (int l = 0; l < L; ++l) {
+    int ld;
+    if ((rc = pack_lstm(bv.src[l], false, &m.enc_w[l], &m.enc_b[l], &ld))) return rc;
+    if ((rc = pack_lstm(bv.tgt[l], l == 0 && desc.feed_input, &m.dec_w[l], &m.dec_b[l], &m.dec_ldw[l]))) return rc;
+  }
+  // attention projections: rows < Hp: W_p (out n, in k) = blob[k*H + n];
+  // rows Hp + j: (W_a^T h)[j] = sum_i W_a[i,j] h[i], W_a[i,j] = blob[j*H + i]  (src/layer_attention.h:327)
+  host.assign((size_t)2 * Hp * Hp, 0.f);
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < H; ++n)
+    for (int kx = 0; kx < H; ++kx) {
+      host[(size_t)n * Hp + kx] = bv.Wp[(size_t)kx * H + n];
+      host[(size_t)(Hp + n) * Hp + kx] = bv.Wa[(size_t)n * H + kx];
+    }
+  if ((rc = upload(&m.att_proj_w, host.size()))) return rc;
+  // attention output: columns (ctx | h_top) -> W_c1 | W_c2 (src/layer_attention.h:441,448)
+  host.assign((size_t)Hp * 2 * Hp, 0.f);
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < H; ++n)
+    for (int kx = 0; kx < H; ++kx) {
+      host[(size_t)n * 2 * Hp + kx] = bv.Wc1[(size_t)kx * H + n];
+      host[(size_t)n * 2 * Hp + Hp + kx] = bv.Wc2[(size_t)kx * H + n];
+    }
+  if ((rc = upload(&m.att_out_w, host.size()))) return rc;
+  host.assign(Hp, 0.f);
+  std::memcpy(host.data(), bv.bout, sizeof(float) * H);
+  if ((rc = upload(&m.att_bout, host.size()))) return rc;
+  host.assign(Hp, 0.f);
+  std::memcpy(host.data(), bv.vp, sizeof(float) * H);
+  if ((rc = upload(&m.vp, host.size()))) return rc;
+  // output matrix D (V x H), element (v,h) = blob[h*V + v]  ->  [Vp][Hp]
+  host.assign((size_t)Vp * Hp, 0.f);
+#pragma omp parallel for schedule(static)
+  for (int v = 0; v < V; ++v)
+    for (int kx = 0; kx < H; ++kx) host[(size_t)v * Hp + kx] = bv.D[(size_t)kx * V + v];
+  if ((rc = upload(&m.voc_w, host.size()))) return rc;
+  host.assign(Vp, 0.f);
+  std::memcpy(host.data(), bv.bd, sizeof(float) * V);
+  if ((rc = upload(&m.voc_b, host.size()))) return rc;
+  return LINMT_OK;
+}
+
+int Engine::alloc_state(DevState& s) {
+  const size_t rh = (size_t)R * Hp;
+  DA(s.x, rh);
+  s.h_cur.resize(L); s.c_cur.resize(L); s.h_prev.resize(L); s.c_prev.resize(L);
+  for (int l = 0; l < L; ++l) { DA(s.h_cur[l], rh); DA(s.c_cur[l], rh); DA(s.h_prev[l], rh); DA(s.c_prev[l], rh); }
+  DA(s.htilde, rh); DA(s.htilde_prev, rh);
+  DA(s.proj, 2 * rh); DA(s.ctx, rh);
+  DA(s.logits, (size_t)R * Vp);
+  DA(s.hs, (size_t)B * opt.max_src_len * Hp);
+  DA(s.enc_x, (size_t)B * Hp);
+  for (int i = 0; i < 2; ++i) {
+    s.enc_h[i].resize(L); s.enc_c[i].resize(L);
+    for (int l = 0; l < L; ++l) { DA(s.enc_h[i][l], (size_t)B * Hp); DA(s.enc_c[i][l], (size_t)B * Hp); }
+  }
+  return LINMT_OK;
+}
+
+int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, size_t blob_floats, const linmt_options& o) {
+  desc = d; opt = o; n_models = nm;
+  if (d.layers < 1 || d.layers > 5 || d.hidden < 4 || d.vocab_tgt < 4 || d.vocab_src < 1)
+    return fail(LINMT_EINVAL, "bad model dimensions (layers 1..5)");
+  if (nm < 1) return fail(LINMT_EINVAL, "need at least one model");
+  if (nm > 1) return fail(LINMT_EINVAL, "ensembles are not built in this version");
+  if (o.precision != LINMT_PREC_FP32) return fail(LINMT_EINVAL, "only fp32 precision is built in this version");
+  if (linmt_blob_floats(&d) != blob_floats) return fail(LINMT_EINVAL, "weight blob size does not match the model dimensions");
+  if (o.beam <= 0) return fail(LINMT_EINVAL, "--beam-size cannot be <= 0");
+  if (o.penalty < 0) return fail(LINMT_EINVAL, "--penalty cannot be < 0");
+  if (o.nbest < 1 || o.nbest > 32) return fail(LINMT_EINVAL, "nbest must be in 1..32");
+  if (o.max_batch < 1 || o.max_src_len < 1 || o.max_steps < 1) return fail(LINMT_EINVAL, "bad capacity options");
+  L = d.layers; H = d.hidden; V = d.vocab_tgt;
+  k = std::min<int>(o.beam, (int)std::sqrt((double)V));  // src/decoder.h:1549-1551
+  if (k > kMaxBeam) return fail(LINMT_ELIMIT, "beam larger than 31 is not supported");
+  kk = k + 1;
+  Hp = round_up(H, 64);
+  Vp = round_up(V, 128);
+  B = o.max_batch; R = B * k;
+  win = (o.attention_mode == LINMT_ATT_LOCAL_P_GENERAL) ? 2 * o.attention_d + 1 : o.max_src_len;
+  Tcap = o.max_steps + 1;
+  fin_cap = Tcap * k;
+  CK(cudaSetDevice(o.device));
+  int cc_major = 0;
+  CK(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, o.device));
+  if (cc_major != 10) return fail(LINMT_ECUDA, "this library is built for sm_100a (B200) only");
+  CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  CK(cudaEventCreate(&ev0_)); CK(cudaEventCreate(&ev1_));
+  models_.resize(nm); states_.resize(nm);
+  for (int i = 0; i < nm; ++i) {
+    int rc = pack_model(blobs[i], models_[i]);
+    if (rc) return rc;
+    if ((rc = alloc_state(states_[i]))) return rc;
+  }
+  DA(d_off_, B + 1); DA(d_len_, B); DA(d_steps_, B); DA(d_orig_, B);
+  CK(cudaMallocHost(&h_meta_, sizeof(int32_t) * 4 * (B + 1)));
+  DA(d_tok_, R); DA(d_parent_, R); DA(d_score_, R);
+  DA(d_hist_tok_, (size_t)Tcap * R); DA(d_hist_parent_, (size_t)Tcap * R);
+  DA(d_fin_t_, (size_t)B * fin_cap); DA(d_fin_b_, (size_t)B * fin_cap); DA(d_fin_n_, B);
+  DA(d_fin_score_, (size_t)B * fin_cap); DA(d_fin_final_, (size_t)B * fin_cap);
+  DA(d_cand_idx_, (size_t)R * kk); DA(d_cand_logp_, (size_t)R * kk); DA(d_eos_logp_, R);
+  if (o.print_info) {
+    DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
+  }
+  // kernels that may need more than the default dynamic shared memory
+  CK(cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 8));
+  CK(cudaStreamSynchronize(stream));
+  return LINMT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Encoder (NeuralMachineTranslation::ForwardPropSource, src/deep_rnn.h:1572-1721): all
+// sentences of the batch advance together, one position per round; a row stops changing
+// once its sentence is consumed.  Top-layer states go to hs[b][pos].
+int Engine::run_encoder(int n, int Smax) {
+  for (int mi = 0; mi < n_models; ++mi) {
+    DevModel& m = models_[mi];
+    DevState& s = states_[mi];
+    for (int l = 0; l < L; ++l) {
+      CK(cudaMemsetAsync(s.enc_h[0][l], 0, sizeof(float) * (size_t)B * Hp, stream));
+      CK(cudaMemsetAsync(s.enc_c[0][l], 0, sizeof(float) * (size_t)B * Hp, stream));
+    }
+    for (int pos = 0; pos < Smax; ++pos) {
+      const int in = pos & 1, out = in ^ 1;
+      enc_embed_kernel<<<n, 256, 0, stream>>>(cur_ids_, d_off_, d_len_, m.emb_src, desc.vocab_src, s.enc_x, Hp, pos);
+      LAUNCHED();
+      for (int l = 0; l < L; ++l) {
+        ASegs a{};
+        a.ptr[0] = (l == 0) ? s.enc_x : s.enc_h[out][l - 1]; a.ld[0] = Hp;
+        a.ptr[1] = s.enc_h[in][l]; a.ld[1] = Hp;
+        a.nseg = 2; a.seg_k = Hp;
+        EpiLstm e{};
+        e.bias = m.enc_b[l]; e.c_prev = s.enc_c[in][l]; e.h_prev = s.enc_h[in][l];
+        e.c_out = s.enc_c[out][l]; e.h_out = s.enc_h[out][l];
+        e.h_out2 = (l == L - 1) ? s.hs + (size_t)pos * Hp : nullptr;
+        e.h2_row_stride = (long long)opt.max_src_len * Hp;
+        e.row_len = d_len_; e.pos = pos; e.ld = Hp;
+        CK(gemm_simt(a, m.enc_w[l], 2 * Hp, n, 4 * Hp, 2 * Hp, e, stream));
+        LAUNCHED();
+      }
+    }
+  }
+  return LINMT_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// One decoder forward for the first `rows` rows plus beam selection
+// (DecoderModelWrapper::ForwardPropTarget src/decoder.h:1396-1423,
+//  NeuralMachineTranslation::ForwardPropTarget src/deep_rnn.h:1754-1836).
+int Engine::run_decoder_step(int t, int rows) {
+  DevModel& m = models_[0];
+  DevState& s = states_[0];
+  const int n_act = rows / k;
+  // 1. reorder states through the parents, look up the new tokens' embeddings
+  {
+    PrepArrays pa{};
+    int na = 0;
+    for (int l = 0; l < L; ++l) {
+      pa.src[na] = (t == 0) ? enc_final_h_[l] : s.h_cur[l]; pa.dst[na++] = s.h_prev[l];
+      pa.src[na] = (t == 0) ? enc_final_c_[l] : s.c_cur[l]; pa.dst[na++] = s.c_prev[l];
+    }
+    if (t > 0 && desc.feed_input) { pa.src[na] = s.htilde; pa.dst[na++] = s.htilde_prev; }
+    pa.n_arr = na;
+    dim3 grid(rows, na + 1);
+    dec_prep_kernel<<<grid, 256, 0, stream>>>(pa, d_parent_, d_tok_, m.emb_tgt, V, s.x, Hp, k, t == 0 ? 1 : 0);
+    LAUNCHED();
+  }
+  // 2. LSTM stack
+  for (int l = 0; l < L; ++l) {
+    ASegs a{};
+    a.seg_k = Hp;
+    a.ptr[0] = (l == 0) ? s.x : s.h_cur[l - 1]; a.ld[0] = Hp;
+    a.ptr[1] = s.h_prev[l]; a.ld[1] = Hp;
+    a.nseg = 2;
+    if (l == 0 && desc.feed_input && t > 0) { a.ptr[2] = s.htilde_prev; a.ld[2] = Hp; a.nseg = 3; }  // node_input_to_hidden.h:325
+    EpiLstm e{};
+    e.bias = m.dec_b[l]; e.c_prev = s.c_prev[l]; e.h_prev = s.h_prev[l];
+    e.c_out = s.c_cur[l]; e.h_out = s.h_cur[l]; e.h_out2 = nullptr; e.h2_row_stride = 0;
+    e.row_len = nullptr; e.pos = 0; e.ld = Hp;
+    CK(gemm_simt(a, m.dec_w[l], m.dec_ldw[l], rows, 4 * Hp, a.nseg * Hp, e, stream));
+    LAUNCHED();
+  }
+  float* htop = s.h_cur[L - 1];
+  // 3. attention projections
+  const float* u_alt = nullptr;
+  if (opt.attention_mode == LINMT_ATT_LOCAL_P_GENERAL) {
+    ASegs a{}; a.ptr[0] = htop; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
+    EpiAttnProj e{s.proj, 2 * Hp, Hp};
+    CK(gemm_simt(a, m.att_proj_w, Hp, rows, 2 * Hp, Hp, e, stream));
+    LAUNCHED();
+  } else if (opt.attention_mode == LINMT_ATT_GLOBAL_GENERAL) {
+    ASegs a{}; a.ptr[0] = htop; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
+    EpiBias e{nullptr, s.proj + Hp, 2 * Hp};
+    CK(gemm_simt(a, m.att_proj_w + (size_t)Hp * Hp, Hp, rows, Hp, Hp, e, stream));
+    LAUNCHED();
+  } else {
+    u_alt = htop;
+  }
+  // 4. scores, softmax x Gaussian, context
+  {
+    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
+    int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
+    int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
+    const size_t smem = sizeof(float) * (win + 8);
+    attention_kernel<<<rows, 128, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
+                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv);
+    LAUNCHED();
+  }
+  // 5. attentional state htilde = tanh(W_c1 ctx + W_c2 h + b)
+  {
+    ASegs a{}; a.ptr[0] = s.ctx; a.ld[0] = Hp; a.ptr[1] = htop; a.ld[1] = Hp; a.nseg = 2; a.seg_k = Hp;
+    EpiBiasTanh e{m.att_bout, s.htilde, Hp};
+    CK(gemm_simt(a, m.att_out_w, 2 * Hp, rows, Hp, 2 * Hp, e, stream));
+    LAUNCHED();
+  }
+  // 6. logits
+  {
+    ASegs a{}; a.ptr[0] = s.htilde; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
+    EpiBias e{m.voc_b, s.logits, Vp};
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (kernel_timing) {
+      if (gemm_ev_used_ + 2 > gemm_ev_.size()) {
+        for (int i = 0; i < 2; ++i) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); gemm_ev_.push_back(ev); }
+      }
+      e0 = gemm_ev_[gemm_ev_used_++]; e1 = gemm_ev_[gemm_ev_used_++];
+      CK(cudaEventRecord(e0, stream));
+    }
+    CK(gemm_simt(a, m.voc_w, Hp, rows, Vp, Hp, e, stream));
+    LAUNCHED();
+    if (kernel_timing) CK(cudaEventRecord(e1, stream));
+  }
+  // 7. log-softmax statistics + per-beam top-(k+1)
+  {
+    TopkOut o{d_cand_idx_, d_cand_logp_, d_eos_logp_};
+    softmax_topk_kernel<<<rows, 256, (size_t)256 * kk * 8, stream>>>(s.logits, Vp, V, kk, o);
+    LAUNCHED();
+  }
+  // 8. beam selection
+  {
+    BeamState bs{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
+    const size_t smem = (size_t)k * kk * 16;
+    beam_select_kernel<<<n_act, 128, smem, stream>>>(bs, d_cand_idx_, d_cand_logp_, d_eos_logp_, d_steps_, d_orig_, t, k,
+                                                     opt.penalty, opt.diversity, trace_dev_);
+    LAUNCHED();
+  }
+  CK(cudaGetLastError());
+  stats.decoder_row_steps += rows;
+  stats.sentence_steps += n_act;
+  return LINMT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode of one device batch (n <= max_batch); every data pointer is a device pointer.
+int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, const int32_t* steps_host, int max_len,
+                        int32_t* d_out_tok, int32_t* d_out_len, float* d_out_score, int32_t* d_out_vit, float* d_out_align,
+                        const linmt_trace* trace_dev, int trace_Tm) {
+  if (n < 1) return LINMT_OK;
+  if (n > B) return fail(LINMT_ELIMIT, "batch larger than max_batch");
+  // order by step count, longest first: the rows still decoding at any step are a prefix
+  std::vector<int> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return steps_host[a] > steps_host[b]; });
+  int32_t* m_off = h_meta_;
+  int32_t* m_len = h_meta_ + (B + 1);
+  int32_t* m_steps = h_meta_ + 2 * (B + 1);
+  int32_t* m_orig = h_meta_ + 3 * (B + 1);
+  int Smax = 0, Tm = 0;
+  for (int i = 0; i < n; ++i) {
+    const int s = order[i];
+    const int len = off_host[s + 1] - off_host[s];
+    if (len < 1) return fail(LINMT_EINVAL, "empty source sentence");
+    if (len > opt.max_src_len) return fail(LINMT_ELIMIT, "source sentence longer than max_src_len");
+    if (steps_host[s] < 0 || steps_host[s] > opt.max_steps) return fail(LINMT_ELIMIT, "step count outside 0..max_steps");
+    m_off[i] = off_host[s]; m_len[i] = len; m_steps[i] = steps_host[s]; m_orig[i] = s;
+    Smax = std::max(Smax, len); Tm = std::max(Tm, steps_host[s]);
+  }
+  if (max_len < Tm + 2) return fail(LINMT_EINVAL, "max_len smaller than max steps + 2");
+  CK(cudaSetDevice(opt.device));
+  CK(cudaEventRecord(ev0_, stream));
+  CK(cudaMemcpyAsync(d_off_, m_off, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream));
+  CK(cudaMemcpyAsync(d_len_, m_len, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream));
+  CK(cudaMemcpyAsync(d_steps_, m_steps, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream));
+  CK(cudaMemcpyAsync(d_orig_, m_orig, sizeof(int32_t) * n, cudaMemcpyHostToDevice, stream));
+  CK(cudaMemsetAsync(d_tok_, 0, sizeof(int32_t) * R, stream));     // START = 0 (src/decoder.h:339-342)
+  CK(cudaMemsetAsync(d_parent_, 0, sizeof(int32_t) * R, stream));
+  CK(cudaMemsetAsync(d_score_, 0, sizeof(float) * R, stream));
+  CK(cudaMemsetAsync(d_fin_n_, 0, sizeof(int32_t) * B, stream));
+  cur_ids_ = d_ids;
+  trace_dev_ = TraceDev{};
+  if (trace_dev) {
+    trace_dev_.cand_tok = trace_dev->cand_tok; trace_dev_.cand_logp = trace_dev->cand_logp;
+    trace_dev_.surv_tok = trace_dev->surv_tok; trace_dev_.surv_parent = trace_dev->surv_parent;
+    trace_dev_.surv_score = trace_dev->surv_score; trace_dev_.final_logp = trace_dev->final_logp;
+    trace_dev_.force_tok = trace_dev->force_tok; trace_dev_.force_parent = trace_dev->force_parent;
+    trace_dev_.force_score = trace_dev->force_score; trace_dev_.Tm = trace_Tm;
+  }
+  gemm_ev_used_ = 0;
+  int rc = run_encoder(n, Smax);
+  if (rc) return rc;
+  // the encoder's final states sit in buffer (Smax & 1)
+  enc_final_h_.assign(states_[0].enc_h[Smax & 1].begin(), states_[0].enc_h[Smax & 1].end());
+  enc_final_c_.assign(states_[0].enc_c[Smax & 1].begin(), states_[0].enc_c[Smax & 1].end());
+  for (int t = 0; t <= Tm; ++t) {
+    int n_act = 0;
+    while (n_act < n && m_steps[n_act] >= t) ++n_act;
+    if (n_act == 0) break;
+    if ((rc = run_decoder_step(t, n_act * k))) return rc;
+  }
+  {
+    FinalizeArgs a{};
+    a.bs = BeamState{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
+    a.steps = d_steps_; a.src_len = d_len_; a.orig = d_orig_;
+    a.rec_align = d_rec_align_; a.rec_lo = d_rec_lo_; a.rec_vit = d_rec_vit_;
+    a.fin_final = d_fin_final_; a.win = win; a.k = k; a.nbest = opt.nbest; a.max_len = max_len; a.max_src = opt.max_src_len;
+    a.lp_alpha = opt.lp_alpha; a.cp_beta = opt.cp_beta; a.min_ratio = opt.min_ratio;
+    a.out_tok = d_out_tok; a.out_len = d_out_len; a.out_score = d_out_score; a.out_vit = d_out_vit; a.out_align = d_out_align;
+    const size_t smem = 4 * ((size_t)opt.max_src_len * sizeof(float) + (size_t)max_len * sizeof(int));
+    finalize_kernel<<<n, 128, smem, stream>>>(a);
+    LAUNCHED();
+    CK(cudaGetLastError());
+  }
+  CK(cudaEventRecord(ev1_, stream));
+  return LINMT_OK;
+}
+
+int Engine::finish_timing() {
+  CK(cudaStreamSynchronize(stream));
+  CK(cudaEventElapsedTime(&stats.last_decode_ms, ev0_, ev1_));
+  stats.last_gemm_ms = 0.f;
+  stats.last_gemm_launches = (int)(gemm_ev_used_ / 2);
+  for (size_t i = 0; i + 1 < gemm_ev_used_; i += 2) {
+    float ms = 0.f;
+    CK(cudaEventElapsedTime(&ms, gemm_ev_[i], gemm_ev_[i + 1]));
+    stats.last_gemm_ms += ms;
+  }
+  return LINMT_OK;
+}
+
+// Host-pointer front of decode_core: copies ids in, results out, in chunks of max_batch.
+int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, const int32_t* steps, int max_len,
+                        int32_t* out_tok, int32_t* out_len, float* out_score, int32_t* out_vit, float* out_align,
+                        const linmt_trace* trace) {
+  if (n < 0 || !src_ids || !src_off || !steps || !out_tok || !out_len || !out_score) return fail(LINMT_EINVAL, "null argument");
+  if (out_align && !opt.print_info) return fail(LINMT_EINVAL, "alignments need print_info = 1");
+  CK(cudaSetDevice(opt.device));
+  const int nb = opt.nbest;
+  int Tm_all = 0;
+  for (int i = 0; i < n; ++i) Tm_all = std::max(Tm_all, steps[i]);
+  float total_ms = 0.f, gemm_ms = 0.f;
+  int gemm_launches = 0;
+  for (int c0 = 0; c0 < n; c0 += B) {
+    const int cn = std::min(B, n - c0);
+    const int32_t base = src_off[c0];
+    const size_t n_ids = (size_t)(src_off[c0 + cn] - base);
+    if (n_ids > d_ids_cap_) {
+      DA(d_ids_, n_ids + 1024);
+      d_ids_cap_ = n_ids + 1024;
+    }
+    const size_t need = (size_t)cn * nb;
+    if (need > out_cap_len_ || max_len > out_cap_maxlen_) {
+      const size_t ml = std::max<size_t>(max_len, out_cap_maxlen_);
+      const size_t cap = std::max<size_t>(need, (size_t)B * nb);
+      DA(d_out_tok_, cap * ml); DA(d_out_vit_, cap * ml); DA(d_out_len_, cap); DA(d_out_score_, cap);
+      if (opt.print_info) DA(d_out_align_, cap * ml * opt.max_src_len);
+      out_cap_len_ = cap; out_cap_maxlen_ = ml;
+    }
+    CK(cudaMemcpyAsync(d_ids_, src_ids + base, n_ids * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    std::vector<int32_t> off(cn + 1);
+    for (int i = 0; i <= cn; ++i) off[i] = src_off[c0 + i] - base;
+    // per-chunk device trace buffers
+    linmt_trace td{};
+    std::vector<std::pair<void*, std::pair<void*, size_t>>> copy_back;  // (device, (host, bytes))
+    if (trace) {
+      for (void* p : trace_allocs_) cudaFree(p);
+      trace_allocs_.clear();
+      const size_t n_c = (size_t)cn * Tm_all * k * kk, n_s = (size_t)cn * Tm_all * k, n_f = (size_t)cn * k;
+      auto mk = [&](size_t count, size_t esz, void* host_dst, const void* host_src, void** dev) -> int {
+        if (!host_dst && !host_src) { *dev = nullptr; return LINMT_OK; }
+        void* q = nullptr;
+        if (cudaMalloc(&q, std::max<size_t>(count, 1) * esz) != cudaSuccess) return fail(LINMT_ENOMEM, "trace buffer allocation failed");
+        trace_allocs_.push_back(q);
+        if (host_src) {
+          if (cudaMemcpyAsync(q, host_src, count * esz, cudaMemcpyHostToDevice, stream) != cudaSuccess) return fail(LINMT_ECUDA, "trace upload failed");
+        } else {
+          if (cudaMemsetAsync(q, 0xff, count * esz, stream) != cudaSuccess) return fail(LINMT_ECUDA, "trace clear failed");
+          copy_back.push_back({q, {host_dst, count * esz}});
+        }
+        *dev = q;
+        return LINMT_OK;
+      };
+      int rc;
+      if ((rc = mk(n_c, 4, trace->cand_tok ? trace->cand_tok + (size_t)c0 * Tm_all * k * kk : nullptr, nullptr, (void**)&td.cand_tok))) return rc;
+      if ((rc = mk(n_c, 4, trace->cand_logp ? trace->cand_logp + (size_t)c0 * Tm_all * k * kk : nullptr, nullptr, (void**)&td.cand_logp))) return rc;
+      if ((rc = mk(n_s, 4, trace->surv_tok ? trace->surv_tok + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_tok))) return rc;
+      if ((rc = mk(n_s, 4, trace->surv_parent ? trace->surv_parent + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_parent))) return rc;
+      if ((rc = mk(n_s, 4, trace->surv_score ? trace->surv_score + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_score))) return rc;
+      if ((rc = mk(n_f, 4, trace->final_logp ? trace->final_logp + (size_t)c0 * k : nullptr, nullptr, (void**)&td.final_logp))) return rc;
+      if ((rc = mk(n_s, 4, nullptr, trace->force_tok ? trace->force_tok + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_tok))) return rc;
+      if ((rc = mk(n_s, 4, nullptr, trace->force_parent ? trace->force_parent + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_parent))) return rc;
+      if ((rc = mk(n_s, 4, nullptr, trace->force_score ? trace->force_score + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_score))) return rc;
+    }
+    int rc = decode_core(d_ids_, off.data(), cn, steps + c0, max_len, d_out_tok_, d_out_len_, d_out_score_,
+                         out_vit ? d_out_vit_ : nullptr, out_align ? d_out_align_ : nullptr, trace ? &td : nullptr, Tm_all);
+    if (rc) return rc;
+    CK(cudaMemcpyAsync(out_tok + (size_t)c0 * nb * max_len, d_out_tok_, need * max_len * 4, cudaMemcpyDeviceToHost, stream));
+    CK(cudaMemcpyAsync(out_len + (size_t)c0 * nb, d_out_len_, need * 4, cudaMemcpyDeviceToHost, stream));
+    CK(cudaMemcpyAsync(out_score + (size_t)c0 * nb, d_out_score_, need * 4, cudaMemcpyDeviceToHost, stream));
+    if (out_vit) CK(cudaMemcpyAsync(out_vit + (size_t)c0 * nb * max_len, d_out_vit_, need * max_len * 4, cudaMemcpyDeviceToHost, stream));
+    if (out_align)
+      CK(cudaMemcpyAsync(out_align + (size_t)c0 * nb * max_len * opt.max_src_len, d_out_align_,
+                         need * max_len * opt.max_src_len * 4, cudaMemcpyDeviceToHost, stream));
+    for (auto& cb : copy_back) CK(cudaMemcpyAsync(cb.second.first, cb.first, cb.second.second, cudaMemcpyDeviceToHost, stream));
+    if ((rc = finish_timing())) return rc;
+    total_ms += stats.last_decode_ms; gemm_ms += stats.last_gemm_ms; gemm_launches += stats.last_gemm_launches;
+  }
+  stats.last_decode_ms = total_ms; stats.last_gemm_ms = gemm_ms; stats.last_gemm_launches = gemm_launches;
+  return LINMT_OK;
+}
+
+}  // namespace linmt
+
+// =========================================================================================
+// C ABI (numeric part; the sentence front-end lives in frontend.cpp)
+// =========================================================================================
+using linmt::Engine;
+
+
+static std::string g_create_error;
+
+extern "C" {
+
+void linmt_default_options(linmt_options* o) {
+  std::memset(o, 0, sizeof(*o));
+  o->beam = 12; o->nbest = 1; o->attention_mode = LINMT_ATT_LOCAL_P_GENERAL; o->attention_d = 10;
+  o->print_info = 0; o->precision = LINMT_PREC_FP32; o->ensemble_mode = LINMT_ENS_PROB_MEAN; o->gemm_path = LINMT_GEMM_AUTO;
+  o->max_batch = 64; o->max_src_len = 100; o->max_steps = 200; o->device = 0;
+  o->penalty = 0.f; o->diversity = 0.f; o->lp_alpha = 0.65f; o->cp_beta = 0.20f; o->min_ratio = 0.5f; o->max_ratio = 1.5f;
+}
+
+size_t linmt_blob_floats(const linmt_model_desc* d) {
+  const size_t H = d->hidden, hh = H * H, L = d->layers;
+  size_t n = 0;
+  n += 8 * hh + 4 * H + H * (size_t)d->vocab_src;
+  n += (L - 1) * (8 * hh + 4 * H);
+  n += 8 * hh + 4 * H + H * (size_t)d->vocab_tgt + (d->feed_input ? 4 * hh : 0);
+  n += (L - 1) * (8 * hh + 4 * H);
+  n += 4 * hh + 2 * H;
+  n += (size_t)d->vocab_tgt * H + d->vocab_tgt;
+  return n;
+}
+
+int linmt_create_from_weights(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models, size_t blob_floats,
+                              const linmt_options* opt, linmt_engine** out) {
+  if (!desc || !blobs || !opt || !out) { g_create_error = "null argument"; return LINMT_EINVAL; }
+  linmt_engine* e = new (std::nothrow) linmt_engine();
+  if (!e) { g_create_error = "out of host memory"; return LINMT_ENOMEM; }
+  int rc = e->eng.init(*desc, blobs, n_models, blob_floats, *opt);
+  if (rc != LINMT_OK) {
+    g_create_error = e->eng.err;
+    delete e;
+    *out = nullptr;
+    return rc;
+  }
+  *out = e;
+  return LINMT_OK;
+}
+
+void linmt_destroy(linmt_engine* e) { delete e; }
+
+const char* linmt_last_error(const linmt_engine* e) { return e ? e->eng.err.c_str() : g_create_error.c_str(); }
+
+int32_t linmt_beam(const linmt_engine* e) { return e ? e->eng.k : 0; }
+
+int linmt_decode_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* src_off, int32_t n, const int32_t* steps,
+                       int32_t max_len, int32_t* out_tok, int32_t* out_len, float* out_score, int32_t* out_vit,
+                       float* out_align, const linmt_trace* trace) {
+  if (!e) return LINMT_EINVAL;
+  return e->eng.decode_host(src_ids, src_off, n, steps, max_len, out_tok, out_len, out_score, out_vit, out_align, trace);
+}
+
+int linmt_decode_batch_device(linmt_engine* e, const int32_t* d_src_ids, const int32_t* src_off_host, int32_t n,
+                              const int32_t* steps_host, int32_t max_len, int32_t* d_out_tok, int32_t* d_out_len,
+                              float* d_out_score) {
+  if (!e) return LINMT_EINVAL;
+  int rc = e->eng.decode_core(d_src_ids, src_off_host, n, steps_host, max_len, d_out_tok, d_out_len, d_out_score, nullptr,
+                              nullptr, nullptr, 0);
+  if (rc) return rc;
+  return e->eng.finish_timing();
+}
+
+int linmt_get_stats(const linmt_engine* e, linmt_stats* out) {
+  if (!e || !out) return LINMT_EINVAL;
+  *out = e->eng.stats;
+  return LINMT_OK;
+}
+
+int linmt_set_kernel_timing(linmt_engine* e, int32_t on) {
+  if (!e) return LINMT_EINVAL;
+  e->eng.kernel_timing = on != 0;
+  return LINMT_OK;
+}
+
+}  // extern "C"

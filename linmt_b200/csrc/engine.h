@@ -1,0 +1,122 @@
+// engine.h -- the decoding engine behind the C ABI (host side, C++).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/linmt_decoder.h"
+#include "step_kernels.cuh"
+
+namespace linmt {
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Packed weights of one ensemble member in device memory.  Every dense operand is stored
+// K-major ("[out][in]", in padded to Hp) so both GEMM operands are K-contiguous.
+struct DevModel {
+  float* emb_src = nullptr;              // [Vs][Hp]
+  float* emb_tgt = nullptr;              // [V][Hp]
+  std::vector<float*> enc_w, enc_b;      // [4Hp][2Hp], [4Hp]   gate-interleaved rows 4j+g
+  std::vector<float*> dec_w, dec_b;      // layer 0: [4Hp][3Hp] (x | h' | htilde'), others [4Hp][2Hp]
+  std::vector<int> dec_ldw;
+  float* att_proj_w = nullptr;           // [2Hp][Hp]: rows < Hp = W_p, rows >= Hp = W_a^T
+  float* att_out_w = nullptr;            // [Hp][2Hp]: (ctx | h_top)
+  float* att_bout = nullptr;             // [Hp]
+  float* vp = nullptr;                   // [Hp]
+  float* voc_w = nullptr;                // [Vp][Hp]
+  float* voc_b = nullptr;                // [Vp]
+};
+
+struct DevState {
+  float* x = nullptr;                        // [R][Hp]
+  std::vector<float*> h_cur, c_cur, h_prev, c_prev;  // [L] x [R][Hp]
+  float *htilde = nullptr, *htilde_prev = nullptr;   // [R][Hp]
+  float *proj = nullptr, *ctx = nullptr;             // [R][2Hp], [R][Hp]
+  float* logits = nullptr;                           // [R][Vp]
+  float* hs = nullptr;                               // [B][max_src][Hp]
+  float* enc_x = nullptr;                            // [B][Hp]
+  std::vector<float*> enc_h[2], enc_c[2];            // [L] x [B][Hp], double buffered
+};
+
+class Engine {
+ public:
+  Engine() = default;
+  ~Engine();
+  int init(const linmt_model_desc& d, const float* const* blobs, int n_models, size_t blob_floats, const linmt_options& o);
+  int decode_core(const int32_t* d_ids, const int32_t* off_host, int n, const int32_t* steps_host, int max_len,
+                  int32_t* d_out_tok, int32_t* d_out_len, float* d_out_score, int32_t* d_out_vit, float* d_out_align,
+                  const linmt_trace* trace_dev, int trace_Tm);
+  int finish_timing();
+  int decode_host(const int32_t* src_ids, const int32_t* src_off, int n, const int32_t* steps, int max_len,
+                  int32_t* out_tok, int32_t* out_len, float* out_score, int32_t* out_vit, float* out_align,
+                  const linmt_trace* trace);
+
+  std::string err;
+  linmt_model_desc desc{};
+  linmt_options opt{};
+  int k = 0, kk = 0, H = 0, Hp = 0, V = 0, Vp = 0, L = 0, B = 0, R = 0, win = 0, Tcap = 0, fin_cap = 0;
+  int n_models = 0;
+  cudaStream_t stream = nullptr;
+  linmt_stats stats{};
+  bool kernel_timing = false;
+
+  // sentence front-end (filled by the config-file constructor)
+  std::vector<std::string> tgt_words;
+  std::vector<std::pair<std::string, int>> src_words_sorted;
+  int longest_sentence = 0;
+  int print_align_scores = 0;
+  std::string result_buf;
+
+ private:
+  int fail(int code, const std::string& msg) { err = msg; return code; }
+  int pack_model(const float* blob, DevModel& m);
+  int alloc_state(DevState& s);
+  int run_encoder(int n, int Smax);
+  int run_decoder_step(int t, int rows);
+
+  const int32_t* cur_ids_ = nullptr;
+  TraceDev trace_dev_{};
+  std::vector<float*> enc_final_h_, enc_final_c_;
+  size_t out_cap_maxlen_ = 0;
+  std::vector<DevModel> models_;
+  std::vector<DevState> states_;
+  std::vector<void*> allocs_;
+  template <class T> int dalloc(T** p, size_t count);
+
+  // batch metadata (device) and pinned staging
+  int32_t *d_off_ = nullptr, *d_len_ = nullptr, *d_steps_ = nullptr, *d_orig_ = nullptr;
+  int32_t* h_meta_ = nullptr;  // pinned [4][B+1]
+  // beam state
+  int32_t *d_tok_ = nullptr, *d_parent_ = nullptr, *d_hist_tok_ = nullptr, *d_hist_parent_ = nullptr;
+  float* d_score_ = nullptr;
+  int32_t *d_fin_t_ = nullptr, *d_fin_b_ = nullptr, *d_fin_n_ = nullptr;
+  float *d_fin_score_ = nullptr, *d_fin_final_ = nullptr;
+  int32_t* d_cand_idx_ = nullptr;
+  float *d_cand_logp_ = nullptr, *d_eos_logp_ = nullptr;
+  // alignment records (print_info)
+  float* d_rec_align_ = nullptr;
+  int32_t *d_rec_lo_ = nullptr, *d_rec_vit_ = nullptr;
+  // host staging for decode_host
+  int32_t* d_ids_ = nullptr;
+  size_t d_ids_cap_ = 0;
+  int32_t *d_out_tok_ = nullptr, *d_out_len_ = nullptr, *d_out_vit_ = nullptr;
+  float *d_out_score_ = nullptr, *d_out_align_ = nullptr;
+  size_t out_cap_len_ = 0;
+  // trace buffers (device), sized on demand
+  std::vector<void*> trace_allocs_;
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+  std::vector<cudaEvent_t> gemm_ev_;
+  size_t gemm_ev_used_ = 0;
+};
+
+// host-side weight packing
+void pack_gate_weights(const float* const* mats, int nseg, int H, int Hp, float* out /*[4Hp][nseg*Hp]*/);
+
+}  // namespace linmt
+
+// The opaque handle of the C ABI.
+struct linmt_engine {
+  linmt::Engine eng;
+};

@@ -1,0 +1,69 @@
+// kernel_entry.cu -- single-kernel entry points of the C ABI (host pointers), used by the
+// parity tests to check one kernel at a time against the CPU checker.
+#include <cstring>
+#include <vector>
+
+#include "engine.h"
+#include "gemm_simt.cuh"
+#include "step_kernels.cuh"
+
+namespace {
+struct DevBuf {
+  void* p = nullptr;
+  ~DevBuf() { if (p) cudaFree(p); }
+  cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+  template <class T> T* as() { return static_cast<T*>(p); }
+};
+#define KCK(x) do { if ((x) != cudaSuccess) return LINMT_ECUDA; } while (0)
+}  // namespace
+
+extern "C" {
+
+int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K, int32_t N, int32_t gemm_path,
+                 int32_t precision, int32_t device) {
+  using namespace linmt;
+  if (!X || !W || !Y || R < 1 || K < 1 || N < 1) return LINMT_EINVAL;
+  if (gemm_path != LINMT_GEMM_SIMT || precision != LINMT_PREC_FP32) return LINMT_EINVAL;
+  KCK(cudaSetDevice(device));
+  const int Kp = round_up(K, 64), Np = round_up(N, 128);
+  std::vector<float> xp((size_t)R * Kp, 0.f), wt((size_t)Np * Kp, 0.f);
+  for (int r = 0; r < R; ++r) std::memcpy(&xp[(size_t)r * Kp], X + (size_t)r * K, sizeof(float) * K);
+  for (int n = 0; n < N; ++n)
+    for (int k = 0; k < K; ++k) wt[(size_t)n * Kp + k] = W[(size_t)k * N + n];
+  DevBuf dx, dw, dy;
+  KCK(dx.alloc(xp.size() * 4)); KCK(dw.alloc(wt.size() * 4)); KCK(dy.alloc((size_t)R * Np * 4));
+  KCK(cudaMemcpy(dx.p, xp.data(), xp.size() * 4, cudaMemcpyHostToDevice));
+  KCK(cudaMemcpy(dw.p, wt.data(), wt.size() * 4, cudaMemcpyHostToDevice));
+  ASegs a{}; a.ptr[0] = dx.as<float>(); a.ld[0] = Kp; a.nseg = 1; a.seg_k = Kp;
+  EpiBias e{nullptr, dy.as<float>(), Np};
+  KCK(gemm_simt(a, dw.as<float>(), Kp, R, Np, Kp, e, 0));
+  KCK(cudaDeviceSynchronize());
+  std::vector<float> yp((size_t)R * Np);
+  KCK(cudaMemcpy(yp.data(), dy.p, yp.size() * 4, cudaMemcpyDeviceToHost));
+  for (int r = 0; r < R; ++r) std::memcpy(Y + (size_t)r * N, &yp[(size_t)r * Np], sizeof(float) * N);
+  return LINMT_OK;
+}
+
+int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, int32_t* idx, float* logp,
+                         float* eos_logp, int32_t device) {
+  using namespace linmt;
+  if (!logits || !idx || !logp || R < 1 || V < 2 || kk < 1 || kk > kMaxBeam + 1) return LINMT_EINVAL;
+  KCK(cudaSetDevice(device));
+  const int Vp = round_up(V, 4);
+  std::vector<float> lp((size_t)R * Vp, 0.f);
+  for (int r = 0; r < R; ++r) std::memcpy(&lp[(size_t)r * Vp], logits + (size_t)r * V, sizeof(float) * V);
+  DevBuf dl, di, dp, de;
+  KCK(dl.alloc(lp.size() * 4)); KCK(di.alloc((size_t)R * kk * 4)); KCK(dp.alloc((size_t)R * kk * 4)); KCK(de.alloc((size_t)R * 4));
+  KCK(cudaMemcpy(dl.p, lp.data(), lp.size() * 4, cudaMemcpyHostToDevice));
+  KCK(cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 8));
+  TopkOut o{di.as<int32_t>(), dp.as<float>(), de.as<float>()};
+  softmax_topk_kernel<<<R, 256, (size_t)256 * kk * 8>>>(dl.as<float>(), Vp, V, kk, o);
+  KCK(cudaGetLastError());
+  KCK(cudaDeviceSynchronize());
+  KCK(cudaMemcpy(idx, di.p, (size_t)R * kk * 4, cudaMemcpyDeviceToHost));
+  KCK(cudaMemcpy(logp, dp.p, (size_t)R * kk * 4, cudaMemcpyDeviceToHost));
+  if (eos_logp) KCK(cudaMemcpy(eos_logp, de.p, (size_t)R * 4, cudaMemcpyDeviceToHost));
+  return LINMT_OK;
+}
+
+}  // extern "C"

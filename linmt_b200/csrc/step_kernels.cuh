@@ -1,0 +1,604 @@
+// step_kernels.cuh -- the non-GEMM kernels of the decoding step loop: embedding gather and
+// beam reorder, attention, log-softmax + per-beam top-(k+1), beam selection, finalisation.
+// All beam state lives on the device; the host only launches.
+#pragma once
+#include <cuda_runtime.h>
+#include <float.h>
+#include <math.h>
+#include <stdint.h>
+
+namespace linmt {
+
+constexpr int kMaxBeam = 31;          // kk = beam + 1 <= 32
+constexpr int kStart = 0, kEos = 1, kUnk = 2;  // src/input_file_preprocess.cc:549-567
+constexpr float kDeadScore = -1e30f;  // score of a hypothesis created when candidates run out
+
+// ---------------------------------------------------------------------------------------
+// Encoder input: x[b] = E_src[ids_rev[b][pos]] (SparseLookupKernel,
+// src/deep_rnn_kernel.h:248-255); the sentence is read back to front
+// (src/decoder_sentence.cu:68).  Rows past their length get zeros.
+// grid = (B), block = 256
+static __global__ void enc_embed_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ off,
+                                 const int32_t* __restrict__ len, const float* __restrict__ emb, int vocab,
+                                 float* __restrict__ x, int Hp, int pos) {
+  const int b = blockIdx.x;
+  const int S = len[b];
+  float4* dst = reinterpret_cast<float4*>(x + (size_t)b * Hp);
+  if (pos < S) {
+    int tok = ids[off[b] + (S - 1 - pos)];
+    if (tok < 0 || tok >= vocab) tok = 0;  // out-of-range ids read <UNK> (src/decoder_sentence.cu:61-62)
+    const float4* src = reinterpret_cast<const float4*>(emb + (size_t)tok * Hp);
+    for (int i = threadIdx.x; i < Hp / 4; i += blockDim.x) dst[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < Hp / 4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Start of a decoder step: gathers every state row through the parent chosen by the last
+// beam selection and looks up the new token's embedding.  Replaces SwapDecodingStates +
+// TargetCopyPrevStates (src/deep_rnn.h:1842-1872, 2L(k+1)+k+2L cudaMemcpy calls) and the
+// embedding lookup of src/node_input_to_hidden.h:243.  At step 0 the source rows are the
+// encoder's final states, one per sentence (src/deep_rnn.h:1766-1789).
+//   src[a], dst[a]: n_arr state arrays [rows][Hp]; src_per_sentence = 1 at step 0.
+// grid = (rows, n_arr + 1), block = 256; blockIdx.y == n_arr is the embedding.
+struct PrepArrays {
+  const float* src[12];
+  float* dst[12];
+  int n_arr;
+};
+static __global__ void dec_prep_kernel(PrepArrays arr, const int32_t* __restrict__ parent, const int32_t* __restrict__ tok,
+                                const float* __restrict__ emb, int vocab, float* __restrict__ x, int Hp, int k,
+                                int src_per_sentence) {
+  const int r = blockIdx.x;
+  const int a = blockIdx.y;
+  const float4* src;
+  float4* dst;
+  if (a == arr.n_arr) {
+    int t = tok[r];
+    if (t < 0 || t >= vocab) t = kUnk;
+    src = reinterpret_cast<const float4*>(emb + (size_t)t * Hp);
+    dst = reinterpret_cast<float4*>(x + (size_t)r * Hp);
+  } else {
+    const int sent = r / k;
+    const int srow = src_per_sentence ? sent : sent * k + parent[r];
+    src = reinterpret_cast<const float4*>(arr.src[a] + (size_t)srow * Hp);
+    dst = reinterpret_cast<float4*>(arr.dst[a] + (size_t)r * Hp);
+  }
+  for (int i = threadIdx.x; i < Hp / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------------
+// Block-wide sum in a fixed order (deterministic).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  const int nw = blockDim.x >> 5;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------
+// Attention for one decoder row (AttentionNode::ForwardProp, src/layer_attention.h:243-483,
+// kernels k12-k20: Sgemm m=1, SigmoidKernel, AlignmentPosKernel, LowerUpperKernel,
+// CreateIndicesKernel, LoadInHSKernel, ElemReduceKernelLarge, AlignmentReductionKernel,
+// CreateCTKernel).
+//   proj [rows][2*Hp]: tanh(W_p h) | W_a^T h      (global_dot: `u` = h_top itself)
+//   hs   [B][max_src][Hp]: top encoder state after consuming reversed position p
+//   ctx  [rows][Hp]
+//   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
+//   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
+// grid = rows, block = 128, dynamic smem = (2*win + 8) floats
+static __global__ void __launch_bounds__(128) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+                                 const float* __restrict__ vp, const float* __restrict__ hs,
+                                 const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
+                                 int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
+                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit) {
+  extern __shared__ float sm[];
+  float* e = sm;            // [win]
+  float* red = sm + win;    // [8]
+  __shared__ float s_pt;
+  __shared__ int s_lo, s_hi;
+  const int r = blockIdx.x;
+  const int sent = r / k;
+  const int S = src_len[sent];
+  const float* u = u_alt ? (u_alt + (size_t)r * ldu) : (proj + (size_t)r * ldp + Hp);
+  const float* hsb = hs + (size_t)sent * max_src * Hp;
+
+  if (mode == 0) {
+    float part = 0.f;
+    const float* t1 = proj + (size_t)r * ldp;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) part = fmaf(vp[j], t1[j], part);
+    const float dot = block_sum(part, red);
+    if (threadIdx.x == 0) {
+      const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)dot)));  // SigmoidKernel, deep_rnn_kernel.h:1075-1080
+      const float pt = (float)S * sg;
+      s_pt = pt;
+      s_lo = (0 > (int)pt - D) ? 0 : ((int)pt - D);                       // LowerUpperKernel, :1094-1100
+      s_hi = ((S - 1) < (int)pt + D) ? (S - 1) : ((int)pt + D);
+    }
+  } else if (threadIdx.x == 0) {
+    s_pt = 0.f; s_lo = 0; s_hi = S - 1;
+  }
+  __syncthreads();
+  const int lo = s_lo, hi = s_hi;
+  const int W = hi - lo + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int w = warp; w < W; w += nw) {
+    const float* hrow = hsb + (size_t)(S - 1 - (lo + w)) * Hp;
+    float acc = 0.f;
+    for (int j = lane * 4; j < Hp; j += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(hrow + j);
+      const float4 b = *reinterpret_cast<const float4*>(u + j);
+      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) e[w] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // AlignmentReductionKernel, deep_rnn_kernel.h:1197-1241 (max starts at 0, no
+    // renormalisation after the Gaussian)
+    float mx = 0.f;
+    for (int w = 0; w < W; ++w) if (e[w] > mx) mx = e[w];
+    float sum = 0.f;
+    for (int w = 0; w < W; ++w) { e[w] = expf(e[w] - mx); sum += e[w]; }
+    const float sigma_sq = ((float)D * (float)D) / 4.0f;
+    const float pt = s_pt;
+    float best = 0.f; int besti = -1;
+    for (int w = 0; w < W; ++w) {
+      float a = e[w];
+      if (mode == 0) {
+        const float tmp = expf((-1 * powf(pt - (float)(lo + w), 2.0f)) / (2 * sigma_sq));
+        if (0 != sum) a = (a / sum) * tmp;
+      } else if (0 != sum) a = a / sum;
+      e[w] = a;
+      if (a > best) { best = a; besti = lo + w; }  // viterbi vote, src/decoder.h:1948-1962
+    }
+    if (rec_lo) { rec_lo[r] = lo; rec_vit[r] = besti; }
+  }
+  __syncthreads();
+  if (rec_align)
+    for (int w = threadIdx.x; w < win; w += blockDim.x) rec_align[(size_t)r * win + w] = (w < W) ? e[w] : 0.f;
+  // context: CreateCTKernel, deep_rnn_kernel.h:1250-1260 (sum over window positions in order)
+  float* crow = ctx + (size_t)r * Hp;
+  for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w = 0; w < W; ++w) {
+      const float a = e[w];
+      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
+      acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
+    }
+    *reinterpret_cast<float4*>(crow + j) = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Log-softmax statistics and per-row top-kk of the logits in ONE pass over HBM.
+// Replaces MatrixBiasKernel's consumer OutputdistOverflowPreventionKernel
+// (src/deep_rnn_kernel.h:352-429, three passes), the V x k device-to-host copy
+// (src/decoder.h:1413) and the host scan that keeps the k+1 best per beam
+// (src/decoder.h:401-410).  Order: value descending, vocabulary index ascending -- what the
+// strict-greater replacement of the reference keeps.  log p = (z - max) - log(sum exp).
+// grid = rows, block = 256, dynamic smem = 256*kk*8 bytes.
+struct TopkOut {
+  int32_t* idx;    // [rows][kk]
+  float* logp;     // [rows][kk]
+  float* eos_logp; // [rows]
+};
+__device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out) {
+  extern __shared__ unsigned char smraw[];
+  float* lv = reinterpret_cast<float*>(smraw);            // [kk][256] values, sorted descending per thread
+  int* li = reinterpret_cast<int*>(lv + kk * 256);        // [kk][256] indices
+  __shared__ float s_m[8], s_s[8];
+  __shared__ float s_bv[8];
+  __shared__ int s_bi[8], s_bt[8];
+  __shared__ float s_max, s_lse;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* z = logits + (size_t)r * ld;
+  for (int s = 0; s < kk; ++s) { lv[s * 256 + tid] = -INFINITY; li[s * 256 + tid] = 0x7fffffff; }
+  float m = -INFINITY, ssum = 0.f;
+  float thr = -INFINITY;  // current smallest kept value of this thread
+  auto visit = [&](float v, int i) {
+    if (v > m) { ssum = ssum * expf(m - v) + 1.0f; m = v; } else { ssum += expf(v - m); }
+    if (v > thr) {
+      int s = kk - 1;
+      while (s > 0 && lv[(s - 1) * 256 + tid] < v) {
+        lv[s * 256 + tid] = lv[(s - 1) * 256 + tid];
+        li[s * 256 + tid] = li[(s - 1) * 256 + tid];
+        --s;
+      }
+      lv[s * 256 + tid] = v; li[s * 256 + tid] = i;
+      thr = lv[(kk - 1) * 256 + tid];
+    }
+  };
+  const int V4 = V & ~3;
+  for (int i = tid * 4; i < V4; i += 256 * 4) {
+    const float4 q = *reinterpret_cast<const float4*>(z + i);
+    visit(q.x, i); visit(q.y, i + 1); visit(q.z, i + 2); visit(q.w, i + 3);
+  }
+  for (int i = V4 + tid; i < V; i += 256) visit(z[i], i);
+  // block (max, sum)
+  float wm = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+  float ws = (m == -INFINITY) ? 0.f : ssum * expf(m - wm);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+  const int warp = tid >> 5, lane = tid & 31;
+  if (lane == 0) { s_m[warp] = wm; s_s[warp] = ws; }
+  __syncthreads();
+  if (tid == 0) {
+    float bm = s_m[0];
+    for (int w = 1; w < 8; ++w) bm = fmaxf(bm, s_m[w]);
+    float bs = 0.f;
+    for (int w = 0; w < 8; ++w) bs += s_s[w] * expf(s_m[w] - bm);
+    s_max = bm; s_lse = logf(bs);
+    if (out.eos_logp) out.eos_logp[r] = (z[kEos] - bm) - s_lse;
+  }
+  __syncthreads();
+  // kk rounds of block arg-best over each thread's best remaining entry
+  int head = 0;
+  for (int round = 0; round < kk; ++round) {
+    float v = (head < kk) ? lv[head * 256 + tid] : -INFINITY;
+    int i = (head < kk) ? li[head * 256 + tid] : 0x7fffffff;
+    int t = tid;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+      const int ot = __shfl_xor_sync(0xffffffffu, t, o);
+      if (better(ov, oi, v, i)) { v = ov; i = oi; t = ot; }
+    }
+    if (lane == 0) { s_bv[warp] = v; s_bi[warp] = i; s_bt[warp] = t; }
+    __syncthreads();
+    float bv = s_bv[0]; int bi = s_bi[0], bt = s_bt[0];
+    for (int w = 1; w < 8; ++w) if (better(s_bv[w], s_bi[w], bv, bi)) { bv = s_bv[w]; bi = s_bi[w]; bt = s_bt[w]; }
+    if (tid == bt) ++head;
+    if (tid == 0) {
+      const bool valid = bi != 0x7fffffff;
+      out.idx[(size_t)r * kk + round] = valid ? bi : -1;
+      out.logp[(size_t)r * kk + round] = valid ? ((bv - s_max) - s_lse) : -INFINITY;
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Beam selection for one sentence and one step, all on the device.  Replaces
+// Decoder<T>::ExpandHypothesis (src/decoder.h:355-480) and, on a sentence's last step,
+// Decoder<T>::FinishCurrentHypotheses (src/decoder.h:502-525).
+// Candidate order = (score desc, beam asc, vocab asc), the defined order of the reference's
+// global heap.  START is skipped, EOS goes to the finished list without using a slot.
+struct BeamState {
+  int32_t* tok;        // [R] current token of each slot
+  float* score;        // [R]
+  int32_t* parent;     // [R] parent slot chosen by the last selection
+  int32_t* hist_tok;   // [Tcap][R]
+  int32_t* hist_parent;// [Tcap][R]
+  int32_t* fin_t;      // [B][fin_cap] step at which EOS was produced
+  int32_t* fin_b;      // [B][fin_cap] slot whose history the hypothesis continues
+  float* fin_score;    // [B][fin_cap]
+  int32_t* fin_n;      // [B]
+  int fin_cap;
+  int R;
+};
+struct TraceDev {
+  int32_t* cand_tok; float* cand_logp; int32_t* surv_tok; int32_t* surv_parent; float* surv_score; float* final_logp;
+  const int32_t* force_tok; const int32_t* force_parent; const float* force_score;
+  int Tm;
+};
+// grid = active sentences, block = 128, dynamic smem = k*kk*(4+4+4+4) bytes
+static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_logp,
+                                   const float* __restrict__ eos_logp, const int32_t* __restrict__ steps,
+                                   const int32_t* __restrict__ orig, int t, int k, float penalty, float diversity,
+                                   TraceDev tr) {
+  extern __shared__ unsigned char smraw[];
+  const int kk = k + 1;
+  const int ncap = k * kk;
+  float* cs = reinterpret_cast<float*>(smraw);   // candidate score
+  int* cb = reinterpret_cast<int*>(cs + ncap);   // beam
+  int* cv = cb + ncap;                           // vocab id
+  int* order = cv + ncap;                        // sorted position -> candidate
+  const int sent = blockIdx.x;
+  const int T = steps[sent];
+  const int r0 = sent * k;
+  const int osent = orig[sent];
+  if (t > T) return;
+  if (t == T) {
+    if (threadIdx.x == 0) {
+      int n = bs.fin_n[sent];
+      for (int b = 0; b < k; ++b) {
+        const float lp = eos_logp[r0 + b];
+        if (tr.final_logp) tr.final_logp[(size_t)osent * k + b] = lp;
+        if (n < bs.fin_cap) {
+          bs.fin_t[(size_t)sent * bs.fin_cap + n] = t;
+          bs.fin_b[(size_t)sent * bs.fin_cap + n] = b;
+          bs.fin_score[(size_t)sent * bs.fin_cap + n] = bs.score[r0 + b] + (lp + penalty);
+          ++n;
+        }
+      }
+      bs.fin_n[sent] = n;
+    }
+    return;
+  }
+  const int cols = (t == 0) ? 1 : k;
+  const int n = cols * kk;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const int b = c / kk, q = c - b * kk;
+    const float lp = cand_logp[(size_t)(r0 + b) * kk + q];
+    const int v = cand_idx[(size_t)(r0 + b) * kk + q];
+    const float rank_penalty = (float)(q + 1) * diversity;
+    cs[c] = (lp + bs.score[r0 + b]) - rank_penalty;
+    cb[c] = b; cv[c] = v;
+    if (tr.cand_tok) {
+      const size_t off = ((((size_t)osent * tr.Tm + t) * k + b) * kk) + q;
+      tr.cand_tok[off] = v; tr.cand_logp[off] = lp;
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float s = cs[c]; const int b = cb[c], v = cv[c];
+    int pos = 0;
+    for (int d = 0; d < n; ++d) {
+      const float s2 = cs[d];
+      if (s2 > s || (s2 == s && (cb[d] < b || (cb[d] == b && cv[d] < v)))) ++pos;
+    }
+    order[pos] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ns = 0;
+    int nf = bs.fin_n[sent];
+    int32_t* ht = bs.hist_tok + (size_t)t * bs.R;
+    int32_t* hp = bs.hist_parent + (size_t)t * bs.R;
+    for (int p = 0; p < n && ns < k; ++p) {
+      const int c = order[p];
+      const int v = cv[c];
+      if (v == kStart || v < 0) continue;
+      if (v == kEos) {
+        if (nf < bs.fin_cap) {
+          bs.fin_t[(size_t)sent * bs.fin_cap + nf] = t;
+          bs.fin_b[(size_t)sent * bs.fin_cap + nf] = cb[c];
+          bs.fin_score[(size_t)sent * bs.fin_cap + nf] = cs[c] + penalty;
+          ++nf;
+        }
+        continue;
+      }
+      bs.tok[r0 + ns] = v; bs.parent[r0 + ns] = cb[c]; bs.score[r0 + ns] = cs[c] + penalty;
+      ++ns;
+    }
+    for (; ns < k; ++ns) { bs.tok[r0 + ns] = kUnk; bs.parent[r0 + ns] = 0; bs.score[r0 + ns] = kDeadScore; }
+    bs.fin_n[sent] = nf;
+    for (int b = 0; b < k; ++b) {
+      if (tr.surv_tok) {
+        const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
+        tr.surv_tok[off] = bs.tok[r0 + b]; tr.surv_parent[off] = bs.parent[r0 + b]; tr.surv_score[off] = bs.score[r0 + b];
+      }
+      if (tr.force_tok) {
+        const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
+        bs.tok[r0 + b] = tr.force_tok[off]; bs.parent[r0 + b] = tr.force_parent[off]; bs.score[r0 + b] = tr.force_score[off];
+      }
+      ht[r0 + b] = bs.tok[r0 + b];
+      hp[r0 + b] = bs.parent[r0 + b];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Final scoring and n-best extraction for one sentence.  Replaces
+// Decoder<T>::ObtainOneBestHypothesis (src/decoder.h:703-859) up to the numeric result:
+// length normalisation (:708-713), coverage penalty (:716-759), minimum-ratio filter
+// (:762-765), n-best with strictly-greater replacement (:766-773), then the hypothesis is
+// rebuilt from the back-pointers.
+struct FinalizeArgs {
+  BeamState bs;
+  const int32_t* steps;     // [B]
+  const int32_t* src_len;   // [B]
+  const int32_t* orig;      // [B] caller's sentence index
+  const float* rec_align;   // [Tcap][R][win] or null
+  const int32_t* rec_lo;    // [Tcap][R]
+  const int32_t* rec_vit;   // [Tcap][R]
+  float* fin_final;         // [B][fin_cap] scratch: final score, -inf if filtered
+  int win;
+  int k;
+  int nbest;
+  int max_len;
+  int max_src;
+  float lp_alpha, cp_beta, min_ratio;
+  int32_t* out_tok;   // [n][nbest][max_len]
+  int32_t* out_len;   // [n][nbest]
+  float* out_score;   // [n][nbest]
+  int32_t* out_vit;   // [n][nbest][max_len] or null
+  float* out_align;   // [n][nbest][max_len][max_src] or null
+};
+// grid = sentences, block = 128, dynamic smem = 4 warps * (max_src floats + max_len ints)
+static __global__ void __launch_bounds__(128) finalize_kernel(FinalizeArgs a) {
+  extern __shared__ unsigned char smraw[];
+  const int sent = blockIdx.x;
+  const int S = a.src_len[sent];
+  const int k = a.k, R = a.bs.R;
+  const int nf = a.bs.fin_n[sent];
+  const int r0 = sent * k;
+  const int32_t* ft = a.bs.fin_t + (size_t)sent * a.bs.fin_cap;
+  const int32_t* fb = a.bs.fin_b + (size_t)sent * a.bs.fin_cap;
+  const float* fs = a.bs.fin_score + (size_t)sent * a.bs.fin_cap;
+  float* ff = a.fin_final + (size_t)sent * a.bs.fin_cap;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* cov = reinterpret_cast<float*>(smraw) + warp * a.max_src;
+  int* path = reinterpret_cast<int*>(reinterpret_cast<float*>(smraw) + 4 * a.max_src) + warp * a.max_len;
+  const bool tracked = a.rec_align != nullptr;
+
+  if (!tracked || a.cp_beta == 0.f) {
+    for (int q = threadIdx.x; q < nf; q += blockDim.x) {
+      const int n = ft[q] + 2;
+      float sc = fs[q];
+      if (0 != a.lp_alpha) {
+        const float lp = powf((float)(5 + n), a.lp_alpha) / powf((float)(5 + 1), a.lp_alpha);
+        sc /= lp;
+      }
+      if (0 != a.cp_beta) {
+        // alignments are all zero when they are not tracked: every position becomes the
+        // uniform row (0 + 0.01) / sum; same loops as the reference, in fp32
+        float sum = 0.f;
+        const float one = (float)(0.0f + 0.01);
+        for (int s = 0; s < S; ++s) sum += one;
+        const float u = one / sum;
+        float c1 = 0.f;
+        for (int j = 1; j < n - 1; ++j) c1 += u;
+        float cp = 0.f;
+        const float lg = logf(fminf(c1, 1.0f));
+        for (int s = 0; s < S; ++s) cp += lg;
+        cp *= a.cp_beta;
+        if (cp < -20) cp = -20;
+        sc += cp;
+      }
+      const float ratio = ((float)n) / S;
+      ff[q] = (ratio > a.min_ratio) ? sc : -INFINITY;
+    }
+  } else {
+    // tracked alignments: one warp per hypothesis, lanes over source positions
+    for (int q = warp; q < nf; q += 4) {
+      const int t = ft[q];
+      const int n = t + 2;
+      float sc = fs[q];
+      if (0 != a.lp_alpha) {
+        const float lp = powf((float)(5 + n), a.lp_alpha) / powf((float)(5 + 1), a.lp_alpha);
+        sc /= lp;
+      }
+      // path[p] = slot that ran the forward producing position p (p = 1 .. t+1)
+      if (lane == 0) {
+        int slot = fb[q];
+        path[t + 1] = slot;
+        for (int tt = t - 1; tt >= 0; --tt) {
+          const int par = a.bs.hist_parent[(size_t)tt * R + r0 + slot];
+          path[tt + 1] = par;
+          slot = par;
+        }
+      }
+      __syncwarp();
+      for (int s = lane; s < S; s += 32) cov[s] = 0.f;
+      for (int p = 2; p <= n - 1; ++p) {
+        const int step = p - 1;
+        const size_t row = (size_t)step * R + r0 + path[p];
+        const int lo = a.rec_lo[row];
+        float part = 0.f;
+        for (int s = lane; s < S; s += 32) {
+          const int w = s - lo;
+          const float v = ((w >= 0 && w < a.win) ? a.rec_align[row * a.win + w] : 0.f) + 0.01f;
+          part += v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        for (int s = lane; s < S; s += 32) {
+          const int w = s - lo;
+          const float v = ((w >= 0 && w < a.win) ? a.rec_align[row * a.win + w] : 0.f) + 0.01f;
+          cov[s] += v / part;
+        }
+      }
+      __syncwarp();
+      float cp = 0.f;
+      for (int s = lane; s < S; s += 32) cp += logf(fminf(cov[s], 1.0f));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cp += __shfl_xor_sync(0xffffffffu, cp, o);
+      cp *= a.cp_beta;
+      if (cp < -20) cp = -20;
+      sc += cp;
+      const float ratio = ((float)n) / S;
+      if (lane == 0) ff[q] = (ratio > a.min_ratio) ? sc : -INFINITY;
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  // n-best in creation order with strictly-greater replacement, then descending
+  __shared__ int s_best[32];
+  __shared__ int s_nb;
+  if (threadIdx.x == 0) {
+    int nb = 0;
+    for (int q = 0; q < nf; ++q) {
+      const float sc = ff[q];
+      if (sc == -INFINITY) continue;
+      if (nb < a.nbest) s_best[nb++] = q;
+      else {
+        int worst = 0;
+        for (int z = 1; z < nb; ++z)
+          if (ff[s_best[z]] < ff[s_best[worst]] || (ff[s_best[z]] == ff[s_best[worst]] && s_best[z] > s_best[worst])) worst = z;
+        if (ff[s_best[worst]] < sc) s_best[worst] = q;
+      }
+    }
+    for (int i = 1; i < nb; ++i) {  // insertion sort: score desc, creation order asc
+      const int q = s_best[i];
+      int j = i - 1;
+      while (j >= 0 && (ff[s_best[j]] < ff[q] || (ff[s_best[j]] == ff[q] && s_best[j] > q))) { s_best[j + 1] = s_best[j]; --j; }
+      s_best[j + 1] = q;
+    }
+    s_nb = nb;
+  }
+  __syncthreads();
+  const int osent = a.orig[sent];
+  for (int q = warp; q < a.nbest; q += 4) {
+    const size_t ob = (size_t)osent * a.nbest + q;
+    if (q >= s_nb) {
+      if (lane == 0) { a.out_len[ob] = 0; a.out_score[ob] = 0.f; }
+      continue;
+    }
+    const int h = s_best[q];
+    const int t = ft[h];
+    const int n = t + 2;
+    if (lane == 0) {
+      a.out_len[ob] = n;
+      a.out_score[ob] = ff[h];
+      int32_t* ot = a.out_tok + ob * a.max_len;
+      int32_t* ov = a.out_vit ? a.out_vit + ob * a.max_len : nullptr;
+      ot[0] = kStart; ot[t + 1] = kEos;
+      int slot = fb[h];
+      path[t + 1] = slot;
+      if (ov) { ov[0] = -20; ov[t + 1] = a.rec_vit ? a.rec_vit[(size_t)t * R + r0 + slot] : -1; }
+      for (int tt = t - 1; tt >= 0; --tt) {
+        ot[tt + 1] = a.bs.hist_tok[(size_t)tt * R + r0 + slot];
+        const int par = a.bs.hist_parent[(size_t)tt * R + r0 + slot];
+        if (ov) ov[tt + 1] = a.rec_vit ? a.rec_vit[(size_t)tt * R + r0 + par] : -1;
+        path[tt + 1] = par;
+        slot = par;
+      }
+    }
+    __syncwarp();
+    if (a.out_align && tracked) {
+      float* oa = a.out_align + ob * a.max_len * a.max_src;
+      for (int p = 0; p < n; ++p) {
+        float part = 0.f;
+        const bool norm = (a.cp_beta != 0.f) && p >= 2;
+        size_t row = 0; int lo = 0;
+        if (p >= 1) { row = (size_t)(p - 1) * R + r0 + path[p]; lo = a.rec_lo[row]; }
+        if (norm) {
+          for (int s = lane; s < S; s += 32) {
+            const int w = s - lo;
+            part += ((w >= 0 && w < a.win) ? a.rec_align[row * a.win + w] : 0.f) + 0.01f;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        }
+        for (int s = lane; s < a.max_src; s += 32) {
+          float v = 0.f;
+          if (p >= 1 && s < S) {
+            const int w = s - lo;
+            v = (w >= 0 && w < a.win) ? a.rec_align[row * a.win + w] : 0.f;
+            if (norm) v = (v + 0.01f) / part;
+          }
+          oa[(size_t)p * a.max_src + s] = v;
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace linmt

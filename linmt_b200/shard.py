@@ -1,0 +1,45 @@
+"""Sentence sharding across the GPUs of one box.
+
+Sentences are independent (src/decoder.h:1780-1840 keeps no state between calls), so the
+only multi-GPU structure is: split the work, decode locally on a replica, gather the
+hypotheses once at the end.  No collective runs inside the step loop.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+
+def batches_by_length(sents, batch: int) -> List[List[int]]:
+    """Sentence indices sorted by step count (longest first) and cut into batches, so the
+    sentences of a batch need similar numbers of steps."""
+    order = sorted(range(sents.n), key=lambda i: (-int(sents.steps[i]), i))
+    return [order[i:i + batch] for i in range(0, len(order), batch)]
+
+
+def partition(sents, world: int, batch: int) -> List[List[int]]:
+    """Deals length-bucketed batches to ranks, heaviest first, always to the least loaded rank
+    (load = sum of decoder forwards T_i + 1)."""
+    bl = batches_by_length(sents, batch)
+    cost = [sum(int(sents.steps[i]) + 1 for i in b) * 0 + (max(int(sents.steps[i]) for i in b) + 1) * len(b) for b in bl]
+    load = [0] * world
+    parts: List[List[int]] = [[] for _ in range(world)]
+    for bi in sorted(range(len(bl)), key=lambda j: -cost[j]):
+        r = min(range(world), key=lambda x: (load[x], x))
+        parts[r].extend(bl[bi])
+        load[r] += cost[bi]
+    return parts
+
+
+def gather_results(local: Dict[int, object], dst: int = 0):
+    """One gather of the per-sentence results to rank ``dst`` (the only collective of a job)."""
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return dict(local)
+    out = [None] * dist.get_world_size() if dist.get_rank() == dst else None
+    dist.gather_object(local, out, dst=dst)
+    if dist.get_rank() != dst:
+        return None
+    merged = {}
+    for part in out:
+        merged.update(part)
+    return merged

@@ -1,0 +1,41 @@
+"""Generates the golden decode fixtures from the CPU checker (the reference itself cannot be
+built or run, and ships neither a model nor expected outputs).  Run from the repository root:
+
+    python tests/golden/make_golden.py
+
+Writes tests/golden/c1_greedy.npz, c1_beam4.npz and tiny_global.npz: inputs are regenerated
+from seeds by linmt_b200.synth, the files hold the expected outputs."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from linmt_b200 import synth  # noqa: E402
+from oracle import oracle_py  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+CASES = {
+    "c1_greedy": dict(beam=1, nbest=1, cp_beta=0.0, print_info=0, attention="local_p_general"),
+    "c1_beam4": dict(beam=4, nbest=3, cp_beta=0.2, print_info=1, attention="local_p_general"),
+    "tiny_global": dict(beam=3, nbest=2, cp_beta=0.0, print_info=0, attention="global_general"),
+}
+
+
+def main():
+    c = synth.configs()["C1"]
+    blob = c.blobs()[0]
+    sents = c.sentences()
+    for name, kw in CASES.items():
+        o = oracle_py.decode(c.desc, [blob], sents, trace=True, **kw)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), tok=o["tok"], len=o["len"], score=o["score"],
+                            vit=o["vit"], surv_tok=o["surv_tok"], surv_parent=o["surv_parent"],
+                            surv_score=o["surv_score"], cand_tok=o["cand_tok"], cand_logp=o["cand_logp"],
+                            final_logp=o["final_logp"])
+        print(name, o["len"][:, 0].tolist())
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,172 @@
+"""GPU parity tests of the whole decode against the CPU checker and the golden fixtures.
+
+Tolerances: fp32 weights -> per-step log-probabilities within 1e-4 relative; beam outputs are
+compared token by token.  Two searches that sum in different orders can part ways where
+fp32 cumulative scores tie, so the per-step check runs with the engine's beam forced to the
+checker's survivors (every step comparable), and the free-running check counts sentences."""
+import os
+
+import numpy as np
+import pytest
+
+from linmt_b200 import synth
+from parity import RTOL_FP32, compare_forced, hyps, token_identity
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def c1():
+    c = synth.configs()["C1"]
+    return c, c.blobs()[0], c.sentences()
+
+
+def _decoder(c, blob, **kw):
+    from linmt_b200 import decoder
+    args = dict(beam=c.beam, max_batch=8, max_src_len=32, max_steps=64)
+    args.update(kw)
+    return decoder.Decoder(c.desc, [blob], **args)
+
+
+@pytest.mark.parametrize("case,kw", [
+    ("c1_greedy", dict(beam=1, nbest=1, cp_beta=0.0, print_info=0)),
+    ("c1_beam4", dict(beam=4, nbest=3, cp_beta=0.2, print_info=1)),
+    ("tiny_global", dict(beam=3, nbest=2, cp_beta=0.0, print_info=0, attention="global_general")),
+])
+def test_c1_against_golden_and_checker(oracle, cuda_lib, c1, case, kw):
+    c, blob, sents = c1
+    g = np.load(os.path.join(GOLD, case + ".npz"))
+    dec = _decoder(c, blob, **kw)
+    forced = dec.decode(sents, trace=True, force={k: g[k] for k in ("surv_tok", "surv_parent", "surv_score")})
+    worst, bad = compare_forced(forced, {k: g[k] for k in ("cand_tok", "cand_logp")}, sents.steps)
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    np.testing.assert_allclose(forced["final_logp"], g["final_logp"], rtol=RTOL_FP32)
+    free = dec.decode(sents, trace=True)
+    same = token_identity(free, {"tok": g["tok"], "len": g["len"]}, sents.n)
+    assert same >= 0.75, same
+    for i in range(sents.n):
+        if hyps(free, i) == list(g["tok"][i, 0, :g["len"][i, 0]]):
+            np.testing.assert_allclose(free["score"][i, 0], g["score"][i, 0], rtol=RTOL_FP32)
+            if kw.get("print_info"):
+                n = int(g["len"][i, 0])
+                assert (free["vit"][i, 0, :n] == g["vit"][i, 0, :n]).all()
+    dec.close()
+
+
+def test_global_dot_and_diversity(oracle, cuda_lib, c1):
+    c, blob, sents = c1
+    kw = dict(beam=3, nbest=2, attention="global_dot", diversity=0.1, penalty=0.05, lp_alpha=0.0, cp_beta=0.3)
+    o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
+    dec = _decoder(c, blob, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    worst, bad = compare_forced(forced, o, sents.steps)
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    dec.close()
+
+
+def test_alignments_and_coverage(oracle, cuda_lib, c1):
+    c, blob, sents = c1
+    kw = dict(beam=4, nbest=2, cp_beta=0.2, print_info=1)
+    o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
+    dec = _decoder(c, blob, **kw)
+    e = dec.decode(sents, trace=True, want_align=True)
+    for i in range(sents.n):
+        n = int(o["len"][i, 0])
+        if hyps(e, i) != hyps(o, i):
+            continue
+        S = int(sents.lengths()[i])
+        np.testing.assert_allclose(e["align"][i, 0, :n, :S], o["align"][i, 0, :n, :S], rtol=2e-4, atol=1e-6)
+        assert (e["vit"][i, 0, :n] == o["vit"][i, 0, :n]).all()
+    dec.close()
+
+
+def test_ragged_batches_and_chunking(oracle, cuda_lib):
+    """More sentences than one device batch, very different lengths, a one-word sentence and a
+    zero-step sentence."""
+    c = synth.configs()["C1"]
+    blob = c.blobs()[0]
+    rng = np.random.default_rng(5)
+    lens = [1, 20, 3, 17, 2, 9, 11, 1, 5, 13, 7]
+    ids = synth.zipf_ids(rng, sum(lens), 1, c.desc.Vs, 1.1)
+    off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    steps = np.array([0, 40, 6, 5, 4, 18, 22, 2, 10, 26, 1], np.int32)
+    sents = synth.Sentences(ids, off, steps)
+    kw = dict(beam=3, nbest=2, min_ratio=0.0)
+    o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
+    dec = _decoder(c, blob, max_batch=4, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    worst, bad = compare_forced(forced, o, sents.steps)
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    free = dec.decode(sents)
+    assert token_identity(free, o, sents.n) >= 0.7
+    assert (free["len"][:, 0] == o["len"][:, 0]).all()
+    dec.close()
+
+
+def test_limits_are_errors_not_faults(cuda_lib, c1):
+    from linmt_b200 import decoder
+    c, blob, sents = c1
+    dec = _decoder(c, blob, max_src_len=8)
+    with pytest.raises(decoder.LinmtError, match="max_src_len"):
+        dec.decode(sents)
+    dec.close()
+    dec = _decoder(c, blob, max_steps=4)
+    with pytest.raises(decoder.LinmtError, match="max_steps"):
+        dec.decode(sents)
+    dec.close()
+    with pytest.raises(decoder.LinmtError):
+        decoder.Decoder(c.desc, [blob[:-1]], beam=2)
+
+
+def test_c2_shape_subset(oracle, cuda_lib):
+    """The 4 x 1000, 30k-vocabulary, beam-12 model on 6 sentences of the reference decode
+    configuration, against the checker."""
+    c = synth.configs()["C2"]
+    blob = c.blobs()[0]
+    sents = c.sentences().subset(range(6))
+    kw = dict(beam=12, nbest=1, lp_alpha=0.65, cp_beta=0.0)
+    o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
+    from linmt_b200 import decoder
+    dec = decoder.Decoder(c.desc, [blob], max_batch=8, max_src_len=64, max_steps=100, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    worst, bad = compare_forced(forced, o, sents.steps)
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    free = dec.decode(sents)
+    assert token_identity(free, o, sents.n) >= 0.66
+    dec.close()
+
+
+def test_sentence_api_matches_checker(oracle, cuda_lib, c1, tmp_path):
+    """python_decoder_init / python_decoder_do_job on a model file in the reference's text
+    format, compared with the checker's hypothesis formatted the reference's way."""
+    from linmt_b200 import decoder, modelfile
+    c, blob, _ = c1
+    d = synth.ModelDesc(2, 32, 60, 50, 1)
+    blob = synth.make_blob(d, 4)
+    mp, cp = tmp_path / "model.nmt", tmp_path / "dec.config"
+    modelfile.write_model(str(mp), d, blob)
+    modelfile.write_config(str(cp), [str(mp)], beam_size=3, nbest=1, longest_sent=30, lp_alpha=0.65, cp_beta=0.2,
+                           print_decoding_info=1)
+    src = modelfile.default_vocab(d.Vs, "src")
+    tgt = modelfile.default_vocab(d.V, "tgt")
+    words = [src[i] for i in (5, 9, 1, 33, 7, 7, 12)] + ["never-seen-word"]
+    ids = np.array([5, 9, 1, 33, 7, 7, 12, 0], np.int32)
+    sents = synth.Sentences(ids, np.array([0, len(ids)], np.int32), np.array([min(int(1.5 * len(ids)), 32)], np.int32))
+    o = oracle.decode(d, [blob], sents, beam=3, nbest=1, cp_beta=0.2, print_info=1, trace=True)
+    ds = decoder.DecoderSentence()
+    ds.Init(str(cp))
+    got = ds.Process(" ".join(words) + " |||| ignored tail")
+    n = int(o["len"][0, 0])
+    exp_words = " ".join(tgt[t] for t in o["tok"][0, 0, 1:n - 1])
+    fields = got.split(" |||| ")
+    assert fields[0] == exp_words
+    assert abs(float(fields[1]) - float(o["score"][0, 0])) <= 2e-4 * abs(float(o["score"][0, 0]))
+    assert [int(x) for x in fields[2].split()] == o["vit"][0, 0, 2:n].tolist()
+    ds.close()
+    # the exported pair, binary form of the same model file
+    modelfile.write_model(str(mp), d, blob, binary=True)
+    cuda_lib.python_decoder_init(str(cp).encode())
+    got2 = cuda_lib.python_decoder_do_job((" ".join(words)).encode()).decode()
+    assert got2 == got
+    assert cuda_lib.python_decoder_do_job(b"") == b""
