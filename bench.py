@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Benchmark of the beam-search decoding path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one full decode (encoder, step loop, finalisation) of one batch of synthetic
+sentences of the reference decode configuration: 4-layer 1000-unit LSTM encoder/decoder,
+30k/30k vocabularies, local-p 'general' attention with feed-input, beam 12, 64 sentences of
+10..50 words, T = floor(1.5 S) + 10 expansions, fp32 weights uniform[-0.08, 0.08] (seed 1).
+With N > 1 every rank decodes its own batch of the same distribution on its own replica
+(weak scaling, no collective in the data path).  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from linmt_b200 import synth  # noqa: E402
+
+METRIC = "decoded target tokens/sec, beam 12, 4x1000 LSTM"
+UNIT = "tokens/s"
+FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
+# DRAM bytes of one vocabulary-GEMM launch from an ncu capture (see profiles/); None = not captured
+VOCAB_GEMM_TRAFFIC_BYTES = None
+
+
+def workload(rank: int):
+    c = synth.configs()["C2"]
+    sents = synth.make_sentences(c.n_sent, c.len_lo, c.len_hi, c.desc.Vs, c.zipf_s, c.seeds[0] + 7919 * rank, c.step_rule)
+    return c, sents
+
+
+def clocks_start():
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+    f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+    try:
+        p = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                             stdout=f, stderr=subprocess.DEVNULL)
+    except OSError:
+        return None, f.name
+    return p, f.name
+
+
+def clocks_stop(p, path, device_index: int):
+    if p is not None:
+        p.terminate()
+        try:
+            p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            p.kill()
+    sm, mx, reasons = [], [], set()
+    try:
+        for line in open(path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) != device_index:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(path)
+    except OSError:
+        pass
+    if not sm:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+    return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+    except Exception:
+        return FALLBACK_TFLOPS, "fallback"
+
+
+def emitted_tokens(out_len: np.ndarray) -> int:
+    return int(np.maximum(out_len[:, 0] - 2, 0).sum())
+
+
+def cpu_leg(c, blob, sents, n_sample: int, threads: int = 0, repeat: int = 1):
+    """Times the CPU checker (a port of the reference's math; the reference has no CPU path
+    of its own) on the first n_sample sentences of the batch."""
+    from oracle import oracle_py
+    sub = sents.subset(range(min(n_sample, sents.n)))
+    best = None
+    for _ in range(repeat):
+        t0 = time.perf_counter()
+        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta, threads=threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    toks = emitted_tokens(o["len"])
+    return toks / best, best, sub.n, oracle_py.lib().linmt_oracle_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    c, sents = workload(0)
+    blob = c.blobs()[0]
+    n_sample = 8
+    times = []
+    toks = 0
+    from oracle import oracle_py
+    sub = sents.subset(range(n_sample))
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta)
+        dt = time.perf_counter() - t0
+        if i >= args.warmup:
+            times.append(dt)
+            toks = emitted_tokens(o["len"])
+        if sum(times) > 150:
+            break
+    steps_done = len(times)
+    ms = 1e3 * sum(times) / steps_done
+    value = toks / (ms / 1e3)
+    cores = oracle_py.lib().linmt_oracle_threads()
+    sample = f"first {n_sample} of the 64 sentences of the batch per step, rows = {n_sample}*12, all host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps_done,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": config_block(c, sents, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference has no CPU forward path and cannot be built here (Boost, GPU-only math); this arm "
+                "times the CPU port of its math (oracle/) on the host cores",
+    }
+    print(json.dumps(line))
+
+
+def config_block(c, sents, n_gpus):
+    return {"workload": "C2: 4x1000 LSTM enc/dec, 30k/30k vocab, local-p general attention + feed-input, beam 12, "
+                        "64 sentences/batch, S in [10,50], T=floor(1.5S)+10, lp_alpha 0.65, fp32 weights",
+            "sentences_per_step_per_gpu": int(sents.n), "beam": c.beam,
+            "decoder_positions_per_step_per_gpu": int((sents.steps + 1).sum()),
+            "l2": "inputs larger than L2 (>= 0.65 GB of weights streamed every decoder step)",
+            "parallelism": f"replicas x{n_gpus}, sentence-sharded, no data-path collective"}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from linmt_b200 import decoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    c, sents = workload(rank)
+    blob = c.blobs()[0]
+    max_src = int(sents.lengths().max())
+    Tm = int(sents.steps.max())
+    max_len = Tm + 2
+    dec = decoder.Decoder(c.desc, [blob], beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                          gemm_path=args.gemm_path, max_batch=sents.n, max_src_len=max(max_src, 64),
+                          max_steps=max(Tm, 100), device=local)
+    dev = torch.device("cuda", local)
+    d_ids = torch.from_numpy(sents.ids.astype(np.int32)).to(dev)
+    d_tok = torch.zeros((sents.n, 1, max_len), dtype=torch.int32, device=dev)
+    d_len = torch.zeros((sents.n, 1), dtype=torch.int32, device=dev)
+    d_score = torch.zeros((sents.n, 1), dtype=torch.float32, device=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device():
+        dec.decode_device(d_ids.data_ptr(), sents.off, sents.steps, max_len, d_tok.data_ptr(), d_len.data_ptr(), d_score.data_ptr())
+        return dec.stats()
+
+    # ---- device-resident leg: `value` ----
+    for _ in range(args.warmup):
+        step_device()
+    dec.set_kernel_timing(True)
+    s0 = dec.stats()
+    barrier()
+    clk_p, clk_path = clocks_start() if rank == 0 else (None, None)
+    dev_ms, gemm_ms, gemm_n = 0.0, 0.0, 0
+    w0 = time.perf_counter()
+    for _ in range(args.steps):
+        s = step_device()
+        dev_ms += s["last_decode_ms"]; gemm_ms += s["last_gemm_ms"]; gemm_n += s["last_gemm_launches"]
+    barrier()
+    wall_ms = 1e3 * (time.perf_counter() - w0)
+    clocks = clocks_stop(clk_p, clk_path, local) if rank == 0 else None
+    s1 = dec.stats()
+    dec.set_kernel_timing(False)
+    launches = s1["kernel_launches"] - s0["kernel_launches"]
+    toks = emitted_tokens(d_len.cpu().numpy())
+    row_steps = s1["decoder_row_steps"] - s0["decoder_row_steps"]
+
+    # ---- end-to-end leg through the public host API: pinned host buffers, copies inside ----
+    h_ids = torch.from_numpy(sents.ids.astype(np.int32)).pin_memory()
+    host_sents = synth.Sentences(h_ids.numpy(), sents.off, sents.steps)
+    for _ in range(min(args.warmup, 2)):
+        out = dec.decode(host_sents)
+    barrier()
+    e0 = time.perf_counter()
+    e_dev_ms = 0.0
+    for _ in range(args.steps):
+        out = dec.decode(host_sents)
+        e_dev_ms += dec.stats()["last_decode_ms"]
+    barrier()
+    e2e_wall_ms = 1e3 * (time.perf_counter() - e0)
+    e_toks = emitted_tokens(out["len"])
+    h2d = int(sents.ids.nbytes + 4 * 4 * sents.n)
+    d2h = int(out["tok"].nbytes + out["len"].nbytes + out["score"].nbytes + out["vit"].nbytes)
+
+    # ---- reduce over ranks: max time, summed tokens ----
+    vals = torch.tensor([dev_ms, wall_ms, e2e_wall_ms, gemm_ms], dtype=torch.float64, device=dev)
+    sums = torch.tensor([toks, e_toks, launches, row_steps, gemm_n], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    dev_ms, wall_ms, e2e_wall_ms, gemm_ms_max = vals.tolist()
+    toks_all, e_toks_all, launches_all, row_steps_all, gemm_n_all = sums.tolist()
+
+    if rank == 0:
+        ms_per_step = dev_ms / args.steps
+        value = toks_all / (dev_ms / 1e3)
+        e2e_value = e_toks_all / (e2e_wall_ms / 1e3)
+        # roofline of the dominant kernel (the vocabulary GEMM): algorithmic FLOPs = 2 * rows * H * V
+        H, V = c.desc.H, c.desc.V
+        flops_local = 2.0 * (s1["decoder_row_steps"] - s0["decoder_row_steps"]) * H * V
+        achieved = flops_local / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
+        peak, peak_src = peaks()
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            v, secs, ns, cores = cpu_leg(c, blob, sents, 16)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                   "sample": f"first {ns} of the {sents.n} sentences, batched (rows = {ns}*12), {secs:.1f} s of CPU work"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config_block(c, sents, world),
+            "positions_per_s": row_steps_all / c.beam / (dev_ms / 1e3),
+            "wall_ms_per_step": wall_ms / args.steps,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_wall_ms / args.steps},
+            "gpu_launches": int(launches_all),
+            "roofline": {"bound": "tensor", "kernel": "vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": (achieved / peak) if achieved else None, "traffic": VOCAB_GEMM_TRAFFIC_BYTES,
+                         "peak_source": peak_src, "launches": int(gemm_n),
+                         "avg_launch_ms": gemm_ms / max(gemm_n, 1)},
+            "cpu_baseline": cpu, "clocks": clocks, "gemm_path": args.gemm_path,
+        }
+        print(json.dumps(line))
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

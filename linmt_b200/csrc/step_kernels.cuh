@@ -93,7 +93,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   ctx  [rows][Hp]
 //   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
 //   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
-// grid = rows, block = 128, dynamic smem = (2*win + 8) floats
+// grid = rows, block = 128, dynamic smem = (win + 8) floats
 static __global__ void __launch_bounds__(128) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
@@ -339,6 +339,7 @@ static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, c
     const float rank_penalty = (float)(q + 1) * diversity;
     cs[c] = (lp + bs.score[r0 + b]) - rank_penalty;
     cb[c] = b; cv[c] = v;
+    order[c] = c;  // overwritten by the ranking below; keeps every entry valid even for NaN scores
     if (tr.cand_tok) {
       const size_t off = ((((size_t)osent * tr.Tm + t) * k + b) * kk) + q;
       tr.cand_tok[off] = v; tr.cand_logp[off] = lp;
