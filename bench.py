@@ -241,8 +241,8 @@ def run_ours(args):
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
-        value = toks_all / (dev_ms / 1e3)
-        e2e_value = e_toks_all / (e2e_wall_ms / 1e3)
+        value = toks_all * args.steps / (dev_ms / 1e3)
+        e2e_value = e_toks_all * args.steps / (e2e_wall_ms / 1e3)
         # roofline of the dominant kernel (the vocabulary GEMM): algorithmic FLOPs = 2 * rows * H * V
         H, V = c.desc.H, c.desc.V
         flops_local = 2.0 * (s1["decoder_row_steps"] - s0["decoder_row_steps"]) * H * V
@@ -281,7 +281,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor"])
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor", "tensor2"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -40,7 +40,10 @@ enum { LINMT_OK = 0, LINMT_EINVAL = 1, LINMT_ECUDA = 2, LINMT_EIO = 3, LINMT_ENO
 enum { LINMT_ATT_LOCAL_P_GENERAL = 0, LINMT_ATT_GLOBAL_GENERAL = 1, LINMT_ATT_GLOBAL_DOT = 2 };
 enum { LINMT_ENS_PROB_MEAN = 0, LINMT_ENS_LOGPROB_MEAN = 1 };
 enum { LINMT_PREC_FP32 = 0, LINMT_PREC_BF16 = 1 };
-enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2 };
+/* GEMM kernel family.  SIMT = fp32 CUDA-core kernels (exact fp32 arithmetic).  TENSOR = tcgen05
+ * tensor-core kernels; with fp32 precision every operand is split into three bf16 planes
+ * (fp32-class accuracy), TENSOR2 uses two planes (error ~2^-17 per product, faster). */
+enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3 };
 
 /* Model dimensions: first five of the nine integers on line 1 of a model file
  * (src/decoder.h:1202-1210). */

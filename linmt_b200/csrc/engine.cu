@@ -119,11 +119,16 @@ int Engine::pack_model(const float* blob, DevModel& m) {
     if (e != cudaSuccess) return fail(LINMT_ECUDA, std::string("weight upload: ") + cudaGetErrorString(e));
     return LINMT_OK;
   };
-  auto pack_emb = [&](const float* emb, int vocab, float** dst) -> int {
+  // a dense operand goes to the device either as fp32 (CUDA-core path) or as bf16 planes
+  auto store = [&](float** dst, tc::Planes* planes, size_t rows, int ld) -> int {
+    if (use_tc_) return to_planes(host, rows, ld, *planes);
+    return upload(dst, host.size());
+  };
+  auto pack_emb = [&](const float* emb, int vocab, float** dst, tc::Planes* planes) -> int {
     host.assign((size_t)vocab * Hp, 0.f);
 #pragma omp parallel for schedule(static)
     for (int v = 0; v < vocab; ++v) std::memcpy(&host[(size_t)v * Hp], emb + (size_t)v * H, sizeof(float) * H);
-    return upload(dst, host.size());
+    return store(dst, planes, vocab, Hp);
   };
   auto pack_bias4 = [&](const BlobView::Lstm& w, float** dst) -> int {
     host.assign((size_t)4 * Hp, 0.f);
@@ -132,24 +137,25 @@ int Engine::pack_model(const float* blob, DevModel& m) {
       for (int g = 0; g < 4; ++g) host[(size_t)4 * j + g] = bs[g][j];
     return upload(dst, host.size());
   };
-  auto pack_lstm = [&](const BlobView::Lstm& w, bool feed, float** wdst, float** bdst, int* ldw) -> int {
+  auto pack_lstm = [&](const BlobView::Lstm& w, bool feed, float** wdst, tc::Planes* planes, float** bdst, int* ldw) -> int {
     const int nseg = feed ? 3 : 2;
     const float* mats[12] = {w.Mi, w.Mf, w.Mc, w.Mo, w.Whi, w.Whf, w.Whc, w.Who, w.Qi, w.Qf, w.Qc, w.Qo};
     host.resize((size_t)4 * Hp * nseg * Hp);
     pack_gate_weights(mats, nseg, H, Hp, host.data());
     *ldw = nseg * Hp;
-    int rc = upload(wdst, host.size());
+    int rc = store(wdst, planes, (size_t)4 * Hp, nseg * Hp);
     if (rc) return rc;
     return pack_bias4(w, bdst);
   };
   int rc;
-  if ((rc = pack_emb(bv.src[0].emb, desc.vocab_src, &m.emb_src))) return rc;
-  if ((rc = pack_emb(bv.tgt[0].emb, desc.vocab_tgt, &m.emb_tgt))) return rc;
+  if ((rc = pack_emb(bv.src[0].emb, desc.vocab_src, &m.emb_src, &m.p_emb_src))) return rc;
+  if ((rc = pack_emb(bv.tgt[0].emb, desc.vocab_tgt, &m.emb_tgt, &m.p_emb_tgt))) return rc;
   m.enc_w.resize(L); m.enc_b.resize(L); m.dec_w.resize(L); m.dec_b.resize(L); m.dec_ldw.resize(L);
+  m.p_enc_w.resize(L); m.p_dec_w.resize(L);
   for (int l = 0; l < L; ++l) {
     int ld;
-    if ((rc = pack_lstm(bv.src[l], false, &m.enc_w[l], &m.enc_b[l], &ld))) return rc;
-    if ((rc = pack_lstm(bv.tgt[l], l == 0 && desc.feed_input, &m.dec_w[l], &m.dec_b[l], &m.dec_ldw[l]))) return rc;
+    if ((rc = pack_lstm(bv.src[l], false, &m.enc_w[l], &m.p_enc_w[l], &m.enc_b[l], &ld))) return rc;
+    if ((rc = pack_lstm(bv.tgt[l], l == 0 && desc.feed_input, &m.dec_w[l], &m.p_dec_w[l], &m.dec_b[l], &m.dec_ldw[l]))) return rc;
   }
   // attention projections: rows < Hp: W_p (out n, in k) = blob[k*H + n];
   // rows Hp + j: (W_a^T h)[j] = sum_i W_a[i,j] h[i], W_a[i,j] = blob[j*H + i]  (src/layer_attention.h:327)
@@ -160,7 +166,7 @@ int Engine::pack_model(const float* blob, DevModel& m) {
       host[(size_t)n * Hp + kx] = bv.Wp[(size_t)kx * H + n];
       host[(size_t)(Hp + n) * Hp + kx] = bv.Wa[(size_t)n * H + kx];
     }
-  if ((rc = upload(&m.att_proj_w, host.size()))) return rc;
+  if ((rc = store(&m.att_proj_w, &m.p_att_proj_w, (size_t)2 * Hp, Hp))) return rc;
   // attention output: columns (ctx | h_top) -> W_c1 | W_c2 (src/layer_attention.h:441,448)
   host.assign((size_t)Hp * 2 * Hp, 0.f);
 #pragma omp parallel for schedule(static)
@@ -169,7 +175,7 @@ int Engine::pack_model(const float* blob, DevModel& m) {
       host[(size_t)n * 2 * Hp + kx] = bv.Wc1[(size_t)kx * H + n];
       host[(size_t)n * 2 * Hp + Hp + kx] = bv.Wc2[(size_t)kx * H + n];
     }
-  if ((rc = upload(&m.att_out_w, host.size()))) return rc;
+  if ((rc = store(&m.att_out_w, &m.p_att_out_w, (size_t)Hp, 2 * Hp))) return rc;
   host.assign(Hp, 0.f);
   std::memcpy(host.data(), bv.bout, sizeof(float) * H);
   if ((rc = upload(&m.att_bout, host.size()))) return rc;
@@ -181,7 +187,7 @@ int Engine::pack_model(const float* blob, DevModel& m) {
 #pragma omp parallel for schedule(static)
   for (int v = 0; v < V; ++v)
     for (int kx = 0; kx < H; ++kx) host[(size_t)v * Hp + kx] = bv.D[(size_t)kx * V + v];
-  if ((rc = upload(&m.voc_w, host.size()))) return rc;
+  if ((rc = store(&m.voc_w, &m.p_voc_w, (size_t)Vp, Hp))) return rc;
   host.assign(Vp, 0.f);
   std::memcpy(host.data(), bv.bd, sizeof(float) * V);
   if ((rc = upload(&m.voc_b, host.size()))) return rc;
@@ -211,7 +217,12 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
     return fail(LINMT_EINVAL, "bad model dimensions (layers 1..5)");
   if (nm < 1) return fail(LINMT_EINVAL, "need at least one model");
   if (nm > 1) return fail(LINMT_EINVAL, "ensembles are not built in this version");
-  if (o.precision != LINMT_PREC_FP32) return fail(LINMT_EINVAL, "only fp32 precision is built in this version");
+  if (o.precision != LINMT_PREC_FP32 && o.precision != LINMT_PREC_BF16) return fail(LINMT_EINVAL, "bad precision");
+  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR2) return fail(LINMT_EINVAL, "bad gemm_path");
+  if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
+    return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
+  use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
+  nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR2 ? 2 : 3);
   if (linmt_blob_floats(&d) != blob_floats) return fail(LINMT_EINVAL, "weight blob size does not match the model dimensions");
   if (o.beam <= 0) return fail(LINMT_EINVAL, "--beam-size cannot be <= 0");
   if (o.penalty < 0) return fail(LINMT_EINVAL, "--penalty cannot be < 0");
@@ -233,11 +244,15 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (cc_major != 10) return fail(LINMT_ECUDA, "this library is built for sm_100a (B200) only");
   CK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
   CK(cudaEventCreate(&ev0_)); CK(cudaEventCreate(&ev1_));
-  models_.resize(nm); states_.resize(nm);
+  CK(cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, o.device));
+  DA(d_tc_err_, 1);
+  CK(cudaMemset(d_tc_err_, 0, sizeof(int)));
+  models_.resize(nm); states_.resize(nm); tc_states_.resize(nm);
   for (int i = 0; i < nm; ++i) {
     int rc = pack_model(blobs[i], models_[i]);
     if (rc) return rc;
     if ((rc = alloc_state(states_[i]))) return rc;
+    if (use_tc_ && (rc = alloc_state_tc(tc_states_[i]))) return rc;
   }
   DA(d_off_, B + 1); DA(d_len_, B); DA(d_steps_, B); DA(d_orig_, B);
   CK(cudaMallocHost(&h_meta_, sizeof(int32_t) * 4 * (B + 1)));
@@ -251,7 +266,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   }
   // kernels that may need more than the default dynamic shared memory
   CK(cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 8));
-  CK(cudaStreamSynchronize(stream));
+  CK(cudaDeviceSynchronize());  // every weight upload has landed before the first decode
   return LINMT_OK;
 }
 
@@ -351,7 +366,8 @@ int Engine::run_decoder_step(int t, int rows) {
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
     const size_t smem = sizeof(float) * (win + 8);
     attention_kernel<<<rows, 128, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
-                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv);
+                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
+                                                  tc::Planes{}, 0);
     LAUNCHED();
   }
   // 5. attentional state htilde = tanh(W_c1 ctx + W_c2 h + b)
@@ -377,13 +393,18 @@ int Engine::run_decoder_step(int t, int rows) {
     LAUNCHED();
     if (kernel_timing) CK(cudaEventRecord(e1, stream));
   }
-  // 7. log-softmax statistics + per-beam top-(k+1)
+  return step_tail(t, rows);
+}
+
+// Log-softmax statistics + per-beam top-(k+1), then beam selection (both paths).
+int Engine::step_tail(int t, int rows) {
+  DevState& s = states_[0];
+  const int n_act = rows / k;
   {
     TopkOut o{d_cand_idx_, d_cand_logp_, d_eos_logp_};
     softmax_topk_kernel<<<rows, 256, (size_t)256 * kk * 8, stream>>>(s.logits, Vp, V, kk, o);
     LAUNCHED();
   }
-  // 8. beam selection
   {
     BeamState bs{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
     const size_t smem = (size_t)k * kk * 16;
@@ -443,16 +464,17 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     trace_dev_.force_score = trace_dev->force_score; trace_dev_.Tm = trace_Tm;
   }
   gemm_ev_used_ = 0;
-  int rc = run_encoder(n, Smax);
+  int rc = use_tc_ ? run_encoder_tc(n, Smax) : run_encoder(n, Smax);
   if (rc) return rc;
   // the encoder's final states sit in buffer (Smax & 1)
+  enc_final_buf_ = Smax & 1;
   enc_final_h_.assign(states_[0].enc_h[Smax & 1].begin(), states_[0].enc_h[Smax & 1].end());
   enc_final_c_.assign(states_[0].enc_c[Smax & 1].begin(), states_[0].enc_c[Smax & 1].end());
   for (int t = 0; t <= Tm; ++t) {
     int n_act = 0;
     while (n_act < n && m_steps[n_act] >= t) ++n_act;
     if (n_act == 0) break;
-    if ((rc = run_decoder_step(t, n_act * k))) return rc;
+    if ((rc = use_tc_ ? run_decoder_step_tc(t, n_act * k) : run_decoder_step(t, n_act * k))) return rc;
   }
   {
     FinalizeArgs a{};
@@ -473,6 +495,11 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
 
 int Engine::finish_timing() {
   CK(cudaStreamSynchronize(stream));
+  if (use_tc_) {
+    int herr = 0;
+    CK(cudaMemcpy(&herr, d_tc_err_, sizeof(int), cudaMemcpyDeviceToHost));
+    if (herr) return fail(LINMT_ECUDA, "a tensor-core GEMM gave up waiting on a barrier (results of this call are invalid)");
+  }
   CK(cudaEventElapsedTime(&stats.last_decode_ms, ev0_, ev1_));
   stats.last_gemm_ms = 0.f;
   stats.last_gemm_launches = (int)(gemm_ev_used_ / 2);

@@ -8,6 +8,10 @@
 
 #include "../../include/linmt_decoder.h"
 #include "step_kernels.cuh"
+#include "gemm_tc.cuh"
+#include <array>
+#include <map>
+#include <tuple>
 
 namespace linmt {
 
@@ -27,6 +31,19 @@ struct DevModel {
   float* vp = nullptr;                   // [Hp]
   float* voc_w = nullptr;                // [Vp][Hp]
   float* voc_b = nullptr;                // [Vp]
+  // the same operands as bf16 planes for the tensor-core path (fp32 copies are then not kept)
+  tc::Planes p_emb_src{}, p_emb_tgt{}, p_att_proj_w{}, p_att_out_w{}, p_voc_w{};
+  std::vector<tc::Planes> p_enc_w, p_dec_w;
+};
+
+// Activation panels of the tensor-core path: every GEMM reads ONE K-contiguous panel, so the
+// producers write straight into the column range of the panel that consumes them.
+struct TcState {
+  tc::Planes panel1{};               // [R][3Hp]  x | h_prev(layer 0) | htilde_prev
+  std::vector<tc::Planes> panel;     // l = 1..L-1: [R][2Hp]  h_cur(l-1) | h_prev(l)
+  tc::Planes panel_top{};            // [R][2Hp]  ctx | h_cur(L-1)
+  tc::Planes panel_ht{};             // [R][Hp]   htilde
+  std::vector<tc::Planes> encp[2];   // [L] x [B][2Hp]  below | h_prev, double buffered over positions
 };
 
 struct DevState {
@@ -75,10 +92,28 @@ class Engine {
   int alloc_state(DevState& s);
   int run_encoder(int n, int Smax);
   int run_decoder_step(int t, int rows);
+  int run_encoder_tc(int n, int Smax);
+  int run_decoder_step_tc(int t, int rows);
+  int step_tail(int t, int rows);
+  int alloc_state_tc(TcState& s);
+  int alloc_planes(tc::Planes& p, size_t rows, int ld);
+  int to_planes(const std::vector<float>& host, size_t rows, int ld, tc::Planes& dst);
+  const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K);
+  const CUtensorMap* b_maps(const tc::Planes& p, int rows, int K, int bn);
+  template <class Epi>
+  int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e);
+
+  bool use_tc_ = false;
+  int nt_ = 3;
+  int n_sm_ = 148;
+  int* d_tc_err_ = nullptr;
+  std::vector<TcState> tc_states_;
+  std::map<std::tuple<const void*, int, int, int, int>, std::array<CUtensorMap, 3>> tmap_cache_;
 
   const int32_t* cur_ids_ = nullptr;
   TraceDev trace_dev_{};
   std::vector<float*> enc_final_h_, enc_final_c_;
+  int enc_final_buf_ = 0;
   size_t out_cap_maxlen_ = 0;
   std::vector<DevModel> models_;
   std::vector<DevState> states_;

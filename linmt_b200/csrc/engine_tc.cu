@@ -1,0 +1,246 @@
+// engine_tc.cu -- the tensor-core path of the engine: operands as bf16 planes, every GEMM a
+// tcgen05/TMEM kernel fed by TMA, LSTM cell / tanh / bias fused into the epilogues.
+#include <cstdio>
+#include <cstring>
+
+#include "engine.h"
+#include "gemm_tc.cuh"
+#include "step_kernels.cuh"
+
+namespace linmt {
+
+#define CK(call)                                                                              \
+  do {                                                                                        \
+    cudaError_t e_ = (call);                                                                  \
+    if (e_ != cudaSuccess) {                                                                  \
+      char b_[512];                                                                           \
+      snprintf(b_, sizeof b_, "CUDA error %s at %s:%d: %s", cudaGetErrorName(e_), __FILE__, __LINE__, cudaGetErrorString(e_)); \
+      return fail(LINMT_ECUDA, b_);                                                           \
+    }                                                                                         \
+  } while (0)
+#define LAUNCHED() (++stats.kernel_launches)
+
+int Engine::alloc_planes(tc::Planes& p, size_t rows, int ld) {
+  p = tc::Planes{};
+  p.ld = ld;
+  for (int t = 0; t < nt_; ++t) {
+    void* q = nullptr;
+    const size_t bytes = rows * (size_t)ld * sizeof(__nv_bfloat16);
+    if (cudaMalloc(&q, bytes ? bytes : 2) != cudaSuccess) return fail(LINMT_ENOMEM, "cudaMalloc failed (operand planes)");
+    allocs_.push_back(q);
+    if (cudaMemset(q, 0, bytes) != cudaSuccess) return fail(LINMT_ECUDA, "cudaMemset failed (operand planes)");
+    p.p[t] = static_cast<__nv_bfloat16*>(q);
+  }
+  return LINMT_OK;
+}
+
+// fp32 host matrix -> device -> bf16 planes (the split runs on the GPU).
+int Engine::to_planes(const std::vector<float>& host, size_t rows, int ld, tc::Planes& dst) {
+  int rc = alloc_planes(dst, rows, ld);
+  if (rc) return rc;
+  float* tmp = nullptr;
+  const size_t n = rows * (size_t)ld;
+  if (host.size() < n) return fail(LINMT_EINVAL, "internal: packed matrix smaller than its planes");
+  if (cudaMalloc(&tmp, n * sizeof(float)) != cudaSuccess) return fail(LINMT_ENOMEM, "cudaMalloc failed (weight staging)");
+  // stream-ordered copy: the split kernel must not start before the last byte has landed
+  cudaError_t e = cudaMemcpyAsync(tmp, host.data(), n * sizeof(float), cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) {
+    tc::split_planes_kernel<<<2048, 256, 0, stream>>>(tmp, dst, nt_, n);
+    LAUNCHED();
+    e = cudaStreamSynchronize(stream);
+  }
+  cudaFree(tmp);
+  if (e != cudaSuccess) return fail(LINMT_ECUDA, std::string("weight split: ") + cudaGetErrorString(e));
+  return LINMT_OK;
+}
+
+int Engine::alloc_state_tc(TcState& s) {
+  int rc;
+  if ((rc = alloc_planes(s.panel1, R, 3 * Hp))) return rc;
+  s.panel.resize(L);
+  for (int l = 1; l < L; ++l)
+    if ((rc = alloc_planes(s.panel[l], R, 2 * Hp))) return rc;
+  if ((rc = alloc_planes(s.panel_top, R, 2 * Hp))) return rc;
+  if ((rc = alloc_planes(s.panel_ht, R, Hp))) return rc;
+  for (int i = 0; i < 2; ++i) {
+    s.encp[i].resize(L);
+    for (int l = 0; l < L; ++l)
+      if ((rc = alloc_planes(s.encp[i][l], B, 2 * Hp))) return rc;
+  }
+  return LINMT_OK;
+}
+
+// Tensor maps are built once per (buffer view, shape) and reused by every launch.
+const CUtensorMap* Engine::a_maps(const tc::Planes& p, int col0, int rows_cap, int K) {
+  auto key = std::make_tuple((const void*)(p.p[0] + col0), rows_cap, K, p.ld, (int)tc::BM);
+  auto it = tmap_cache_.find(key);
+  if (it == tmap_cache_.end()) {
+    std::array<CUtensorMap, 3> m{};
+    for (int t = 0; t < nt_; ++t)
+      if (!tc::make_tmap(&m[t], p.p[t] + col0, rows_cap, K, p.ld, tc::BM)) return nullptr;
+    it = tmap_cache_.emplace(key, m).first;
+  }
+  return it->second.data();
+}
+const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn) {
+  auto key = std::make_tuple((const void*)p.p[0], rows, K, p.ld, bn);
+  auto it = tmap_cache_.find(key);
+  if (it == tmap_cache_.end()) {
+    std::array<CUtensorMap, 3> m{};
+    for (int t = 0; t < nt_; ++t)
+      if (!tc::make_tmap(&m[t], p.p[t], rows, K, p.ld, bn)) return nullptr;
+    it = tmap_cache_.emplace(key, m).first;
+  }
+  return it->second.data();
+}
+
+// C[M][N] = A[:, a_col0 : a_col0+K] . W[N][K]^T with the tile width chosen for this shape.
+template <class Epi>
+int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e) {
+  const int bn = tc::pick_bn(M, N, n_sm_);
+  const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K);
+  const CUtensorMap* bm = b_maps(W, N, K, bn);
+  if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
+  tc::TmapSet tm;
+  std::memcpy(tm.a, am, sizeof(tm.a));
+  std::memcpy(tm.b, bm, sizeof(tm.b));
+  CK(tc::launch_gemm_tc(tm, M, N, K, tc::make_shape(bn, nt_), e, d_tc_err_, stream));
+  LAUNCHED();
+  return LINMT_OK;
+}
+
+static tc::Planes no_planes() { return tc::Planes{}; }
+
+// Encoder, tensor-core path (see Engine::run_encoder for the reference procedure).  Panel of
+// layer l at position p: encp[p&1][l] = (input from below | h_prev).  The epilogue writes h to
+// the next position's h_prev slot and to the next layer's input slot of this position.
+int Engine::run_encoder_tc(int n, int Smax) {
+  for (int mi = 0; mi < n_models; ++mi) {
+    DevModel& m = models_[mi];
+    DevState& s = states_[mi];
+    TcState& ts = tc_states_[mi];
+    for (int l = 0; l < L; ++l) {
+      CK(cudaMemsetAsync(s.enc_c[0][l], 0, sizeof(float) * (size_t)B * Hp, stream));
+      for (int t = 0; t < nt_; ++t)  // h_prev = 0 at the first position
+        CK(cudaMemset2DAsync(ts.encp[0][l].p[t] + Hp, (size_t)2 * Hp * 2, 0, (size_t)Hp * 2, B, stream));
+    }
+    for (int pos = 0; pos < Smax; ++pos) {
+      const int in = pos & 1, out = in ^ 1;
+      {
+        dim3 grid(n, nt_);
+        enc_embed_planes_kernel<<<grid, 128, 0, stream>>>(cur_ids_, d_off_, d_len_, m.p_emb_src, desc.vocab_src, ts.encp[in][0], Hp, pos);
+        LAUNCHED();
+      }
+      for (int l = 0; l < L; ++l) {
+        tc::TcEpiLstm e{};
+        e.bias = m.enc_b[l]; e.c_prev = s.enc_c[in][l]; e.ldc = Hp; e.c_out = s.enc_c[out][l];
+        e.h_out1 = ts.encp[out][l]; e.h1_col0 = Hp;
+        if (l + 1 < L) { e.h_out2 = ts.encp[in][l + 1]; e.h2_col0 = 0; } else { e.h_out2 = no_planes(); e.h2_col0 = 0; }
+        e.h_prev = ts.encp[in][l]; e.hp_col0 = Hp;
+        e.h_f32 = (l == L - 1) ? s.hs + (size_t)pos * Hp : nullptr;
+        e.hf_row_stride = (long long)opt.max_src_len * Hp;
+        e.row_len = d_len_; e.pos = pos; e.nt = nt_;
+        int rc = tc_gemm(ts.encp[in][l], 0, B, m.p_enc_w[l], n, 4 * Hp, 2 * Hp, e);
+        if (rc) return rc;
+      }
+    }
+  }
+  return LINMT_OK;
+}
+
+// One decoder forward, tensor-core path (see Engine::run_decoder_step).
+int Engine::run_decoder_step_tc(int t, int rows) {
+  DevModel& m = models_[0];
+  DevState& s = states_[0];
+  TcState& ts = tc_states_[0];
+  const bool feed = desc.feed_input && t > 0;
+  // where h_cur of layer l lives after its GEMM: the input slot of the consumer panel
+  auto hcur_planes = [&](int l) -> const tc::Planes& { return (l + 1 < L) ? ts.panel[l + 1] : ts.panel_top; };
+  auto hcur_col0 = [&](int l) { return (l + 1 < L) ? 0 : Hp; };
+  auto hprev_planes = [&](int l) -> const tc::Planes& { return l == 0 ? ts.panel1 : ts.panel[l]; };
+  // 1. gather states through the parents into the h_prev slots, look up embeddings
+  {
+    GatherJobs jobs{};
+    int nj = 0;
+    auto add = [&](const void* src, long long sstride, void* dst, long long dstride, int bytes, int kind) {
+      jobs.j[nj++] = GatherJob{static_cast<const unsigned char*>(src), sstride, static_cast<unsigned char*>(dst), dstride, bytes, kind};
+    };
+    const int fb = enc_final_buf_;
+    for (int l = 0; l < L; ++l) {
+      for (int p = 0; p < nt_; ++p) {
+        const __nv_bfloat16* src;
+        long long sst;
+        if (t == 0) { src = ts.encp[fb][l].p[p] + Hp; sst = (long long)ts.encp[fb][l].ld * 2; }
+        else { src = hcur_planes(l).p[p] + hcur_col0(l); sst = (long long)hcur_planes(l).ld * 2; }
+        add(src, sst, hprev_planes(l).p[p] + Hp, (long long)hprev_planes(l).ld * 2, Hp * 2, 0);
+      }
+      add(t == 0 ? s.enc_c[fb][l] : s.c_cur[l], (long long)Hp * 4, s.c_prev[l], (long long)Hp * 4, Hp * 4, 0);
+    }
+    if (feed)
+      for (int p = 0; p < nt_; ++p)
+        add(ts.panel_ht.p[p], (long long)ts.panel_ht.ld * 2, ts.panel1.p[p] + 2 * Hp, (long long)ts.panel1.ld * 2, Hp * 2, 0);
+    for (int p = 0; p < nt_; ++p)
+      add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
+    jobs.n = nj;
+    dim3 grid(rows, nj);
+    row_gather_kernel<<<grid, 128, 0, stream>>>(jobs, d_parent_, d_tok_, V, k, t == 0 ? 1 : 0);
+    LAUNCHED();
+  }
+  // 2. LSTM stack
+  for (int l = 0; l < L; ++l) {
+    tc::TcEpiLstm e{};
+    e.bias = m.dec_b[l]; e.c_prev = s.c_prev[l]; e.ldc = Hp; e.c_out = s.c_cur[l];
+    e.h_out1 = hcur_planes(l); e.h1_col0 = hcur_col0(l);
+    e.h_out2 = no_planes(); e.h2_col0 = 0;
+    e.h_prev = no_planes(); e.hp_col0 = 0;
+    e.h_f32 = (l == L - 1 && opt.attention_mode == LINMT_ATT_GLOBAL_DOT) ? s.h_cur[l] : nullptr;
+    e.hf_row_stride = Hp;
+    e.row_len = nullptr; e.pos = 0; e.nt = nt_;
+    const int K = (l == 0 && feed) ? 3 * Hp : 2 * Hp;
+    int rc = tc_gemm(hprev_planes(l), 0, R, m.p_dec_w[l], rows, 4 * Hp, K, e);
+    if (rc) return rc;
+  }
+  // 3. attention projections: tanh(W_p h) | W_a^T h
+  const float* u_alt = nullptr;
+  if (opt.attention_mode != LINMT_ATT_GLOBAL_DOT) {
+    tc::TcEpiF32 e{nullptr, s.proj, 2 * Hp, Hp};
+    int rc = tc_gemm(ts.panel_top, Hp, R, m.p_att_proj_w, rows, 2 * Hp, Hp, e);
+    if (rc) return rc;
+  } else {
+    u_alt = s.h_cur[L - 1];
+  }
+  // 4. scores, softmax x Gaussian, context (written into the attention-output panel)
+  {
+    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
+    int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
+    int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
+    const size_t smem = sizeof(float) * (win + 8);
+    attention_kernel<<<rows, 128, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, nullptr, H, Hp, k,
+                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
+                                                  ts.panel_top, nt_);
+    LAUNCHED();
+  }
+  // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)
+  {
+    tc::TcEpiBiasTanh e{m.att_bout, ts.panel_ht, 0, nt_};
+    int rc = tc_gemm(ts.panel_top, 0, R, m.p_att_out_w, rows, Hp, 2 * Hp, e);
+    if (rc) return rc;
+  }
+  // 6. logits
+  {
+    tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (kernel_timing) {
+      if (gemm_ev_used_ + 2 > gemm_ev_.size())
+        for (int i = 0; i < 2; ++i) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); gemm_ev_.push_back(ev); }
+      e0 = gemm_ev_[gemm_ev_used_++]; e1 = gemm_ev_[gemm_ev_used_++];
+      CK(cudaEventRecord(e0, stream));
+    }
+    int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e);
+    if (rc) return rc;
+    if (kernel_timing) CK(cudaEventRecord(e1, stream));
+  }
+  return step_tail(t, rows);
+}
+
+}  // namespace linmt

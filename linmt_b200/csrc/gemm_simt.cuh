@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(ASegs a, const float* __
 
   const int tid = threadIdx.x;
   const int tx = tid % TXN, ty = tid / TXN;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
 
   constexpr int A_F4 = BM * BK / 4 / 256;  // float4 loads per thread
   constexpr int B_F4 = BN * BK / 4 / 256;
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(ASegs a, const float* __
 
 template <int BM, int BN, class Epi>
 inline cudaError_t launch_gemm_simt(const ASegs& a, const float* wt, int ldw, int M, int N, int K, const Epi& epi, cudaStream_t st) {
-  dim3 grid(N / BN, (M + BM - 1) / BM);
+  dim3 grid((M + BM - 1) / BM, N / BN);
   gemm_simt_kernel<BM, BN, Epi><<<grid, 256, 0, st>>>(a, wt, ldw, M, N, K, epi);
   return cudaGetLastError();
 }

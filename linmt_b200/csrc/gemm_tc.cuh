@@ -1,0 +1,419 @@
+// gemm_tc.cuh -- tensor-core GEMM for sm_100a: tcgen05.mma with the accumulator in TMEM,
+// operands brought to shared memory by TMA (no multicast), fused epilogues.
+//
+//   C[M][N] = A[M][K] . Wt[N][K]^T        (both operands K-contiguous, "K-major")
+//
+// Precision.  The tensor cores multiply bf16.  An fp32 operand x is held as NT bf16 planes
+// x ~ p0 + p1 (+ p2), p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1); a product of
+// two split operands is the sum of the partial products whose weight is at least 2^-16
+// (NT = 3: p0p0, p0p1, p1p0, p1p1, p0p2, p2p0 -- error ~2^-23 per product, i.e. fp32-class
+// results; NT = 2: p0p0, p0p1, p1p0, p1p1 -- error ~2^-17; NT = 1: plain bf16).  The tensor
+// core truncates a little on every accumulate, in units of the accumulator's magnitude, so the
+// leading product p0p0 has a TMEM accumulator of its own and all the small cross terms share a
+// second one (their truncation is 2^-8 smaller in absolute terms); the epilogue adds the two.
+//
+// One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) and NT are launch
+// parameters so the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues TMA loads, warp 1 owns TMEM and issues
+// the MMAs, warps 2..5 run the epilogue (tcgen05.ld -> registers -> fused math -> global).
+// A ring of shared-memory stages is handed back and forth with mbarriers; every wait is
+// bounded and reports through an error flag instead of hanging.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace linmt {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 32;             // bf16 elements per stage row = 64 bytes -> 64-byte swizzle
+constexpr int UMMA_K = 16;         // bf16 elements per tcgen05.mma
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
+
+struct alignas(64) TmapSet {
+  CUtensorMap a[3];
+  CUtensorMap b[3];
+};
+
+constexpr int A_BYTES = BM * BK * 2;         // one plane of the A tile of a stage
+constexpr int SMEM_BUDGET = 222 * 1024;
+constexpr int TMEM_COLS = 512;         // two accumulators of up to 256 columns each
+constexpr int ACC2_COL = 256;          // first column of the second accumulator
+constexpr int kMaxStages = 8;
+
+struct Shape {
+  int bn;        // tile width
+  int nt;        // planes per operand
+  int stages;
+  int stage_bytes;
+  int smem_bytes;
+};
+inline Shape make_shape(int bn, int nt) {
+  Shape s;
+  s.bn = bn; s.nt = nt;
+  s.stage_bytes = nt * (A_BYTES + bn * BK * 2);
+  s.stages = SMEM_BUDGET / s.stage_bytes;
+  if (s.stages > kMaxStages) s.stages = kMaxStages;
+  s.smem_bytes = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  return s;
+}
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false (and raises *abort_flag) when the phase does not complete in
+// about a second or when another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long)clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 64 bytes (BK bf16) with
+// the 64-byte swizzle TMA wrote: 8-row groups are 512 bytes apart.
+//   bits 0-13 start address >> 4 | 16-29 leading byte offset >> 4 (unused here) |
+//   32-45 stride byte offset >> 4 | 46-47 descriptor version (1) | 61-63 swizzle (4 = 64 B)
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(512u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ inline uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- operand planes -----------------------------------------------------------------------
+// An activation or weight matrix as NT bf16 planes with a common leading dimension.
+struct Planes {
+  __nv_bfloat16* p[3];
+  int ld;
+};
+__device__ __forceinline__ void split_store(const Planes& pl, int nt, size_t idx, float x) {
+  const __nv_bfloat16 b0 = __float2bfloat16_rn(x);
+  pl.p[0][idx] = b0;
+  if (nt > 1) {
+    const float r1 = x - __bfloat162float(b0);
+    const __nv_bfloat16 b1 = __float2bfloat16_rn(r1);
+    pl.p[1][idx] = b1;
+    if (nt > 2) pl.p[2][idx] = __float2bfloat16_rn(r1 - __bfloat162float(b1));
+  }
+}
+// The value a consumer of the planes sees.
+__device__ __forceinline__ float planes_value(float x, int nt) {
+  const __nv_bfloat16 b0 = __float2bfloat16_rn(x);
+  if (nt == 1) return __bfloat162float(b0);
+  return x;
+}
+
+// ---- epilogues: called per (row, 16 consecutive columns) ------------------------------------
+__device__ __forceinline__ float sigmoid_tc(float x) { return 1.0f / (1.0f + expf(-1.0f * x)); }
+
+// LSTM cell update on gate-interleaved columns (see EpiLstm in gemm_simt.cuh for the math and
+// the reference kernels it replaces).  h goes out as bf16 planes to up to two places (the
+// operand panels that read it next) and optionally as fp32 (encoder top states).
+struct TcEpiLstm {
+  const float* bias;
+  const float* c_prev; int ldc;
+  float* c_out;
+  Planes h_out1; int h1_col0;      // element (row, j) at plane[row * ld + h1_col0 + j]
+  Planes h_out2; int h2_col0;      // optional (p[0] == nullptr: none)
+  Planes h_prev; int hp_col0;      // read for rows past their length (encoder)
+  float* h_f32; long long hf_row_stride;  // optional fp32 copy, element (row, j) at h_f32[row*stride + j]
+  const int* row_len; int pos;
+  int nt;
+  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+    const bool active = (row_len == nullptr) || (pos < row_len[row]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = (col0 >> 2) + u;
+      const size_t ic = (size_t)row * ldc + j;
+      if (active) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * u);
+        const float gi = sigmoid_tc(v[4 * u + 0] + b.x);
+        const float gf = sigmoid_tc(v[4 * u + 1] + b.y);
+        const float gg = tanhf(v[4 * u + 2] + b.z);
+        const float go = sigmoid_tc(v[4 * u + 3] + b.w);
+        const float c = gf * c_prev[ic] + gi * gg;
+        const float h = go * tanhf(c);
+        c_out[ic] = c;
+        split_store(h_out1, nt, (size_t)row * h_out1.ld + h1_col0 + j, h);
+        if (h_out2.p[0]) split_store(h_out2, nt, (size_t)row * h_out2.ld + h2_col0 + j, h);
+        if (h_f32) h_f32[(size_t)row * hf_row_stride + j] = planes_value(h, nt);
+      } else {
+        c_out[ic] = c_prev[ic];
+        const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j;
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+          if (t < nt) {
+            const __nv_bfloat16 hv = h_prev.p[t][ip];
+            h_out1.p[t][(size_t)row * h_out1.ld + h1_col0 + j] = hv;
+            if (h_out2.p[0]) h_out2.p[t][(size_t)row * h_out2.ld + h2_col0 + j] = hv;
+          }
+      }
+    }
+  }
+};
+
+// out = tanh(acc + bias) as bf16 planes (the attentional state).
+struct TcEpiBiasTanh {
+  const float* bias;
+  Planes out; int col_off;
+  int nt;
+  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      split_store(out, nt, (size_t)row * out.ld + col_off + col0 + i, tanhf(v[i] + bias[col0 + i]));
+  }
+};
+
+// fp32 out, tanh on columns below `split`, optional bias (attention projections, logits).
+struct TcEpiF32 {
+  const float* bias;  // may be null
+  float* out; int ld;
+  int split;          // columns < split get tanh
+  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+    float* o = out + (size_t)row * ld + col0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float4 r = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      if (bias) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
+        r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+      }
+      if (col0 < split) { r.x = tanhf(r.x); r.y = tanhf(r.y); r.z = tanhf(r.z); r.w = tanhf(r.w); }
+      *reinterpret_cast<float4*>(o + 4 * q) = r;
+    }
+  }
+};
+
+// ---- kernel -------------------------------------------------------------------------------
+template <class Epi>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int NT, int STAGES, Epi epi,
+               int* __restrict__ err_flag) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // stage tiles need 1024-byte alignment
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const int B_BYTES = BN * BK * 2;
+  const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
+  const uint32_t bars = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], accum
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
+  const int nkb = K / BK;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) break;
+        mbar_expect_tx(full_bar(s), (uint32_t)STAGE_BYTES);
+        const uint32_t st = base + s * STAGE_BYTES;
+        for (int t = 0; t < NT; ++t) tma_load_2d(st + t * A_BYTES, &tm.a[t], kb * BK, m0, full_bar(s));
+        for (int t = 0; t < NT; ++t) tma_load_2d(st + NT * A_BYTES + t * B_BYTES, &tm.b[t], kb * BK, n0, full_bar(s));
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN);
+      // partial products (plane of A, plane of B) in increasing order of weight, packed 2 bits each
+      const int NP = (NT == 1) ? 1 : (NT == 2 ? 4 : 6);
+      const uint32_t PA = (NT == 3) ? (2u | 0u << 2 | 1u << 4 | 1u << 6 | 0u << 8 | 0u << 10) : (NT == 2 ? (1u | 1u << 2) : 0u);
+      const uint32_t PB = (NT == 3) ? (0u | 2u << 2 | 1u << 4 | 0u << 6 | 1u << 8 | 0u << 10) : (NT == 2 ? (1u | 0u << 2 | 1u << 4) : 0u);
+      int s = 0; uint32_t ph = 0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(full_bar(s), ph, &s_abort)) break;
+        tc_fence_after();
+        const uint32_t st = base + s * STAGE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+          for (int p = 0; p < NP; ++p) {
+            const int ia = (PA >> (2 * p)) & 3, ib = (PB >> (2 * p)) & 3;
+            const uint64_t ad = make_desc(st + ia * A_BYTES + ks * UMMA_K * 2);
+            const uint64_t bd = make_desc(st + NT * A_BYTES + ib * B_BYTES + ks * UMMA_K * 2);
+            // the last product of the list is p0p0 (main accumulator); the others go to the second
+            const bool main_acc = (p == NP - 1);
+            umma_bf16(main_acc ? tmem_acc : tmem_acc + ACC2_COL, ad, bd, idesc, (kb | ks | (main_acc ? 0 : p)) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty_bar(s));
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+      umma_commit(accum_bar);
+    }
+  } else {
+    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+    const int q = warp & 3;
+    const int row = m0 + q * 32 + lane;
+    if (mbar_wait(accum_bar, 0, &s_abort)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        if (NT > 1) {
+          float w[16];
+          tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC2_COL + c0), w);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += w[i];
+        }
+        if (row < M && n0 + c0 < N) epi(row, n0 + c0, v);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_acc, TMEM_COLS);
+  if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
+}
+
+// ---- fp32 -> bf16 planes ---------------------------------------------------------------------
+static __global__ void split_planes_kernel(const float* __restrict__ src, Planes dst, int nt, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    split_store(dst, nt, i, src[i]);
+}
+
+// ---- host side -------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map of a K-major bf16 matrix [rows][ld] (K columns used), box = BK x box_rows,
+// 64-byte swizzle.  Rows past `rows` and columns past `K` read as zero.
+inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <class Epi>
+inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
+                                  cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn);
+  gemm_tc_kernel<Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.nt, sh.stages, epi, err_flag);
+  return cudaGetLastError();
+}
+
+// Tile width that fills the SMs best for an M x N problem: the smallest makespan
+// ceil(tiles / SMs) * BN over the allowed widths (multiples of 16 whose tile is a whole
+// number of 1024-byte swizzle atoms, i.e. multiples of 16 rows of 64 bytes).
+inline int pick_bn(int M, int N, int n_sm) {
+  const int mt = (M + BM - 1) / BM;
+  int best = 256;
+  double best_cost = 1e30;
+  for (int bn = 256; bn >= 48; bn -= 16) {
+    const long tiles = (long)mt * ((N + bn - 1) / bn);
+    const long waves = (tiles + n_sm - 1) / n_sm;
+    // cost: tensor time ~ waves * bn, plus a fixed per-tile overhead (prologue, epilogue)
+    const double cost = (double)waves * (bn + 24);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace tc
+}  // namespace linmt

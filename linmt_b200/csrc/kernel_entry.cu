@@ -5,6 +5,7 @@
 
 #include "engine.h"
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
 #include "step_kernels.cuh"
 
 namespace {
@@ -23,7 +24,8 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
                  int32_t precision, int32_t device) {
   using namespace linmt;
   if (!X || !W || !Y || R < 1 || K < 1 || N < 1) return LINMT_EINVAL;
-  if (gemm_path != LINMT_GEMM_SIMT || precision != LINMT_PREC_FP32) return LINMT_EINVAL;
+  if (gemm_path == LINMT_GEMM_SIMT && precision != LINMT_PREC_FP32) return LINMT_EINVAL;
+  if (gemm_path != LINMT_GEMM_SIMT && gemm_path != LINMT_GEMM_TENSOR && gemm_path != LINMT_GEMM_TENSOR2) return LINMT_EINVAL;
   KCK(cudaSetDevice(device));
   const int Kp = round_up(K, 64), Np = round_up(N, 128);
   std::vector<float> xp((size_t)R * Kp, 0.f), wt((size_t)Np * Kp, 0.f);
@@ -34,10 +36,41 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
   KCK(dx.alloc(xp.size() * 4)); KCK(dw.alloc(wt.size() * 4)); KCK(dy.alloc((size_t)R * Np * 4));
   KCK(cudaMemcpy(dx.p, xp.data(), xp.size() * 4, cudaMemcpyHostToDevice));
   KCK(cudaMemcpy(dw.p, wt.data(), wt.size() * 4, cudaMemcpyHostToDevice));
-  ASegs a{}; a.ptr[0] = dx.as<float>(); a.ld[0] = Kp; a.nseg = 1; a.seg_k = Kp;
-  EpiBias e{nullptr, dy.as<float>(), Np};
-  KCK(gemm_simt(a, dw.as<float>(), Kp, R, Np, Kp, e, 0));
-  KCK(cudaDeviceSynchronize());
+  if (gemm_path == LINMT_GEMM_SIMT) {
+    ASegs a{}; a.ptr[0] = dx.as<float>(); a.ld[0] = Kp; a.nseg = 1; a.seg_k = Kp;
+    EpiBias e{nullptr, dy.as<float>(), Np};
+    KCK(gemm_simt(a, dw.as<float>(), Kp, R, Np, Kp, e, 0));
+    KCK(cudaDeviceSynchronize());
+  } else {
+    const int nt = (precision == LINMT_PREC_BF16) ? 1 : (gemm_path == LINMT_GEMM_TENSOR2 ? 2 : 3);
+    DevBuf pa[3], pb[3], derr;
+    tc::Planes A{}, B{};
+    A.ld = Kp; B.ld = Kp;
+    for (int t = 0; t < nt; ++t) {
+      KCK(pa[t].alloc(xp.size() * 2)); KCK(pb[t].alloc(wt.size() * 2));
+      A.p[t] = pa[t].as<__nv_bfloat16>(); B.p[t] = pb[t].as<__nv_bfloat16>();
+    }
+    KCK(derr.alloc(4));
+    KCK(cudaMemset(derr.p, 0, 4));
+    tc::split_planes_kernel<<<256, 256>>>(dx.as<float>(), A, nt, xp.size());
+    tc::split_planes_kernel<<<1024, 256>>>(dw.as<float>(), B, nt, wt.size());
+    KCK(cudaGetLastError());
+    tc::TmapSet tm{};
+    for (int t = 0; t < nt; ++t) {
+      if (!tc::make_tmap(&tm.a[t], A.p[t], R, Kp, Kp, tc::BM)) return LINMT_ECUDA;
+      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, 256)) return LINMT_ECUDA;
+    }
+    tc::TcEpiF32 e{nullptr, dy.as<float>(), Np, 0};
+    const int bn = tc::pick_bn(R, Np, 148);
+    for (int t = 0; t < nt; ++t)
+      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn)) return LINMT_ECUDA;
+    cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, tc::make_shape(bn, nt), e, derr.as<int>(), 0);
+    KCK(le);
+    KCK(cudaDeviceSynchronize());
+    int herr = 0;
+    KCK(cudaMemcpy(&herr, derr.p, 4, cudaMemcpyDeviceToHost));
+    if (herr) return LINMT_ECUDA;
+  }
   std::vector<float> yp((size_t)R * Np);
   KCK(cudaMemcpy(yp.data(), dy.p, yp.size() * 4, cudaMemcpyDeviceToHost));
   for (int r = 0; r < R; ++r) std::memcpy(Y + (size_t)r * N, &yp[(size_t)r * Np], sizeof(float) * N);

@@ -7,6 +7,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "gemm_tc.cuh"
+
 namespace linmt {
 
 constexpr int kMaxBeam = 31;          // kk = beam + 1 <= 32
@@ -69,6 +71,58 @@ static __global__ void dec_prep_kernel(PrepArrays arr, const int32_t* __restrict
 }
 
 // ---------------------------------------------------------------------------------------
+// The same step start for the tensor-core path, where states live as bf16 planes inside the
+// operand panels: a list of byte-row copy jobs.  kind 0: state row gathered through the parent
+// (or, at step 0, the sentence's encoder row); kind 1: embedding row of the slot's token.
+// grid = (rows, n_jobs), block = 128
+struct GatherJob {
+  const unsigned char* src; long long src_stride;   // bytes
+  unsigned char* dst; long long dst_stride;
+  int row_bytes;   // multiple of 16
+  int kind;
+};
+struct GatherJobs {
+  GatherJob j[32];
+  int n;
+};
+static __global__ void row_gather_kernel(GatherJobs jobs, const int32_t* __restrict__ parent, const int32_t* __restrict__ tok,
+                                         int vocab, int k, int src_per_sentence) {
+  const int r = blockIdx.x;
+  const GatherJob& jb = jobs.j[blockIdx.y];
+  long long srow;
+  if (jb.kind == 1) {
+    int t = tok[r];
+    if (t < 0 || t >= vocab) t = kUnk;
+    srow = t;
+  } else {
+    const int sent = r / k;
+    srow = src_per_sentence ? sent : sent * k + parent[r];
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(jb.src + srow * jb.src_stride);
+  uint4* dst = reinterpret_cast<uint4*>(jb.dst + (long long)r * jb.dst_stride);
+  for (int i = threadIdx.x; i < jb.row_bytes / 16; i += blockDim.x) dst[i] = src[i];
+}
+
+// Encoder input for the tensor-core path: embedding planes of the token at reversed position
+// `pos` into columns [0, Hp) of the layer-0 panel; zeros past the sentence.
+// grid = (B, nt), block = 128
+static __global__ void enc_embed_planes_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ off,
+                                               const int32_t* __restrict__ len, tc::Planes emb, int vocab,
+                                               tc::Planes dst, int Hp, int pos) {
+  const int b = blockIdx.x, t = blockIdx.y;
+  const int S = len[b];
+  uint4* d = reinterpret_cast<uint4*>(dst.p[t] + (size_t)b * dst.ld);
+  if (pos < S) {
+    int tok = ids[off[b] + (S - 1 - pos)];
+    if (tok < 0 || tok >= vocab) tok = 0;
+    const uint4* src = reinterpret_cast<const uint4*>(emb.p[t] + (size_t)tok * emb.ld);
+    for (int i = threadIdx.x; i < Hp / 8; i += blockDim.x) d[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < Hp / 8; i += blockDim.x) d[i] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Block-wide sum in a fixed order (deterministic).
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
@@ -90,7 +144,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // CreateCTKernel).
 //   proj [rows][2*Hp]: tanh(W_p h) | W_a^T h      (global_dot: `u` = h_top itself)
 //   hs   [B][max_src][Hp]: top encoder state after consuming reversed position p
-//   ctx  [rows][Hp]
+//   ctx  [rows][Hp] fp32 and/or ctx_planes (bf16 planes, columns [0,Hp) of the panel)
 //   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
 //   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
 // grid = rows, block = 128, dynamic smem = (win + 8) floats
@@ -98,7 +152,7 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
-                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit) {
+                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt) {
   extern __shared__ float sm[];
   float* e = sm;            // [win]
   float* red = sm + win;    // [8]
@@ -167,7 +221,7 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
   if (rec_align)
     for (int w = threadIdx.x; w < win; w += blockDim.x) rec_align[(size_t)r * win + w] = (w < W) ? e[w] : 0.f;
   // context: CreateCTKernel, deep_rnn_kernel.h:1250-1260 (sum over window positions in order)
-  float* crow = ctx + (size_t)r * Hp;
+  float* crow = ctx ? ctx + (size_t)r * Hp : nullptr;
   for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int w = 0; w < W; ++w) {
@@ -175,7 +229,12 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
       const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
       acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
     }
-    *reinterpret_cast<float4*>(crow + j) = acc;
+    if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
+    if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
+      const size_t idx = (size_t)r * ctx_planes.ld + j;
+      tc::split_store(ctx_planes, nt, idx, acc.x); tc::split_store(ctx_planes, nt, idx + 1, acc.y);
+      tc::split_store(ctx_planes, nt, idx + 2, acc.z); tc::split_store(ctx_planes, nt, idx + 3, acc.w);
+    }
   }
 }
 

@@ -512,12 +512,13 @@ void linmt_oracle_softmax_topk(const float* logits, int R, int V, int kk, int32_
 //   tr_surv_tok/tr_surv_parent/tr_surv_score [n_sent][Tm][k]
 //   tr_final_logp [n_sent][k]  logf(p[EOS]) at the extra forward
 //   tr_logp_full  [n_sent][Tm+1][k][V] logf(p) of every forward (small models only)
+//   tr_pt         [n_sent][Tm+1][k] attention centre p_t of member 0 at every forward
 int linmt_oracle_decode(int n_models, const int32_t* desc, const float* const* blobs, size_t blob_n,
                         const void* opts_raw, int n_sent, const int32_t* src_ids, const int32_t* src_off,
                         const int32_t* steps, int32_t* out_tok, int32_t* out_len, float* out_score,
                         int32_t* out_vit, float* out_align, int32_t* tr_cand_tok, float* tr_cand_logp,
                         int32_t* tr_surv_tok, int32_t* tr_surv_parent, float* tr_surv_score,
-                        float* tr_final_logp, float* tr_logp_full) {
+                        float* tr_final_logp, float* tr_logp_full, float* tr_pt) {
   Opts o;
   std::memcpy(&o, opts_raw, sizeof(Opts));
 #ifdef _OPENMP
@@ -634,6 +635,9 @@ int linmt_oracle_decode(int n_models, const int32_t* desc, const float* const* b
           vit[r] = mj;
         }
       }
+      if (tr_pt)
+        for (int i = 0; i < n_act; ++i)
+          for (int b = 0; b < k; ++b) tr_pt[((size_t)order[i] * (Tm + 1) + t) * k + b] = runs[0].pt[i * k + b];
       if (tr_logp_full) {
         for (int i = 0; i < n_act; ++i)
           for (int b = 0; b < k; ++b) {

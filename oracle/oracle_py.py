@@ -103,7 +103,8 @@ def decode(desc, blobs, sents, *, beam, nbest=1, attention="local_p_general", at
     if trace:
         tr = {"cand_tok": np.full((n, Tm, k, k + 1), -1, np.int32), "cand_logp": np.zeros((n, Tm, k, k + 1), np.float32),
               "surv_tok": np.full((n, Tm, k), -1, np.int32), "surv_parent": np.full((n, Tm, k), -1, np.int32),
-              "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32)}
+              "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32),
+              "pt": np.zeros((n, Tm + 1, k), np.float32)}
     if full_logp:
         tr["logp_full"] = np.zeros((n, Tm + 1, k, V), np.float32)
     rc = L.linmt_oracle_decode(
@@ -114,7 +115,7 @@ def decode(desc, blobs, sents, *, beam, nbest=1, attention="local_p_general", at
         _p(out["align"], C.c_float),
         _p(tr.get("cand_tok"), C.c_int32), _p(tr.get("cand_logp"), C.c_float), _p(tr.get("surv_tok"), C.c_int32),
         _p(tr.get("surv_parent"), C.c_int32), _p(tr.get("surv_score"), C.c_float), _p(tr.get("final_logp"), C.c_float),
-        _p(tr.get("logp_full"), C.c_float))
+        _p(tr.get("logp_full"), C.c_float), _p(tr.get("pt"), C.c_float))
     if rc != 0:
         raise RuntimeError(f"linmt_oracle_decode failed with status {rc}")
     out.update(tr)

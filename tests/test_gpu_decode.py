@@ -39,7 +39,7 @@ def test_c1_against_golden_and_checker(oracle, cuda_lib, c1, case, kw):
     g = np.load(os.path.join(GOLD, case + ".npz"))
     dec = _decoder(c, blob, **kw)
     forced = dec.decode(sents, trace=True, force={k: g[k] for k in ("surv_tok", "surv_parent", "surv_score")})
-    worst, bad = compare_forced(forced, {k: g[k] for k in ("cand_tok", "cand_logp")}, sents.steps)
+    worst, bad, _, _ = compare_forced(forced, {k: g[k] for k in ("cand_tok", "cand_logp", "surv_parent")}, sents.steps)
     assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
     np.testing.assert_allclose(forced["final_logp"], g["final_logp"], rtol=RTOL_FP32)
     free = dec.decode(sents, trace=True)
@@ -60,8 +60,8 @@ def test_global_dot_and_diversity(oracle, cuda_lib, c1):
     o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
     dec = _decoder(c, blob, **kw)
     forced = dec.decode(sents, trace=True, force=o)
-    worst, bad = compare_forced(forced, o, sents.steps)
-    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
+    assert worst <= RTOL_FP32 and bad == 0 and skipped <= 0.1 * (skipped + compared), (worst, bad, skipped, compared)
     dec.close()
 
 
@@ -96,8 +96,8 @@ def test_ragged_batches_and_chunking(oracle, cuda_lib):
     o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
     dec = _decoder(c, blob, max_batch=4, **kw)
     forced = dec.decode(sents, trace=True, force=o)
-    worst, bad = compare_forced(forced, o, sents.steps)
-    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
+    assert worst <= RTOL_FP32 and bad == 0 and skipped <= 0.1 * (skipped + compared), (worst, bad, skipped, compared)
     free = dec.decode(sents)
     assert token_identity(free, o, sents.n) >= 0.7
     assert (free["len"][:, 0] == o["len"][:, 0]).all()
@@ -119,7 +119,8 @@ def test_limits_are_errors_not_faults(cuda_lib, c1):
         decoder.Decoder(c.desc, [blob[:-1]], beam=2)
 
 
-def test_c2_shape_subset(oracle, cuda_lib):
+@pytest.mark.parametrize("gemm_path", ["simt", "tensor", "tensor2"])
+def test_c2_shape_subset(oracle, cuda_lib, gemm_path):
     """The 4 x 1000, 30k-vocabulary, beam-12 model on 6 sentences of the reference decode
     configuration, against the checker."""
     c = synth.configs()["C2"]
@@ -128,10 +129,12 @@ def test_c2_shape_subset(oracle, cuda_lib):
     kw = dict(beam=12, nbest=1, lp_alpha=0.65, cp_beta=0.0)
     o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
     from linmt_b200 import decoder
-    dec = decoder.Decoder(c.desc, [blob], max_batch=8, max_src_len=64, max_steps=100, **kw)
+    dec = decoder.Decoder(c.desc, [blob], max_batch=8, max_src_len=64, max_steps=100, gemm_path=gemm_path, **kw)
     forced = dec.decode(sents, trace=True, force=o)
-    worst, bad = compare_forced(forced, o, sents.steps)
-    assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
+    # the two-plane tensor mode trades accuracy for speed: its documented bound is 1e-3
+    rtol = 1e-3 if gemm_path == "tensor2" else RTOL_FP32
+    worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, rtol=rtol, src_len=sents.lengths())
+    assert worst <= rtol and bad == 0 and skipped <= 0.1 * (skipped + compared), (worst, bad, skipped, compared)
     free = dec.decode(sents)
     assert token_identity(free, o, sents.n) >= 0.66
     dec.close()
