@@ -182,6 +182,12 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
 int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, int32_t* idx, float* logp,
                          float* eos_logp, int32_t device);
 
+/* Average milliseconds of one tensor-core GEMM launch (R x N x K, operands already on the
+ * device) for a given tile width / plane count / stage limit; 0 = the engine's own choice.
+ * A tuning and roofline aid; has no counterpart in the reference. */
+int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
+                      float* ms_out, int32_t device);
+
 #ifdef __cplusplus
 }
 #endif

@@ -265,7 +265,6 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
     DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
   }
   // kernels that may need more than the default dynamic shared memory
-  CK(cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 8));
   CK(cudaDeviceSynchronize());  // every weight upload has landed before the first decode
   return LINMT_OK;
 }
@@ -402,7 +401,7 @@ int Engine::step_tail(int t, int rows) {
   const int n_act = rows / k;
   {
     TopkOut o{d_cand_idx_, d_cand_logp_, d_eos_logp_};
-    softmax_topk_kernel<<<rows, 256, (size_t)256 * kk * 8, stream>>>(s.logits, Vp, V, kk, o);
+    CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, stream));
     LAUNCHED();
   }
   {

@@ -9,12 +9,16 @@
 // (NT = 3: p0p0, p0p1, p1p0, p1p1, p0p2, p2p0 -- error ~2^-23 per product, i.e. fp32-class
 // results; NT = 2: p0p0, p0p1, p1p0, p1p1 -- error ~2^-17; NT = 1: plain bf16).  The tensor
 // core truncates a little on every accumulate, in units of the accumulator's magnitude, so the
-// leading product p0p0 has a TMEM accumulator of its own and all the small cross terms share a
+// leading product p0p0 has a TMEM accumulator of its own and the small cross terms share a
 // second one (their truncation is 2^-8 smaller in absolute terms); the epilogue adds the two.
+// Measured against a float64 product this gives the error of an fp32 FMA loop.
 //
-// One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) and NT are launch
-// parameters so the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues TMA loads, warp 1 owns TMEM and issues
-// the MMAs, warps 2..5 run the epilogue (tcgen05.ld -> registers -> fused math -> global).
+// One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) is a launch parameter so
+// the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues the TMA
+// loads, warp 1 owns TMEM and issues the MMAs, warps 2..9 run the epilogue (tcgen05.ld ->
+// registers -> fused math -> global).  The single issuing threads are the critical path of a
+// narrow tile, so their loops carry descriptors forward by constant increments and everything
+// that can be is a compile-time constant; the waiting epilogue warps sleep between polls.
 // A ring of shared-memory stages is handed back and forth with mbarriers; every wait is
 // bounded and reports through an error flag instead of hanging.
 #pragma once
@@ -29,7 +33,7 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 32;             // bf16 elements per stage row = 64 bytes -> 64-byte swizzle
 constexpr int UMMA_K = 16;         // bf16 elements per tcgen05.mma
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
 
 struct alignas(64) TmapSet {
@@ -40,7 +44,6 @@ struct alignas(64) TmapSet {
 constexpr int A_BYTES = BM * BK * 2;         // one plane of the A tile of a stage
 constexpr int SMEM_BUDGET = 222 * 1024;
 constexpr int TMEM_COLS = 512;         // two accumulators of up to 256 columns each
-constexpr int ACC2_COL = 256;          // first column of the second accumulator
 constexpr int kMaxStages = 8;
 
 struct Shape {
@@ -247,11 +250,41 @@ struct TcEpiF32 {
   }
 };
 
+// Accumulator layout in TMEM: accumulator a starts at column a * stride.
+__host__ __device__ inline int acc_stride(int bn) { return (bn + 31) & ~31; }
+
+// Partial products (plane of A, plane of B): the small cross terms first, the leading p0p0 last.
+__host__ __device__ constexpr int num_products(int nt) { return nt == 1 ? 1 : (nt == 2 ? 4 : 6); }
+__host__ __device__ constexpr int prod_a(int nt, int p) {
+  return nt == 3 ? (p == 0 ? 2 : (p == 2 || p == 3) ? 1 : 0) : (nt == 2 ? (p < 2 ? 1 : 0) : 0);
+}
+__host__ __device__ constexpr int prod_b(int nt, int p) {
+  return nt == 3 ? (p == 1 ? 2 : (p == 2 || p == 4) ? 1 : 0) : (nt == 2 ? ((p == 0 || p == 2) ? 1 : 0) : 0);
+}
+static_assert(prod_a(3, 0) == 2 && prod_b(3, 0) == 0 && prod_a(3, 1) == 0 && prod_b(3, 1) == 2 && prod_a(3, 2) == 1 &&
+              prod_b(3, 2) == 1 && prod_a(3, 3) == 1 && prod_b(3, 3) == 0 && prod_a(3, 4) == 0 && prod_b(3, 4) == 1 &&
+              prod_a(3, 5) == 0 && prod_b(3, 5) == 0, "NT=3 products: (2,0)(0,2)(1,1)(1,0)(0,1)(0,0)");
+static_assert(prod_a(2, 0) == 1 && prod_b(2, 0) == 1 && prod_a(2, 1) == 1 && prod_b(2, 1) == 0 && prod_a(2, 2) == 0 &&
+              prod_b(2, 2) == 1 && prod_a(2, 3) == 0 && prod_b(2, 3) == 0, "NT=2 products: (1,1)(1,0)(0,1)(0,0)");
+
+// Polite bounded wait for the warps that have nothing to do until the accumulator is ready:
+// sleeping between polls leaves the issue slots to the TMA and MMA threads.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(256);
+    if (*abort_flag) return false;
+    if ((unsigned long long)clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+  }
+  return true;
+}
+
 // ---- kernel -------------------------------------------------------------------------------
-template <class Epi>
+template <int NT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int NT, int STAGES, Epi epi,
+gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, Epi epi,
                int* __restrict__ err_flag) {
+  constexpr int NP = num_products(NT);
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // stage tiles need 1024-byte alignment
@@ -265,13 +298,11 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
   const int nkb = K / BK;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   const uint32_t accum_bar = bars + 8u * (2 * STAGES);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
     mbar_init(accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -285,58 +316,79 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   if (warp == 0) {
     if (lane == 0) {
       int s = 0; uint32_t ph = 0;
+      uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
       for (int kb = 0; kb < nkb; ++kb) {
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, &s_abort)) break;
-        mbar_expect_tx(full_bar(s), (uint32_t)STAGE_BYTES);
-        const uint32_t st = base + s * STAGE_BYTES;
-        for (int t = 0; t < NT; ++t) tma_load_2d(st + t * A_BYTES, &tm.a[t], kb * BK, m0, full_bar(s));
-        for (int t = 0; t < NT; ++t) tma_load_2d(st + NT * A_BYTES + t * B_BYTES, &tm.b[t], kb * BK, n0, full_bar(s));
-        if (++s == STAGES) { s = 0; ph ^= 1u; }
+        if (!mbar_wait(eb, ph ^ 1u, &s_abort)) break;
+        mbar_expect_tx(fb, (uint32_t)STAGE_BYTES);
+        const int kx = kb * BK;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) tma_load_2d(st + t * A_BYTES, &tm.a[t], kx, m0, fb);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) tma_load_2d(st + NT * A_BYTES + t * B_BYTES, &tm.b[t], kx, n0, fb);
+        st += STAGE_BYTES; fb += 8u; eb += 8u;
+        if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN);
-      // partial products (plane of A, plane of B) in increasing order of weight, packed 2 bits each
-      const int NP = (NT == 1) ? 1 : (NT == 2 ? 4 : 6);
-      const uint32_t PA = (NT == 3) ? (2u | 0u << 2 | 1u << 4 | 1u << 6 | 0u << 8 | 0u << 10) : (NT == 2 ? (1u | 1u << 2) : 0u);
-      const uint32_t PB = (NT == 3) ? (0u | 2u << 2 | 1u << 4 | 0u << 6 | 1u << 8 | 0u << 10) : (NT == 2 ? (1u | 0u << 2 | 1u << 4) : 0u);
+      const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
+      const uint64_t bstep = (uint64_t)(B_BYTES >> 4);           // one B plane, in descriptor units (16 bytes)
       int s = 0; uint32_t ph = 0;
+      uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
       for (int kb = 0; kb < nkb; ++kb) {
-        if (!mbar_wait(full_bar(s), ph, &s_abort)) break;
+        if (!mbar_wait(fb, ph, &s_abort)) break;
         tc_fence_after();
-        const uint32_t st = base + s * STAGE_BYTES;
+        const uint64_t a0 = make_desc(st);                        // plane 0 of A, k-step 0
+        const uint64_t b0 = make_desc(st + NT * A_BYTES);         // plane 0 of B, k-step 0
+        const uint32_t acc_old = kb ? 1u : 0u;
+        // Two passes over the stage, each into one accumulator; the order alternates per k-block
+        // (even: leading then small, odd: small then leading) so that consecutive blocks continue
+        // in the accumulator the previous one ended with.
 #pragma unroll
-        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-          for (int p = 0; p < NP; ++p) {
-            const int ia = (PA >> (2 * p)) & 3, ib = (PB >> (2 * p)) & 3;
-            const uint64_t ad = make_desc(st + ia * A_BYTES + ks * UMMA_K * 2);
-            const uint64_t bd = make_desc(st + NT * A_BYTES + ib * B_BYTES + ks * UMMA_K * 2);
-            // the last product of the list is p0p0 (main accumulator); the others go to the second
-            const bool main_acc = (p == NP - 1);
-            umma_bf16(main_acc ? tmem_acc : tmem_acc + ACC2_COL, ad, bd, idesc, (kb | ks | (main_acc ? 0 : p)) ? 1u : 0u);
+        for (int pass = 0; pass < (NP > 1 ? 2 : 1); ++pass) {
+          const bool lead = (NP == 1) || (pass == (kb & 1));
+          if (lead) {
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks)
+              umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (ks ? 1u : acc_old));
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+#pragma unroll
+              for (int p = 0; p < NP - 1; ++p) {
+                const uint64_t ad = a0 + (uint64_t)(((prod_a(NT, p) * A_BYTES) >> 4) + ks * 2);
+                const uint64_t bd = b0 + (uint64_t)prod_b(NT, p) * bstep + (uint64_t)(ks * 2);
+                umma_bf16(acc1, ad, bd, idesc, ((ks | p) ? 1u : acc_old));
+              }
+            }
           }
         }
-        umma_commit(empty_bar(s));
-        if (++s == STAGES) { s = 0; ph ^= 1u; }
+        umma_commit(eb);
+        st += STAGE_BYTES; fb += 8u; eb += 8u;
+        if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
       }
       umma_commit(accum_bar);
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the two warps of a lane quadrant
+    // take alternate 16-column chunks
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = m0 + q * 32 + lane;
-    if (mbar_wait(accum_bar, 0, &s_abort)) {
+    const uint32_t astride = (uint32_t)acc_stride(BN);
+    if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = half * 16; c0 < BN; c0 += 32) {
         float v[16];
-        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-        if (NT > 1) {
-          float w[16];
-          tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC2_COL + c0), w);
+        const uint32_t ta = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        tmem_ld16(ta, v);
+        if (NP > 1) {
+          float sm[16];
+          tmem_ld16(ta + astride, sm);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += w[i];
+          for (int i = 0; i < 16; ++i) v[i] += sm[i];
         }
         if (row < M && n0 + c0 < N) epi(row, n0 + c0, v);
       }
@@ -384,18 +436,25 @@ inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <class Epi>
-inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
-                                  cudaStream_t st) {
+template <int NT, class Epi>
+inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
+                                     cudaStream_t st) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn);
-  gemm_tc_kernel<Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.nt, sh.stages, epi, err_flag);
+  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, epi, err_flag);
   return cudaGetLastError();
+}
+template <class Epi>
+inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
+                                  cudaStream_t st) {
+  if (sh.nt == 3) return launch_gemm_tc_nt<3, Epi>(tm, M, N, K, sh, epi, err_flag, st);
+  if (sh.nt == 2) return launch_gemm_tc_nt<2, Epi>(tm, M, N, K, sh, epi, err_flag, st);
+  return launch_gemm_tc_nt<1, Epi>(tm, M, N, K, sh, epi, err_flag, st);
 }
 
 // Tile width that fills the SMs best for an M x N problem: the smallest makespan

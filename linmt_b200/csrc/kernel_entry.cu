@@ -88,14 +88,58 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
   DevBuf dl, di, dp, de;
   KCK(dl.alloc(lp.size() * 4)); KCK(di.alloc((size_t)R * kk * 4)); KCK(dp.alloc((size_t)R * kk * 4)); KCK(de.alloc((size_t)R * 4));
   KCK(cudaMemcpy(dl.p, lp.data(), lp.size() * 4, cudaMemcpyHostToDevice));
-  KCK(cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 32 * 8));
   TopkOut o{di.as<int32_t>(), dp.as<float>(), de.as<float>()};
-  softmax_topk_kernel<<<R, 256, (size_t)256 * kk * 8>>>(dl.as<float>(), Vp, V, kk, o);
-  KCK(cudaGetLastError());
+  KCK(launch_softmax_topk(dl.as<float>(), Vp, V, kk, R, o, 0));
   KCK(cudaDeviceSynchronize());
   KCK(cudaMemcpy(idx, di.p, (size_t)R * kk * 4, cudaMemcpyDeviceToHost));
   KCK(cudaMemcpy(logp, dp.p, (size_t)R * kk * 4, cudaMemcpyDeviceToHost));
   if (eos_logp) KCK(cudaMemcpy(eos_logp, de.p, (size_t)R * 4, cudaMemcpyDeviceToHost));
+  return LINMT_OK;
+}
+
+
+// Timing of the tensor-core GEMM alone on device-resident operands (tuning aid): returns the
+// average milliseconds of `iters` launches of an R x N x K problem with tile width bn (0 = the
+// engine's own choice), nt planes and at most max_stages shared-memory stages (0 = all that fit).
+int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
+                      float* ms_out, int32_t device) {
+  using namespace linmt;
+  if (R < 1 || K < 32 || N < 16 || nt < 1 || nt > 3 || iters < 1 || !ms_out) return LINMT_EINVAL;
+  if (K % 32 || N % 16) return LINMT_EINVAL;
+  KCK(cudaSetDevice(device));
+  if (bn <= 0) bn = tc::pick_bn(R, N, 148);
+  if (bn % 16 || bn > 256) return LINMT_EINVAL;
+  DevBuf pa[3], pb[3], dy, derr;
+  tc::Planes A{}, B{};
+  A.ld = K; B.ld = K;
+  for (int t = 0; t < nt; ++t) {
+    KCK(pa[t].alloc((size_t)R * K * 2)); KCK(pb[t].alloc((size_t)N * K * 2));
+    KCK(cudaMemset(pa[t].p, 0x3c, (size_t)R * K * 2)); KCK(cudaMemset(pb[t].p, 0x3c, (size_t)N * K * 2));
+    A.p[t] = pa[t].as<__nv_bfloat16>(); B.p[t] = pb[t].as<__nv_bfloat16>();
+  }
+  KCK(dy.alloc((size_t)R * N * 4)); KCK(derr.alloc(4)); KCK(cudaMemset(derr.p, 0, 4));
+  tc::TmapSet tm{};
+  for (int t = 0; t < nt; ++t) {
+    if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM)) return LINMT_ECUDA;
+    if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn)) return LINMT_ECUDA;
+  }
+  tc::Shape sh = tc::make_shape(bn, nt);
+  if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
+  tc::TcEpiF32 e{nullptr, dy.as<float>(), N, 0};
+  cudaEvent_t e0, e1;
+  KCK(cudaEventCreate(&e0)); KCK(cudaEventCreate(&e1));
+  for (int i = 0; i < 2; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0));
+  KCK(cudaEventRecord(e0, 0));
+  for (int i = 0; i < iters; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0));
+  KCK(cudaEventRecord(e1, 0));
+  KCK(cudaDeviceSynchronize());
+  float ms = 0.f;
+  KCK(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0); cudaEventDestroy(e1);
+  int herr = 0;
+  KCK(cudaMemcpy(&herr, derr.p, 4, cudaMemcpyDeviceToHost));
+  if (herr) return LINMT_ECUDA;
+  *ms_out = ms / iters;
   return LINMT_OK;
 }
 

@@ -245,7 +245,7 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
 // (src/decoder.h:1413) and the host scan that keeps the k+1 best per beam
 // (src/decoder.h:401-410).  Order: value descending, vocabulary index ascending -- what the
 // strict-greater replacement of the reference keeps.  log p = (z - max) - log(sum exp).
-// grid = rows, block = 256, dynamic smem = 256*kk*8 bytes.
+// grid = rows, block = 256.
 struct TopkOut {
   int32_t* idx;    // [rows][kk]
   float* logp;     // [rows][kk]
@@ -253,82 +253,126 @@ struct TopkOut {
 };
 __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
 
+// Pass 1 finds the row maximum and, from the 256 per-thread maxima, a threshold that at least
+// kk elements reach (the kk-th largest thread maximum).  Pass 2 (the row is L2/L1 resident by
+// then) sums exp(z - max) and collects the few elements at or above the threshold, which are
+// then ranked exactly.  If more elements than the candidate buffer holds reach the threshold
+// (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
+constexpr int kTopkCap = 1024;
 static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out) {
-  extern __shared__ unsigned char smraw[];
-  float* lv = reinterpret_cast<float*>(smraw);            // [kk][256] values, sorted descending per thread
-  int* li = reinterpret_cast<int*>(lv + kk * 256);        // [kk][256] indices
-  __shared__ float s_m[8], s_s[8];
-  __shared__ float s_bv[8];
-  __shared__ int s_bi[8], s_bt[8];
-  __shared__ float s_max, s_lse;
+  __shared__ float s_tmax[256];
+  __shared__ float s_cv[kTopkCap];
+  __shared__ int s_ci[kTopkCap];
+  __shared__ float s_red[8];
+  __shared__ int s_redi[8];
+  __shared__ int s_count;
+  __shared__ float s_tau, s_max, s_lse;
   const int r = blockIdx.x, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
   const float* z = logits + (size_t)r * ld;
-  for (int s = 0; s < kk; ++s) { lv[s * 256 + tid] = -INFINITY; li[s * 256 + tid] = 0x7fffffff; }
-  float m = -INFINITY, ssum = 0.f;
-  float thr = -INFINITY;  // current smallest kept value of this thread
+  const int V4 = V & ~3;
+  // ---- pass 1: maxima ----
+  float m = -INFINITY;
+  for (int i = tid * 4; i < V4; i += 256 * 4) {
+    const float4 q = *reinterpret_cast<const float4*>(z + i);
+    m = fmaxf(fmaxf(m, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
+  }
+  for (int i = V4 + tid; i < V; i += 256) m = fmaxf(m, z[i]);
+  s_tmax[tid] = m;
+  if (tid == 0) s_count = 0;
+  __syncthreads();
+  {
+    int rank = 0;
+    float bm = -INFINITY;
+    for (int j = 0; j < 256; ++j) {
+      const float o = s_tmax[j];
+      bm = fmaxf(bm, o);
+      rank += (o > m || (o == m && j < tid)) ? 1 : 0;
+    }
+    if (rank == (kk < 256 ? kk : 256) - 1) s_tau = m;
+    if (tid == 0) s_max = bm;
+  }
+  __syncthreads();
+  const float tau = s_tau, rmax = s_max;
+  // ---- pass 2: sum of exponentials, candidates ----
+  float ssum = 0.f;
   auto visit = [&](float v, int i) {
-    if (v > m) { ssum = ssum * expf(m - v) + 1.0f; m = v; } else { ssum += expf(v - m); }
-    if (v > thr) {
-      int s = kk - 1;
-      while (s > 0 && lv[(s - 1) * 256 + tid] < v) {
-        lv[s * 256 + tid] = lv[(s - 1) * 256 + tid];
-        li[s * 256 + tid] = li[(s - 1) * 256 + tid];
-        --s;
-      }
-      lv[s * 256 + tid] = v; li[s * 256 + tid] = i;
-      thr = lv[(kk - 1) * 256 + tid];
+    ssum += expf(v - rmax);
+    if (v >= tau) {
+      const int pos = atomicAdd(&s_count, 1);
+      if (pos < kTopkCap) { s_cv[pos] = v; s_ci[pos] = i; }
     }
   };
-  const int V4 = V & ~3;
   for (int i = tid * 4; i < V4; i += 256 * 4) {
     const float4 q = *reinterpret_cast<const float4*>(z + i);
     visit(q.x, i); visit(q.y, i + 1); visit(q.z, i + 2); visit(q.w, i + 3);
   }
   for (int i = V4 + tid; i < V; i += 256) visit(z[i], i);
-  // block (max, sum)
-  float wm = m;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-  float ws = (m == -INFINITY) ? 0.f : ssum * expf(m - wm);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
-  const int warp = tid >> 5, lane = tid & 31;
-  if (lane == 0) { s_m[warp] = wm; s_s[warp] = ws; }
+  for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+  if (lane == 0) s_red[warp] = ssum;
   __syncthreads();
   if (tid == 0) {
-    float bm = s_m[0];
-    for (int w = 1; w < 8; ++w) bm = fmaxf(bm, s_m[w]);
     float bs = 0.f;
-    for (int w = 0; w < 8; ++w) bs += s_s[w] * expf(s_m[w] - bm);
-    s_max = bm; s_lse = logf(bs);
-    if (out.eos_logp) out.eos_logp[r] = (z[kEos] - bm) - s_lse;
+    for (int w = 0; w < 8; ++w) bs += s_red[w];
+    s_lse = logf(bs);
+    if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
   }
   __syncthreads();
-  // kk rounds of block arg-best over each thread's best remaining entry
-  int head = 0;
+  const float rlse = s_lse;
+  const int n = s_count;
+  if (n <= kTopkCap) {
+    // exact ranking of the candidates: value descending, index ascending
+    for (int c = tid; c < n; c += 256) {
+      const float v = s_cv[c];
+      const int i = s_ci[c];
+      int rank = 0;
+      for (int d = 0; d < n; ++d) rank += better(s_cv[d], s_ci[d], v, i) ? 1 : 0;
+      if (rank < kk) {
+        out.idx[(size_t)r * kk + rank] = i;
+        out.logp[(size_t)r * kk + rank] = (v - rmax) - rlse;
+      }
+    }
+    for (int q = n + tid; q < kk; q += 256) {  // fewer than kk elements in the row
+      out.idx[(size_t)r * kk + q] = -1;
+      out.logp[(size_t)r * kk + q] = -INFINITY;
+    }
+    return;
+  }
+  // ---- fallback: kk sweeps, each picking the best element after the previous pick ----
+  float last_v = INFINITY;
+  int last_i = -1;
   for (int round = 0; round < kk; ++round) {
-    float v = (head < kk) ? lv[head * 256 + tid] : -INFINITY;
-    int i = (head < kk) ? li[head * 256 + tid] : 0x7fffffff;
-    int t = tid;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < V; i += 256) {
+      const float v = z[i];
+      const bool after = (v < last_v) || (v == last_v && i > last_i);
+      if (after && better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
-      const int ot = __shfl_xor_sync(0xffffffffu, t, o);
-      if (better(ov, oi, v, i)) { v = ov; i = oi; t = ot; }
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    if (lane == 0) { s_bv[warp] = v; s_bi[warp] = i; s_bt[warp] = t; }
     __syncthreads();
-    float bv = s_bv[0]; int bi = s_bi[0], bt = s_bt[0];
-    for (int w = 1; w < 8; ++w) if (better(s_bv[w], s_bi[w], bv, bi)) { bv = s_bv[w]; bi = s_bi[w]; bt = s_bt[w]; }
-    if (tid == bt) ++head;
+    if (lane == 0) { s_red[warp] = bv; s_redi[warp] = bi; }
+    __syncthreads();
+    bv = s_red[0]; bi = s_redi[0];
+    for (int w = 1; w < 8; ++w) if (better(s_red[w], s_redi[w], bv, bi)) { bv = s_red[w]; bi = s_redi[w]; }
     if (tid == 0) {
       const bool valid = bi != 0x7fffffff;
       out.idx[(size_t)r * kk + round] = valid ? bi : -1;
-      out.logp[(size_t)r * kk + round] = valid ? ((bv - s_max) - s_lse) : -INFINITY;
+      out.logp[(size_t)r * kk + round] = valid ? ((bv - rmax) - rlse) : -INFINITY;
     }
-    __syncthreads();
+    last_v = bv; last_i = bi;
   }
+}
+
+inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, cudaStream_t st) {
+  softmax_topk_kernel<<<rows, 256, 0, st>>>(logits, ld, V, kk, out);
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------------------
