@@ -172,9 +172,47 @@ __device__ __forceinline__ float planes_value(float x, int nt) {
 // ---- epilogues: called per (row, 16 consecutive columns) ------------------------------------
 __device__ __forceinline__ float sigmoid_tc(float x) { return 1.0f / (1.0f + expf(-1.0f * x)); }
 
+// Four consecutive values as bf16 planes with one 8-byte store per plane (idx a multiple of 4).
+__device__ __forceinline__ void split_store4(const Planes& pl, int nt, size_t idx, float x0, float x1, float x2, float x3) {
+  const float x[4] = {x0, x1, x2, x3};
+  float r[4];
+  __nv_bfloat16 b[4];
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    if (t < nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float src = (t == 0) ? x[i] : r[i];
+        b[i] = __float2bfloat16_rn(src);
+        r[i] = src - __bfloat162float(b[i]);
+      }
+      uint2 w;
+      w.x = (uint32_t)__bfloat16_as_ushort(b[0]) | ((uint32_t)__bfloat16_as_ushort(b[1]) << 16);
+      w.y = (uint32_t)__bfloat16_as_ushort(b[2]) | ((uint32_t)__bfloat16_as_ushort(b[3]) << 16);
+      *reinterpret_cast<uint2*>(pl.p[t] + idx) = w;
+    }
+  }
+}
+
+// Activation functions of the tensor-core path: exp through ex2.approx and the fast divide.
+// Absolute error ~1e-7, the size of an fp32 rounding of the result; the CUDA-core path keeps
+// the libm-accurate forms.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float ax = fabsf(x);
+  if (ax < 0.04f) {  // odd series where 1 - 2/(e^{2x}+1) would cancel
+    const float x2 = x * x;
+    return x * (1.0f - x2 * (0.33333334f - x2 * 0.13333334f));
+  }
+  const float e = __expf(2.0f * ax);
+  const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
+  return copysignf(t, x);
+}
+
 // LSTM cell update on gate-interleaved columns (see EpiLstm in gemm_simt.cuh for the math and
-// the reference kernels it replaces).  h goes out as bf16 planes to up to two places (the
-// operand panels that read it next) and optionally as fp32 (encoder top states).
+// the reference kernels it replaces).  A call covers 16 columns = 4 hidden units, so every
+// access is a 16-byte (fp32) or 8-byte (bf16 plane) vector.  h goes out as bf16 planes to up to
+// two places (the operand panels that read it next) and optionally as fp32 (encoder top states).
 struct TcEpiLstm {
   const float* bias;
   const float* c_prev; int ldc;
@@ -187,33 +225,40 @@ struct TcEpiLstm {
   int nt;
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
     const bool active = (row_len == nullptr) || (pos < row_len[row]);
+    const int j0 = col0 >> 2;
+    const size_t ic = (size_t)row * ldc + j0;
+    const float4 cp = *reinterpret_cast<const float4*>(c_prev + ic);
+    const size_t i1 = (size_t)row * h_out1.ld + h1_col0 + j0;
+    const size_t i2 = (size_t)row * h_out2.ld + h2_col0 + j0;
+    if (active) {
+      const float cpv[4] = {cp.x, cp.y, cp.z, cp.w};
+      float c[4], h[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = (col0 >> 2) + u;
-      const size_t ic = (size_t)row * ldc + j;
-      if (active) {
+      for (int u = 0; u < 4; ++u) {
         const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * u);
-        const float gi = sigmoid_tc(v[4 * u + 0] + b.x);
-        const float gf = sigmoid_tc(v[4 * u + 1] + b.y);
-        const float gg = tanhf(v[4 * u + 2] + b.z);
-        const float go = sigmoid_tc(v[4 * u + 3] + b.w);
-        const float c = gf * c_prev[ic] + gi * gg;
-        const float h = go * tanhf(c);
-        c_out[ic] = c;
-        split_store(h_out1, nt, (size_t)row * h_out1.ld + h1_col0 + j, h);
-        if (h_out2.p[0]) split_store(h_out2, nt, (size_t)row * h_out2.ld + h2_col0 + j, h);
-        if (h_f32) h_f32[(size_t)row * hf_row_stride + j] = planes_value(h, nt);
-      } else {
-        c_out[ic] = c_prev[ic];
-        const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j;
-#pragma unroll
-        for (int t = 0; t < 3; ++t)
-          if (t < nt) {
-            const __nv_bfloat16 hv = h_prev.p[t][ip];
-            h_out1.p[t][(size_t)row * h_out1.ld + h1_col0 + j] = hv;
-            if (h_out2.p[0]) h_out2.p[t][(size_t)row * h_out2.ld + h2_col0 + j] = hv;
-          }
+        const float gi = sigmoid_fast(v[4 * u + 0] + b.x);
+        const float gf = sigmoid_fast(v[4 * u + 1] + b.y);
+        const float gg = tanh_fast(v[4 * u + 2] + b.z);
+        const float go = sigmoid_fast(v[4 * u + 3] + b.w);
+        c[u] = gf * cpv[u] + gi * gg;
+        h[u] = go * tanh_fast(c[u]);
       }
+      *reinterpret_cast<float4*>(c_out + ic) = make_float4(c[0], c[1], c[2], c[3]);
+      split_store4(h_out1, nt, i1, h[0], h[1], h[2], h[3]);
+      if (h_out2.p[0]) split_store4(h_out2, nt, i2, h[0], h[1], h[2], h[3]);
+      if (h_f32)
+        *reinterpret_cast<float4*>(h_f32 + (size_t)row * hf_row_stride + j0) =
+            make_float4(planes_value(h[0], nt), planes_value(h[1], nt), planes_value(h[2], nt), planes_value(h[3], nt));
+    } else {
+      *reinterpret_cast<float4*>(c_out + ic) = cp;
+      const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j0;
+#pragma unroll
+      for (int t = 0; t < 3; ++t)
+        if (t < nt) {
+          const uint2 hv = *reinterpret_cast<const uint2*>(h_prev.p[t] + ip);
+          *reinterpret_cast<uint2*>(h_out1.p[t] + i1) = hv;
+          if (h_out2.p[0]) *reinterpret_cast<uint2*>(h_out2.p[t] + i2) = hv;
+        }
     }
   }
 };
@@ -224,9 +269,13 @@ struct TcEpiBiasTanh {
   Planes out; int col_off;
   int nt;
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+    const size_t idx = (size_t)row * out.ld + col_off + col0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-      split_store(out, nt, (size_t)row * out.ld + col_off + col0 + i, tanhf(v[i] + bias[col0 + i]));
+    for (int q = 0; q < 4; ++q) {
+      const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
+      split_store4(out, nt, idx + 4 * q, tanh_fast(v[4 * q] + b.x), tanh_fast(v[4 * q + 1] + b.y),
+                   tanh_fast(v[4 * q + 2] + b.z), tanh_fast(v[4 * q + 3] + b.w));
+    }
   }
 };
 
@@ -244,7 +293,7 @@ struct TcEpiF32 {
         const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
         r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
       }
-      if (col0 < split) { r.x = tanhf(r.x); r.y = tanhf(r.y); r.z = tanhf(r.z); r.w = tanhf(r.w); }
+      if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
       *reinterpret_cast<float4*>(o + 4 * q) = r;
     }
   }

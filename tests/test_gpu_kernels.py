@@ -44,3 +44,18 @@ def test_softmax_topk_ties_lowest_index(oracle, cuda_lib):
     assert idx[0].tolist() == list(range(kk))
     assert idx[1].tolist() == [5, 17000, 17001, 29999] + list(range(0, 5)) + list(range(6, 10))
     assert (idx == ridx).all()
+
+
+@pytest.mark.parametrize("R,K,N", [(12, 128, 512), (72, 1000, 30000), (768, 3000, 4000), (131, 257, 391)])
+@pytest.mark.parametrize("path,prec,tol", [("tensor", "fp32", 1e-6), ("tensor2", "fp32", 4e-6), ("tensor", "bf16", 4e-3)])
+def test_gemm_tensor_vs_checker(oracle, cuda_lib, R, K, N, path, prec, tol):
+    """tcgen05 GEMM on bf16 planes against a float64 product: three planes give the error of an
+    fp32 FMA loop, two planes ~2^-17 per product, one plane is plain bf16."""
+    from linmt_b200 import decoder
+    rng = np.random.default_rng(R + K + N)
+    X = rng.uniform(-1, 1, (R, K)).astype(np.float32)
+    W = rng.uniform(-0.08, 0.08, (K, N)).astype(np.float32)
+    Y = decoder.k_gemm(X, W, path, prec)
+    ref = X.astype(np.float64) @ W.astype(np.float64)
+    scale = np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64)
+    assert (np.abs(Y - ref) <= tol * scale + 1e-7).all(), float((np.abs(Y - ref) / scale).max())
