@@ -188,6 +188,22 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
 int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
                       float* ms_out, int32_t device);
 
+/* Y[R][N] = X[R][K] . Wt[N][K]^T on the tensor-core kernel (three bf16 planes, fp32-class
+ * result) WITHOUT allocating: for hosts that cannot call cudaMalloc once they are running --
+ * processes that gave the whole GPU to their own memory pool at start-up, or that share the
+ * device and must not trigger the device-wide stall an allocation can cause.  It has no
+ * counterpart in the reference.
+ *   d_x, d_wt, d_y  DEVICE pointers, fp32, row-major; K a multiple of 32, N a multiple of 16.
+ *   Limits: R <= 256, K <= 1024, N <= 1024 (LINMT_ELIMIT beyond): the kernel's working memory
+ *   (the bf16 planes of both operands, 7.5 MiB) is a fixed array inside the library that every
+ *   GPU loading the library holds until exit.
+ * The first call on a device looks that array's address up (cudaGetSymbolAddress); make it
+ * before any stream capture.  Work is issued on the default stream and the call returns when
+ * the result is in d_y.  All calls share the one array and it keeps the last call's contents:
+ * two calls that overlap on the GPU (from two threads, say) race -- serialise them. */
+int linmt_gemm_f32_noalloc(const float* d_x, const float* d_wt, float* d_y, int32_t R, int32_t K, int32_t N,
+                           int32_t device);
+
 #ifdef __cplusplus
 }
 #endif

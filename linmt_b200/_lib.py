@@ -35,7 +35,7 @@ class StatsC(C.Structure):
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",
            "linmt_create_from_weights", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
            "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
-           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time"]
+           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc"]
 
 _lib = None
 
@@ -79,5 +79,6 @@ def load():
     lib.linmt_k_softmax_topk.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int32]
     lib.linmt_k_gemm_time.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_float), C.c_int32]
+    lib.linmt_gemm_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     _lib = lib
     return lib

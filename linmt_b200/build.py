@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblinmt_decoder.so")
-SOURCES = ["engine.cu", "engine_tc.cu", "frontend.cu", "kernel_entry.cu"]
+SOURCES = ["engine.cu", "engine_tc.cu", "frontend.cu", "kernel_entry.cu", "noalloc_entry.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fopenmp,-O3", "--use_fast_math=false"]
 
