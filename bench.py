@@ -32,7 +32,7 @@ METRIC = "decoded target tokens/sec, beam 12, 4x1000 LSTM"
 UNIT = "tokens/s"
 FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
 # DRAM bytes of one vocabulary-GEMM launch from an ncu capture (see profiles/); None = not captured
-VOCAB_GEMM_TRAFFIC_BYTES = None
+VOCAB_GEMM_TRAFFIC_BYTES = 259.5e6  # dram read 191.4 MB + write 68.1 MB, profiles/vocab_gemm_tensor_path_C2.md (tensor path, 768 rows)
 
 
 def workload(rank: int):
@@ -47,7 +47,7 @@ def clocks_start():
          "clocks_event_reasons.sw_power_cap")
     f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
     try:
-        p = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200"],
+        p = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
                              stdout=f, stderr=subprocess.DEVNULL)
     except OSError:
         return None, f.name
@@ -90,6 +90,15 @@ def peaks():
         return FALLBACK_TFLOPS, "fallback"
 
 
+def host_threads() -> int:
+    """Threads the CPU legs use: every core this process may run on (launchers such as torchrun
+    set OMP_NUM_THREADS=1, which would otherwise serialise the CPU port)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def emitted_tokens(out_len: np.ndarray) -> int:
     return int(np.maximum(out_len[:, 0] - 2, 0).sum())
 
@@ -102,11 +111,12 @@ def cpu_leg(c, blob, sents, n_sample: int, threads: int = 0, repeat: int = 1):
     best = None
     for _ in range(repeat):
         t0 = time.perf_counter()
-        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta, threads=threads)
+        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                             threads=threads or host_threads())
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     toks = emitted_tokens(o["len"])
-    return toks / best, best, sub.n, oracle_py.lib().linmt_oracle_threads()
+    return toks / best, best, sub.n, threads or host_threads()
 
 
 def run_reference(args):
@@ -122,7 +132,8 @@ def run_reference(args):
     sub = sents.subset(range(n_sample))
     for i in range(args.warmup + args.steps):
         t0 = time.perf_counter()
-        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta)
+        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                             threads=host_threads())
         dt = time.perf_counter() - t0
         if i >= args.warmup:
             times.append(dt)
@@ -132,7 +143,7 @@ def run_reference(args):
     steps_done = len(times)
     ms = 1e3 * sum(times) / steps_done
     value = toks / (ms / 1e3)
-    cores = oracle_py.lib().linmt_oracle_threads()
+    cores = host_threads()
     sample = f"first {n_sample} of the 64 sentences of the batch per step, rows = {n_sample}*12, all host threads"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps_done,
@@ -278,7 +289,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor", "tensor2"])

@@ -170,7 +170,6 @@ __device__ __forceinline__ float planes_value(float x, int nt) {
 }
 
 // ---- epilogues: called per (row, 16 consecutive columns) ------------------------------------
-__device__ __forceinline__ float sigmoid_tc(float x) { return 1.0f / (1.0f + expf(-1.0f * x)); }
 
 // Four consecutive values as bf16 planes with one 8-byte store per plane (idx a multiple of 4).
 __device__ __forceinline__ void split_store4(const Planes& pl, int nt, size_t idx, float x0, float x1, float x2, float x3) {
@@ -194,20 +193,10 @@ __device__ __forceinline__ void split_store4(const Planes& pl, int nt, size_t id
   }
 }
 
-// Activation functions of the tensor-core path: exp through ex2.approx and the fast divide.
-// Absolute error ~1e-7, the size of an fp32 rounding of the result; the CUDA-core path keeps
-// the libm-accurate forms.
-__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
-__device__ __forceinline__ float tanh_fast(float x) {
-  const float ax = fabsf(x);
-  if (ax < 0.04f) {  // odd series where 1 - 2/(e^{2x}+1) would cancel
-    const float x2 = x * x;
-    return x * (1.0f - x2 * (0.33333334f - x2 * 0.13333334f));
-  }
-  const float e = __expf(2.0f * ax);
-  const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
-  return copysignf(t, x);
-}
+// Activation functions: the libm-accurate forms, as on the CUDA-core path (the approximate
+// ex2/rcp forms were measured to save only ~2% of a decode).
+__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float tanh_fast(float x) { return tanhf(x); }
 
 // LSTM cell update on gate-interleaved columns (see EpiLstm in gemm_simt.cuh for the math and
 // the reference kernels it replaces).  A call covers 16 columns = 4 hidden units, so every
