@@ -45,6 +45,7 @@ constexpr int A_BYTES = BM * BK * 2;         // one plane of the A tile of a sta
 constexpr int SMEM_BUDGET = 222 * 1024;
 constexpr int TMEM_COLS = 512;         // two accumulators of up to 256 columns each
 constexpr int kMaxStages = 8;
+constexpr int kDrainEvery = 2;         // k-blocks of the leading product per TMEM partial sum (see kernel)
 
 struct Shape {
   int bn;        // tile width
@@ -71,6 +72,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -307,10 +311,10 @@ static_assert(prod_a(2, 0) == 1 && prod_b(2, 0) == 1 && prod_a(2, 1) == 1 && pro
 
 // Polite bounded wait for the warps that have nothing to do until the accumulator is ready:
 // sleeping between polls leaves the issue slots to the TMA and MMA threads.
-__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned ns = 256) {
   const unsigned long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    __nanosleep(256);
+    __nanosleep(ns);
     if (*abort_flag) return false;
     if ((unsigned long long)clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
   }
@@ -330,18 +334,22 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   const int B_BYTES = BN * BK * 2;
   const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
   const uint32_t bars = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], accum
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 3));
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
   const int nkb = K / BK;
   const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+  const uint32_t main_full = accum_bar + 8u, main_free = accum_bar + 16u;
+  const int ndrain = (nkb + kDrainEvery - 1) / kDrainEvery;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
     mbar_init(accum_bar, 1);
+    mbar_init(main_full, 1);
+    mbar_init(main_free, 8);  // one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -379,28 +387,34 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         tc_fence_after();
         const uint64_t a0 = make_desc(st);                        // plane 0 of A, k-step 0
         const uint64_t b0 = make_desc(st + NT * A_BYTES);         // plane 0 of B, k-step 0
-        const uint32_t acc_old = kb ? 1u : 0u;
-        // Two passes over the stage, each into one accumulator; the order alternates per k-block
-        // (even: leading then small, odd: small then leading) so that consecutive blocks continue
-        // in the accumulator the previous one ended with.
+        if (NP == 1) {
+          // plain bf16: one accumulation chain
 #pragma unroll
-        for (int pass = 0; pass < (NP > 1 ? 2 : 1); ++pass) {
-          const bool lead = (NP == 1) || (pass == (kb & 1));
-          if (lead) {
+          for (int ks = 0; ks < BK / UMMA_K; ++ks)
+            umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (kb | ks) ? 1u : 0u);
+        } else {
+          // small cross terms: one long chain in accumulator 1
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks)
-              umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (ks ? 1u : acc_old));
-          } else {
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-#pragma unroll
-              for (int p = 0; p < NP - 1; ++p) {
-                const uint64_t ad = a0 + (uint64_t)(((prod_a(NT, p) * A_BYTES) >> 4) + ks * 2);
-                const uint64_t bd = b0 + (uint64_t)prod_b(NT, p) * bstep + (uint64_t)(ks * 2);
-                umma_bf16(acc1, ad, bd, idesc, ((ks | p) ? 1u : acc_old));
-              }
+            for (int p = 0; p < NP - 1; ++p) {
+              const uint64_t ad = a0 + (uint64_t)(((prod_a(NT, p) * A_BYTES) >> 4) + ks * 2);
+              const uint64_t bd = b0 + (uint64_t)prod_b(NT, p) * bstep + (uint64_t)(ks * 2);
+              umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
             }
           }
+          // leading product: accumulator 0 holds only kDrainEvery k-blocks at a time; the epilogue
+          // warps add each partial sum into registers and hand the accumulator back
+          const int in_chunk = kb % kDrainEvery;
+          if (in_chunk == 0 && kb > 0) {
+            const int d = kb / kDrainEvery;  // this chunk; the previous one must have been drained
+            if (!mbar_wait(main_free, (uint32_t)((d - 1) & 1), &s_abort)) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks)
+            umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (in_chunk | ks) ? 1u : 0u);
+          if (in_chunk == kDrainEvery - 1 || kb == nkb - 1) umma_commit(main_full);
         }
         umma_commit(eb);
         st += STAGE_BYTES; fb += 8u; eb += 8u;
@@ -415,20 +429,58 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     const int half = (warp - 2) >> 2;
     const int row = m0 + q * 32 + lane;
     const uint32_t astride = (uint32_t)acc_stride(BN);
-    if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
-      tc_fence_after();
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16);
+    if (NP == 1) {
+      if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
+        tc_fence_after();
 #pragma unroll 1
-      for (int c0 = half * 16; c0 < BN; c0 += 32) {
-        float v[16];
-        const uint32_t ta = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-        tmem_ld16(ta, v);
-        if (NP > 1) {
-          float sm[16];
-          tmem_ld16(ta + astride, sm);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += sm[i];
+        for (int c0 = half * 16; c0 < BN; c0 += 32) {
+          float v[16];
+          tmem_ld16(lane_base + (uint32_t)c0, v);
+          if (row < M && n0 + c0 < N) epi(row, n0 + c0, v);
         }
-        if (row < M && n0 + c0 < N) epi(row, n0 + c0, v);
+      }
+    } else {
+      // Two-level accumulation of the leading product: the tensor core rounds toward zero on
+      // every accumulate (measured: a bias of -0.5 ulp per MMA, growing with K), so its chain is
+      // kept to kDrainEvery k-blocks and the partial sums are added here in fp32 round-to-nearest.
+      float macc[8][16];
+#pragma unroll
+      for (int ci = 0; ci < 8; ++ci)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) macc[ci][i] = 0.f;
+      bool ok = true;
+      for (int d = 0; d < ndrain && ok; ++d) {
+        ok = mbar_wait_sleepy(main_full, (uint32_t)(d & 1), &s_abort, d == 0 ? 256 : 64);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) {
+          const int c0 = half * 16 + ci * 32;
+          if (c0 < BN) {
+            float w[16];
+            tmem_ld16(lane_base + (uint32_t)c0, w);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) macc[ci][i] += w[i];
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(main_free);
+      }
+      if (ok && mbar_wait(accum_bar, 0, &s_abort)) {
+        tc_fence_after();
+#pragma unroll
+        for (int ci = 0; ci < 8; ++ci) {
+          const int c0 = half * 16 + ci * 32;
+          if (c0 < BN) {
+            float sm[16];
+            tmem_ld16(lane_base + astride + (uint32_t)c0, sm);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) macc[ci][i] += sm[i];
+            if (row < M && n0 + c0 < N) epi(row, n0 + c0, macc[ci]);
+          }
+        }
       }
     }
   }
