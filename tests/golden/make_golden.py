@@ -3,8 +3,10 @@ built or run, and ships neither a model nor expected outputs).  Run from the rep
 
     python tests/golden/make_golden.py
 
-Writes tests/golden/c1_greedy.npz, c1_beam4.npz and tiny_global.npz: inputs are regenerated
-from seeds by linmt_b200.synth, the files hold the expected outputs."""
+Writes tests/golden/c1_greedy.npz, c1_beam4.npz and tiny_global.npz, and (about a minute of
+CPU) c2_batch64.npz, the final hypotheses of the whole 64-sentence reference decode
+configuration: inputs are regenerated from seeds by linmt_b200.synth, the files hold the
+expected outputs."""
 import os
 import sys
 
@@ -35,6 +37,11 @@ def main():
                             surv_score=o["surv_score"], cand_tok=o["cand_tok"], cand_logp=o["cand_logp"],
                             final_logp=o["final_logp"])
         print(name, o["len"][:, 0].tolist())
+    c2 = synth.configs()["C2"]
+    o = oracle_py.decode(c2.desc, [c2.blobs()[0]], c2.sentences(), beam=c2.beam, nbest=1, lp_alpha=c2.lp_alpha,
+                         cp_beta=c2.cp_beta)
+    np.savez_compressed(os.path.join(HERE, "c2_batch64.npz"), tok=o["tok"], len=o["len"], score=o["score"])
+    print("c2_batch64", o["len"][:, 0].tolist())
 
 
 if __name__ == "__main__":
