@@ -91,9 +91,9 @@ class Engine {
   int pack_model(const float* blob, DevModel& m);
   int alloc_state(DevState& s);
   int run_encoder(int n, int Smax);
-  int run_decoder_step(int t, int rows);
+  int run_decoder_step(int mi, int t, int rows);
   int run_encoder_tc(int n, int Smax);
-  int run_decoder_step_tc(int t, int rows);
+  int run_decoder_step_tc(int mi, int t, int rows);
   int step_tail(int t, int rows);
   int alloc_state_tc(TcState& s);
   int alloc_planes(tc::Planes& p, size_t rows, int ld);
@@ -101,10 +101,11 @@ class Engine {
   const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K);
   const CUtensorMap* b_maps(const tc::Planes& p, int rows, int K, int bn);
   template <class Epi>
-  int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e);
+  int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt = 0);
 
   bool use_tc_ = false;
   int nt_ = 3;
+  int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)
   int n_sm_ = 148;
   int* d_tc_err_ = nullptr;
   std::vector<TcState> tc_states_;
@@ -112,7 +113,6 @@ class Engine {
 
   const int32_t* cur_ids_ = nullptr;
   TraceDev trace_dev_{};
-  std::vector<float*> enc_final_h_, enc_final_c_;
   int enc_final_buf_ = 0;
   size_t out_cap_maxlen_ = 0;
   std::vector<DevModel> models_;
@@ -128,6 +128,7 @@ class Engine {
   float* d_score_ = nullptr;
   int32_t *d_fin_t_ = nullptr, *d_fin_b_ = nullptr, *d_fin_n_ = nullptr;
   float *d_fin_score_ = nullptr, *d_fin_final_ = nullptr;
+  float* d_combined_ = nullptr;  // [R][Vp] ensemble-combined log-values (n_models > 1)
   int32_t* d_cand_idx_ = nullptr;
   float *d_cand_logp_ = nullptr, *d_eos_logp_ = nullptr;
   // alignment records (print_info)

@@ -96,7 +96,8 @@ const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn) 
 
 // C[M][N] = A[:, a_col0 : a_col0+K] . W[N][K]^T with the tile width chosen for this shape.
 template <class Epi>
-int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e) {
+int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt) {
+  if (nt <= 0 || nt > nt_) nt = nt_;
   const int bn = tc::pick_bn(M, N, n_sm_);
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K);
   const CUtensorMap* bm = b_maps(W, N, K, bn);
@@ -104,7 +105,7 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   tc::TmapSet tm;
   std::memcpy(tm.a, am, sizeof(tm.a));
   std::memcpy(tm.b, bm, sizeof(tm.b));
-  CK(tc::launch_gemm_tc(tm, M, N, K, tc::make_shape(bn, nt_), e, d_tc_err_, stream));
+  CK(tc::launch_gemm_tc(tm, M, N, K, tc::make_shape(bn, nt), e, d_tc_err_, stream));
   LAUNCHED();
   return LINMT_OK;
 }
@@ -149,10 +150,10 @@ int Engine::run_encoder_tc(int n, int Smax) {
 }
 
 // One decoder forward, tensor-core path (see Engine::run_decoder_step).
-int Engine::run_decoder_step_tc(int t, int rows) {
-  DevModel& m = models_[0];
-  DevState& s = states_[0];
-  TcState& ts = tc_states_[0];
+int Engine::run_decoder_step_tc(int mi, int t, int rows) {
+  DevModel& m = models_[mi];
+  DevState& s = states_[mi];
+  TcState& ts = tc_states_[mi];
   const bool feed = desc.feed_input && t > 0;
   // where h_cur of layer l lives after its GEMM: the input slot of the consumer panel
   auto hcur_planes = [&](int l) -> const tc::Planes& { return (l + 1 < L) ? ts.panel[l + 1] : ts.panel_top; };
@@ -236,11 +237,11 @@ int Engine::run_decoder_step_tc(int t, int rows) {
       e0 = gemm_ev_[gemm_ev_used_++]; e1 = gemm_ev_[gemm_ev_used_++];
       CK(cudaEventRecord(e0, stream));
     }
-    int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e);
+    int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e, nt_vocab_);
     if (rc) return rc;
     if (kernel_timing) CK(cudaEventRecord(e1, stream));
   }
-  return step_tail(t, rows);
+  return LINMT_OK;
 }
 
 }  // namespace linmt

@@ -259,7 +259,8 @@ __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { ret
 // then ranked exactly.  If more elements than the candidate buffer holds reach the threshold
 // (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
 constexpr int kTopkCap = 1024;
-static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out) {
+static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
+                                                                  int normalise) {
   __shared__ float s_tmax[256];
   __shared__ float s_cv[kTopkCap];
   __shared__ int s_ci[kTopkCap];
@@ -315,7 +316,7 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   if (tid == 0) {
     float bs = 0.f;
     for (int w = 0; w < 8; ++w) bs += s_red[w];
-    s_lse = logf(bs);
+    s_lse = normalise ? logf(bs) : -rmax;   // normalise = 0: the row already holds log-probabilities
     if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
   }
   __syncthreads();
@@ -370,9 +371,59 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   }
 }
 
-inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, cudaStream_t st) {
-  softmax_topk_kernel<<<rows, 256, 0, st>>>(logits, ld, V, kk, out);
+inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, int normalise,
+                                       cudaStream_t st) {
+  softmax_topk_kernel<<<rows, 256, 0, st>>>(logits, ld, V, kk, out, normalise);
   return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// Ensemble of up to 8 members for one row: out[v] = log(mean_m softmax(z_m)[v]) (mode 0, the
+// reference's rule, src/decoder.h:1913-1921 -- its renormalisation, :1923-1931, is the
+// log-softmax the next kernel applies to this row) or mean_m log softmax(z_m)[v] (mode 1).
+// grid = rows, block = 256
+struct EnsembleRows {
+  const float* logits[8];
+  int n;
+};
+static __global__ void __launch_bounds__(256) ensemble_combine_kernel(EnsembleRows er, int ld, int V, int mode, float* __restrict__ out) {
+  __shared__ float s_red[8];
+  __shared__ float s_max[8], s_lse[8];
+  const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int m = 0; m < er.n; ++m) {
+    const float* z = er.logits[m] + (size_t)r * ld;
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, z[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = s_red[0];
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int i = tid; i < V; i += 256) sum += expf(z[i] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) s_red[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += s_red[w];
+      s_max[m] = mx; s_lse[m] = logf(t);
+    }
+    __syncthreads();
+  }
+  float* o = out + (size_t)r * ld;
+  for (int i = tid; i < V; i += 256) {
+    double acc = 0.0;
+    for (int m = 0; m < er.n; ++m) {
+      const float lp = (er.logits[m][(size_t)r * ld + i] - s_max[m]) - s_lse[m];
+      acc += (mode == 0) ? (double)expf(lp) : (double)lp;
+    }
+    acc /= er.n;
+    o[i] = (mode == 0) ? logf((float)acc) : (float)acc;
+  }
 }
 
 // ---------------------------------------------------------------------------------------

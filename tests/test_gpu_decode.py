@@ -246,3 +246,30 @@ def test_c2_whole_batch_against_golden(cuda_lib, gemm_path, min_identical):
     again = dec.decode(sents)
     assert (again["tok"] == out["tok"]).all() and (again["score"] == out["score"]).all()
     dec.close()
+
+
+@pytest.mark.parametrize("mode", ["prob_mean", "logprob_mean"])
+@pytest.mark.parametrize("gemm_path", ["tensor", "simt"])
+def test_ensemble_of_three(oracle, cuda_lib, c1, mode, gemm_path):
+    """Three independently seeded members (EnsembleFactory::EnsemblesModels, src/decoder.h:1910-1931):
+    mean of probabilities renormalised (the reference's rule) and mean of log-probabilities."""
+    from linmt_b200 import decoder
+    c, blob, sents = c1
+    blobs = [blob, synth.make_blob(c.desc, 21), synth.make_blob(c.desc, 22)]
+    kw = dict(beam=4, nbest=2, cp_beta=0.0, ensemble=mode)
+    o = oracle.decode(c.desc, blobs, sents, trace=True, **kw)
+    dec = decoder.Decoder(c.desc, blobs, max_batch=8, max_src_len=32, max_steps=64, gemm_path=gemm_path, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad, skipped, compared)
+    np.testing.assert_allclose(forced["final_logp"], o["final_logp"], rtol=RTOL_FP32)
+    free = dec.decode(sents)
+    assert token_identity(free, o, sents.n) >= 0.75
+    dec.close()
+    # a one-member "ensemble" of the reference's rule equals the plain decode
+    if mode == "prob_mean":
+        one = decoder.Decoder(c.desc, [blob, blob], max_batch=8, max_src_len=32, max_steps=64, gemm_path=gemm_path, **kw)
+        single = decoder.Decoder(c.desc, [blob], max_batch=8, max_src_len=32, max_steps=64, gemm_path=gemm_path, **kw)
+        a, b = one.decode(sents, trace=True), single.decode(sents, trace=True)
+        np.testing.assert_allclose(a["cand_logp"][:, 0, 0], b["cand_logp"][:, 0, 0], rtol=1e-5, atol=1e-5)
+        one.close(); single.close()
