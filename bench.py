@@ -35,10 +35,37 @@ FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
 VOCAB_GEMM_TRAFFIC_BYTES = 259.5e6  # dram read 191.4 MB + write 68.1 MB, profiles/vocab_gemm_tensor_path_C2.md (tensor path, 768 rows)
 
 
-def workload(rank: int):
-    c = synth.configs()["C2"]
-    sents = synth.make_sentences(c.n_sent, c.len_lo, c.len_hi, c.desc.Vs, c.zipf_s, c.seeds[0] + 7919 * rank, c.step_rule)
-    return c, sents
+WORKLOADS = {
+    # name: (per-rank batch size, scaling, description)
+    "C1": (8, "weak", "C1: 2x128 LSTM enc/dec, 1k/1k vocab, greedy, 8 sentences, S in [5,20], T=2S, fp32"),
+    "C2": (64, "weak", "C2: 4x1000 LSTM enc/dec, 30k/30k vocab, local-p general attention + feed-input, beam 12, "
+                       "64 sentences/batch, S in [10,50], T=floor(1.5S)+10, lp_alpha 0.65, fp32 weights"),
+    "C3": (128, "strong", "C3: C2's model in bf16 (fp32 accumulate), beam 12, 4096 sentences, S in [10,80], "
+                          "length-bucketed batches of 128 sharded over the GPUs"),
+    "C4": (128, "strong", "C4: 4x1024 LSTM, 80k/80k vocab, global dot attention + feed-input, bf16, beam 5, "
+                          "1024 sentences, S in [20,100], batches of 128 sharded over the GPUs"),
+    "C5": (64, "strong", "C5: ensemble of 4 models (seeds 10-13) of C2's shape, probabilities averaged (reference rule), "
+                         "beam 12, 512 sentences, S in [10,60], batches of 64 sharded over the GPUs"),
+}
+
+
+def workload(name: str, rank: int, world: int, precision=None):
+    """Returns (config, list of per-rank batches).  C1/C2 are weak-scaled (every rank decodes its
+    own batch of the named distribution); C3-C5 are the named fixed jobs, length-bucketed and
+    dealt to the ranks (strong scaling)."""
+    from linmt_b200 import shard
+    c = synth.configs()[name]
+    if precision:
+        c.precision = precision
+    batch, scaling, _ = WORKLOADS[name]
+    if scaling == "weak":
+        sents = synth.make_sentences(c.n_sent, c.len_lo, c.len_hi, c.desc.Vs, c.zipf_s, c.seeds[0] + 7919 * rank, c.step_rule)
+        return c, [sents]
+    allsents = c.sentences()
+    mine = shard.partition(allsents, world, batch)[rank]
+    sub = allsents.subset(mine)
+    batches = [sub.subset(b) for b in shard.batches_by_length(sub, batch)]
+    return c, batches
 
 
 def clocks_start():
@@ -103,7 +130,7 @@ def emitted_tokens(out_len: np.ndarray) -> int:
     return int(np.maximum(out_len[:, 0] - 2, 0).sum())
 
 
-def cpu_leg(c, blob, sents, n_sample: int, threads: int = 0, repeat: int = 1):
+def cpu_leg(c, blobs, sents, n_sample: int, threads: int = 0, repeat: int = 1, ensemble="prob_mean"):
     """Times the CPU checker (a port of the reference's math; the reference has no CPU path
     of its own) on the first n_sample sentences of the batch."""
     from oracle import oracle_py
@@ -111,7 +138,8 @@ def cpu_leg(c, blob, sents, n_sample: int, threads: int = 0, repeat: int = 1):
     best = None
     for _ in range(repeat):
         t0 = time.perf_counter()
-        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+        o = oracle_py.decode(c.desc, blobs, sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                             attention=c.attention, precision=c.precision, ensemble=ensemble,
                              threads=threads or host_threads())
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
@@ -123,7 +151,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    c, sents = workload(0)
+    c, batches = workload(args.workload, 0, 1)
+    sents = batches[0]
     blob = c.blobs()[0]
     n_sample = 8
     times = []
@@ -149,7 +178,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps_done,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": config_block(c, sents, args.gpus),
+        "config": config_block(c, sents, args.gpus, args.workload),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -159,11 +188,11 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def config_block(c, sents, n_gpus):
-    return {"workload": "C2: 4x1000 LSTM enc/dec, 30k/30k vocab, local-p general attention + feed-input, beam 12, "
-                        "64 sentences/batch, S in [10,50], T=floor(1.5S)+10, lp_alpha 0.65, fp32 weights",
-            "sentences_per_step_per_gpu": int(sents.n), "beam": c.beam,
-            "decoder_positions_per_step_per_gpu": int((sents.steps + 1).sum()),
+def config_block(c, sents, n_gpus, name="C2", n_batches=1, n_sent=None, positions=None):
+    return {"workload": WORKLOADS[name][2],
+            "sentences_per_step_per_gpu": int(n_sent if n_sent is not None else sents.n), "beam": c.beam,
+            "batches_per_step_per_gpu": n_batches,
+            "decoder_positions_per_step_per_gpu": int(positions if positions is not None else (sents.steps + 1).sum()),
             "l2": "inputs larger than L2 (>= 0.65 GB of weights streamed every decoder step)",
             "parallelism": f"replicas x{n_gpus}, sentence-sharded, no data-path collective"}
 
@@ -179,19 +208,25 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
-    c, sents = workload(rank)
-    blob = c.blobs()[0]
-    max_src = int(sents.lengths().max())
-    Tm = int(sents.steps.max())
+    name = args.workload
+    c, batches = workload(name, rank, world, args.precision)
+    blobs = c.blobs()
+    max_src = max(int(b.lengths().max()) for b in batches)
+    Tm = max(int(b.steps.max()) for b in batches)
     max_len = Tm + 2
-    dec = decoder.Decoder(c.desc, [blob], beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
-                          gemm_path=args.gemm_path, max_batch=sents.n, max_src_len=max(max_src, 64),
+    bmax = max(b.n for b in batches)
+    ensemble = c.extra.get("ensemble", "prob_mean")
+    dec = decoder.Decoder(c.desc, blobs, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                          attention=c.attention, precision=c.precision, ensemble=ensemble,
+                          gemm_path=args.gemm_path, max_batch=bmax, max_src_len=max(max_src, 64),
                           max_steps=max(Tm, 100), device=local)
     dev = torch.device("cuda", local)
-    d_ids = torch.from_numpy(sents.ids.astype(np.int32)).to(dev)
-    d_tok = torch.zeros((sents.n, 1, max_len), dtype=torch.int32, device=dev)
-    d_len = torch.zeros((sents.n, 1), dtype=torch.int32, device=dev)
-    d_score = torch.zeros((sents.n, 1), dtype=torch.float32, device=dev)
+    dbuf = []
+    for b in batches:
+        dbuf.append((torch.from_numpy(b.ids.astype(np.int32)).to(dev),
+                     torch.zeros((b.n, 1, max_len), dtype=torch.int32, device=dev),
+                     torch.zeros((b.n, 1), dtype=torch.int32, device=dev),
+                     torch.zeros((b.n, 1), dtype=torch.float32, device=dev)))
 
     def barrier():
         torch.cuda.synchronize()
@@ -200,8 +235,14 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     def step_device():
-        dec.decode_device(d_ids.data_ptr(), sents.off, sents.steps, max_len, d_tok.data_ptr(), d_len.data_ptr(), d_score.data_ptr())
-        return dec.stats()
+        """One pass over this rank's batches, ids and outputs resident in HBM."""
+        ms = gms = 0.0
+        gn = 0
+        for b, (d_ids, d_tok, d_len, d_score) in zip(batches, dbuf):
+            dec.decode_device(d_ids.data_ptr(), b.off, b.steps, max_len, d_tok.data_ptr(), d_len.data_ptr(), d_score.data_ptr())
+            st = dec.stats()
+            ms += st["last_decode_ms"]; gms += st["last_gemm_ms"]; gn += st["last_gemm_launches"]
+        return ms, gms, gn
 
     # ---- device-resident leg: `value` ----
     for _ in range(args.warmup):
@@ -213,71 +254,81 @@ def run_ours(args):
     dev_ms, gemm_ms, gemm_n = 0.0, 0.0, 0
     w0 = time.perf_counter()
     for _ in range(args.steps):
-        s = step_device()
-        dev_ms += s["last_decode_ms"]; gemm_ms += s["last_gemm_ms"]; gemm_n += s["last_gemm_launches"]
+        a, g, n = step_device()
+        dev_ms += a; gemm_ms += g; gemm_n += n
     barrier()
     wall_ms = 1e3 * (time.perf_counter() - w0)
     clocks = clocks_stop(clk_p, clk_path, local) if rank == 0 else None
     s1 = dec.stats()
     dec.set_kernel_timing(False)
     launches = s1["kernel_launches"] - s0["kernel_launches"]
-    toks = emitted_tokens(d_len.cpu().numpy())
+    toks = sum(emitted_tokens(d[2].cpu().numpy()) for d in dbuf)
     row_steps = s1["decoder_row_steps"] - s0["decoder_row_steps"]
 
     # ---- end-to-end leg through the public host API: pinned host buffers, copies inside ----
-    h_ids = torch.from_numpy(sents.ids.astype(np.int32)).pin_memory()
-    host_sents = synth.Sentences(h_ids.numpy(), sents.off, sents.steps)
+    hbatches, pins = [], []
+    for b in batches:
+        h_ids = torch.from_numpy(b.ids.astype(np.int32)).pin_memory()
+        pins.append(h_ids)
+        hbatches.append(synth.Sentences(h_ids.numpy(), b.off, b.steps))
+    outs = None
     for _ in range(min(args.warmup, 2)):
-        out = dec.decode(host_sents)
+        outs = [dec.decode(hb) for hb in hbatches]
     barrier()
     e0 = time.perf_counter()
-    e_dev_ms = 0.0
     for _ in range(args.steps):
-        out = dec.decode(host_sents)
-        e_dev_ms += dec.stats()["last_decode_ms"]
+        outs = [dec.decode(hb) for hb in hbatches]
     barrier()
     e2e_wall_ms = 1e3 * (time.perf_counter() - e0)
-    e_toks = emitted_tokens(out["len"])
-    h2d = int(sents.ids.nbytes + 4 * 4 * sents.n)
-    d2h = int(out["tok"].nbytes + out["len"].nbytes + out["score"].nbytes + out["vit"].nbytes)
+    e_toks = sum(emitted_tokens(o["len"]) for o in outs)
+    h2d = int(sum(b.ids.nbytes + 4 * 4 * b.n for b in batches))
+    d2h = int(sum(o["tok"].nbytes + o["len"].nbytes + o["score"].nbytes + o["vit"].nbytes for o in outs))
 
     # ---- reduce over ranks: max time, summed tokens ----
     vals = torch.tensor([dev_ms, wall_ms, e2e_wall_ms, gemm_ms], dtype=torch.float64, device=dev)
-    sums = torch.tensor([toks, e_toks, launches, row_steps, gemm_n], dtype=torch.float64, device=dev)
+    n_sent_local = sum(b.n for b in batches)
+    positions_local = int(sum(int((b.steps + 1).sum()) for b in batches))
+    sums = torch.tensor([toks, e_toks, launches, row_steps, gemm_n, n_sent_local], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
     dev_ms, wall_ms, e2e_wall_ms, gemm_ms_max = vals.tolist()
-    toks_all, e_toks_all, launches_all, row_steps_all, gemm_n_all = sums.tolist()
+    toks_all, e_toks_all, launches_all, row_steps_all, gemm_n_all, n_sent_all = sums.tolist()
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
         value = toks_all * args.steps / (dev_ms / 1e3)
         e2e_value = e_toks_all * args.steps / (e2e_wall_ms / 1e3)
-        # roofline of the dominant kernel (the vocabulary GEMM): algorithmic FLOPs = 2 * rows * H * V
+        # roofline of the dominant kernel (the vocabulary GEMM): algorithmic FLOPs = 2 * rows * H * V per member
         H, V = c.desc.H, c.desc.V
-        flops_local = 2.0 * (s1["decoder_row_steps"] - s0["decoder_row_steps"]) * H * V
+        flops_local = 2.0 * (s1["decoder_row_steps"] - s0["decoder_row_steps"]) * H * V * len(blobs)
         achieved = flops_local / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
         peak, peak_src = peaks()
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            v, secs, ns, cores = cpu_leg(c, blob, sents, 16)
+            v, secs, ns, cores = cpu_leg(c, blobs, batches[0], 16, ensemble=ensemble)
             cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"first {ns} of the {sents.n} sentences, batched (rows = {ns}*12), {secs:.1f} s of CPU work"}
+                   "sample": f"first {ns} sentences of the first batch, batched (rows = {ns}*{c.beam}), {secs:.1f} s of CPU work"}
+        scaling = WORKLOADS[name][1]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": config_block(c, sents, world),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "bf16" if c.precision == "bf16" else "f32", "data": "synthetic",
+            "config": config_block(c, batches[0], world, name, len(batches), n_sent_local, positions_local),
             "positions_per_s": row_steps_all / c.beam / (dev_ms / 1e3),
+            "sentences_per_step": int(n_sent_all),
             "wall_ms_per_step": wall_ms / args.steps,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_wall_ms / args.steps},
             "gpu_launches": int(launches_all),
             "roofline": {"bound": "tensor", "kernel": "vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": VOCAB_GEMM_TRAFFIC_BYTES,
+                         "frac": (achieved / peak) if achieved else None,
+                         "traffic": VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" else None,
                          "peak_source": peak_src, "launches": int(gemm_n),
-                         "avg_launch_ms": gemm_ms / max(gemm_n, 1)},
+                         "avg_launch_ms": gemm_ms / max(gemm_n, 1),
+                         "note": "achieved = algorithmic fp32 FLOPs; the fp32 path runs 4 bf16 partial products per "
+                                 "product in this kernel (6 in the recurrent GEMMs), the bf16 path 1"},
             "cpu_baseline": cpu, "clocks": clocks, "gemm_path": args.gemm_path,
         }
         print(json.dumps(line))
@@ -294,6 +345,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor", "tensor2"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
+    ap.add_argument("--precision", default=None, choices=["fp32", "bf16"], help="override the workload's precision")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

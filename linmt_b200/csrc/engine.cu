@@ -57,6 +57,9 @@ Engine::~Engine() {
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
   for (auto e : gemm_ev_) cudaEventDestroy(e);
+  for (auto& v : enc_events_) for (auto e : v) cudaEventDestroy(e);
+  if (enc_start_ev_) cudaEventDestroy(enc_start_ev_);
+  for (auto st : enc_streams_) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
   if (stream) cudaStreamDestroy(stream);
 }
 

@@ -104,6 +104,10 @@ class Engine {
   int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt = 0);
 
   bool use_tc_ = false;
+  // encoder wavefront: one stream per layer, a small ring of events per layer
+  std::vector<cudaStream_t> enc_streams_;
+  std::vector<std::vector<cudaEvent_t>> enc_events_;
+  cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)
   int n_sm_ = 148;

@@ -115,24 +115,46 @@ static tc::Planes no_planes() { return tc::Planes{}; }
 // Encoder, tensor-core path (see Engine::run_encoder for the reference procedure).  Panel of
 // layer l at position p: encp[p&1][l] = (input from below | h_prev).  The epilogue writes h to
 // the next position's h_prev slot and to the next layer's input slot of this position.
+//
+// (layer l, position p) depends on (l-1, p) and (l, p-1) only, and each launch fills about half
+// the SMs (64 rows = one row tile), so the layers run as a wavefront: one stream per layer,
+// events for the cross-layer edges.  Besides the true dependencies, (l, p) waits for (l+1, p-2),
+// the last reader of the double-buffered input slot it overwrites.
 int Engine::run_encoder_tc(int n, int Smax) {
+  constexpr int kRing = 4;
+  if (enc_streams_.empty()) {
+    enc_streams_.resize(L);
+    enc_events_.assign(L, std::vector<cudaEvent_t>(kRing));
+    for (int l = 0; l < L; ++l) {
+      CK(cudaStreamCreateWithFlags(&enc_streams_[l], cudaStreamNonBlocking));
+      for (int r = 0; r < kRing; ++r) CK(cudaEventCreateWithFlags(&enc_events_[l][r], cudaEventDisableTiming));
+    }
+    CK(cudaEventCreateWithFlags(&enc_start_ev_, cudaEventDisableTiming));
+  }
+  cudaStream_t main_stream = stream;
   for (int mi = 0; mi < n_models; ++mi) {
     DevModel& m = models_[mi];
     DevState& s = states_[mi];
     TcState& ts = tc_states_[mi];
     for (int l = 0; l < L; ++l) {
-      CK(cudaMemsetAsync(s.enc_c[0][l], 0, sizeof(float) * (size_t)B * Hp, stream));
+      CK(cudaMemsetAsync(s.enc_c[0][l], 0, sizeof(float) * (size_t)B * Hp, main_stream));
       for (int t = 0; t < nt_; ++t)  // h_prev = 0 at the first position
-        CK(cudaMemset2DAsync(ts.encp[0][l].p[t] + Hp, (size_t)2 * Hp * 2, 0, (size_t)Hp * 2, B, stream));
+        CK(cudaMemset2DAsync(ts.encp[0][l].p[t] + Hp, (size_t)2 * Hp * 2, 0, (size_t)Hp * 2, B, main_stream));
     }
-    for (int pos = 0; pos < Smax; ++pos) {
+    CK(cudaEventRecord(enc_start_ev_, main_stream));
+    for (int l = 0; l < L; ++l) CK(cudaStreamWaitEvent(enc_streams_[l], enc_start_ev_, 0));
+    int rc = LINMT_OK;
+    for (int pos = 0; pos < Smax && rc == LINMT_OK; ++pos) {
       const int in = pos & 1, out = in ^ 1;
-      {
-        dim3 grid(n, nt_);
-        enc_embed_planes_kernel<<<grid, 128, 0, stream>>>(cur_ids_, d_off_, d_len_, m.p_emb_src, desc.vocab_src, ts.encp[in][0], Hp, pos);
-        LAUNCHED();
-      }
-      for (int l = 0; l < L; ++l) {
+      for (int l = 0; l < L && rc == LINMT_OK; ++l) {
+        cudaStream_t sl = enc_streams_[l];
+        if (l > 0) CK(cudaStreamWaitEvent(sl, enc_events_[l - 1][pos % kRing], 0));
+        if (l + 1 < L && pos >= 2) CK(cudaStreamWaitEvent(sl, enc_events_[l + 1][(pos - 2) % kRing], 0));
+        if (l == 0) {
+          dim3 grid(n, nt_);
+          enc_embed_planes_kernel<<<grid, 128, 0, sl>>>(cur_ids_, d_off_, d_len_, m.p_emb_src, desc.vocab_src, ts.encp[in][0], Hp, pos);
+          LAUNCHED();
+        }
         tc::TcEpiLstm e{};
         e.bias = m.enc_b[l]; e.c_prev = s.enc_c[in][l]; e.ldc = Hp; e.c_out = s.enc_c[out][l];
         e.h_out1 = ts.encp[out][l]; e.h1_col0 = Hp;
@@ -141,10 +163,16 @@ int Engine::run_encoder_tc(int n, int Smax) {
         e.h_f32 = (l == L - 1) ? s.hs + (size_t)pos * Hp : nullptr;
         e.hf_row_stride = (long long)opt.max_src_len * Hp;
         e.row_len = d_len_; e.pos = pos; e.nt = nt_;
-        int rc = tc_gemm(ts.encp[in][l], 0, B, m.p_enc_w[l], n, 4 * Hp, 2 * Hp, e);
-        if (rc) return rc;
+        stream = sl;  // tc_gemm launches on the member stream
+        rc = tc_gemm(ts.encp[in][l], 0, B, m.p_enc_w[l], n, 4 * Hp, 2 * Hp, e);
+        stream = main_stream;
+        if (rc == LINMT_OK) CK(cudaEventRecord(enc_events_[l][pos % kRing], sl));
       }
     }
+    // the decoder (main stream) starts after the last launch of every layer
+    for (int l = 0; l < L; ++l)
+      if (Smax > 0) CK(cudaStreamWaitEvent(main_stream, enc_events_[l][(Smax - 1) % kRing], 0));
+    if (rc != LINMT_OK) return rc;
   }
   return LINMT_OK;
 }

@@ -45,7 +45,7 @@ constexpr int A_BYTES = BM * BK * 2;         // one plane of the A tile of a sta
 constexpr int SMEM_BUDGET = 222 * 1024;
 constexpr int TMEM_COLS = 512;         // two accumulators of up to 256 columns each
 constexpr int kMaxStages = 8;
-constexpr int kDrainEvery = 2;         // k-blocks of the leading product per TMEM partial sum (see kernel)
+constexpr int kDrainDefault = 4;       // k-blocks of the leading product per TMEM partial sum (see kernel)
 
 struct Shape {
   int bn;        // tile width
@@ -53,6 +53,7 @@ struct Shape {
   int stages;
   int stage_bytes;
   int smem_bytes;
+  int drain;     // k-blocks between drains of the leading accumulator
 };
 inline Shape make_shape(int bn, int nt) {
   Shape s;
@@ -61,6 +62,7 @@ inline Shape make_shape(int bn, int nt) {
   s.stages = SMEM_BUDGET / s.stage_bytes;
   if (s.stages > kMaxStages) s.stages = kMaxStages;
   s.smem_bytes = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  s.drain = kDrainDefault;
   return s;
 }
 
@@ -324,7 +326,7 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
 // ---- kernel -------------------------------------------------------------------------------
 template <int NT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, Epi epi,
+gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, int kDrainEvery, Epi epi,
                int* __restrict__ err_flag) {
   constexpr int NP = num_products(NT);
   extern __shared__ unsigned char smem_raw[];
@@ -360,20 +362,27 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   const uint32_t tmem_acc = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      int s = 0; uint32_t ph = 0;
-      uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
-      for (int kb = 0; kb < nkb; ++kb) {
-        if (!mbar_wait(eb, ph ^ 1u, &s_abort)) break;
-        mbar_expect_tx(fb, (uint32_t)STAGE_BYTES);
-        const int kx = kb * BK;
-#pragma unroll
-        for (int t = 0; t < NT; ++t) tma_load_2d(st + t * A_BYTES, &tm.a[t], kx, m0, fb);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) tma_load_2d(st + NT * A_BYTES + t * B_BYTES, &tm.b[t], kx, n0, fb);
-        st += STAGE_BYTES; fb += 8u; eb += 8u;
-        if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
+    // Producer.  A TMA instruction costs its issuing thread ~150 ns whatever the box size
+    // (measured), so the 2*NT boxes of a stage are issued by 2*NT lanes in one warp instruction:
+    // lane t < NT loads plane t of A, lane NT + t plane t of B.
+    const bool is_a = lane < NT;
+    const int t = is_a ? lane : lane - NT;
+    const CUtensorMap* map = reinterpret_cast<const CUtensorMap*>(&tm) + (is_a ? t : 3 + t);  // a[3] then b[3]
+    const uint32_t dst_off = is_a ? (uint32_t)(t * A_BYTES) : (uint32_t)(NT * A_BYTES + t * B_BYTES);
+    const int ycoord = is_a ? m0 : n0;
+    int s = 0; uint32_t ph = 0;
+    uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
+    for (int kb = 0; kb < nkb; ++kb) {
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(eb, ph ^ 1u, &s_abort) ? 1 : 0;
+        if (ok) mbar_expect_tx(fb, (uint32_t)STAGE_BYTES);
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < 2 * NT) tma_load_2d(st + dst_off, map, kb * BK, ycoord, fb);
+      st += STAGE_BYTES; fb += 8u; eb += 8u;
+      if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -536,7 +545,7 @@ inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, con
     attr_done = true;
   }
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn);
-  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, epi, err_flag);
+  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, sh.drain > 0 ? sh.drain : kDrainDefault, epi, err_flag);
   return cudaGetLastError();
 }
 template <class Epi>

@@ -103,6 +103,8 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
 // engine's own choice), nt planes and at most max_stages shared-memory stages (0 = all that fit).
 int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
                       float* ms_out, int32_t device) {
+  int drain = 0;
+  if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }  // tuning: hundreds digit = drain interval
   using namespace linmt;
   if (R < 1 || K < 32 || N < 16 || nt < 1 || nt > 3 || iters < 1 || !ms_out) return LINMT_EINVAL;
   if (K % 32 || N % 16) return LINMT_EINVAL;
@@ -125,6 +127,7 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
   }
   tc::Shape sh = tc::make_shape(bn, nt);
   if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
+  if (drain > 0) sh.drain = drain;
   tc::TcEpiF32 e{nullptr, dy.as<float>(), N, 0};
   cudaEvent_t e0, e1;
   KCK(cudaEventCreate(&e0)); KCK(cudaEventCreate(&e1));
