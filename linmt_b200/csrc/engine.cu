@@ -256,6 +256,11 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   CK(cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, o.device));
   DA(d_tc_err_, 1);
   CK(cudaMemset(d_tc_err_, 0, sizeof(int)));
+  if (use_tc_) {
+    DA(d_splitk_ws_, kSplitKWsFloats);
+    DA(d_splitk_counters_, kSplitKMaxTiles);
+    CK(cudaMemset(d_splitk_counters_, 0, sizeof(int) * kSplitKMaxTiles));
+  }
   models_.resize(nm); states_.resize(nm); tc_states_.resize(nm);
   for (int i = 0; i < nm; ++i) {
     int rc = pack_model(blobs[i], models_[i]);

@@ -112,6 +112,11 @@ class Engine {
   int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)
   int n_sm_ = 148;
   int* d_tc_err_ = nullptr;
+  float* d_splitk_ws_ = nullptr;      // split-K partial tiles
+  int* d_splitk_counters_ = nullptr;  // one arrival counter per output tile
+  static constexpr size_t kSplitKWsFloats = (size_t)16 << 20;  // 64 MiB
+  int ws_part_ = 0, ws_parts_ = 1;    // slice of the workspace a launch may use (concurrent encoder layers get one each)
+  static constexpr int kSplitKMaxTiles = 4096;
   std::vector<TcState> tc_states_;
   std::map<std::tuple<const void*, int, int, int, int>, std::array<CUtensorMap, 3>> tmap_cache_;
 

@@ -98,14 +98,20 @@ const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn) 
 template <class Epi>
 int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt) {
   if (nt <= 0 || nt > nt_) nt = nt_;
-  const int bn = tc::pick_bn(M, N, n_sm_);
+  int bn = 0, splits = 1;
+  const size_t ws_floats = kSplitKWsFloats / ws_parts_;
+  const int max_tiles = kSplitKMaxTiles / ws_parts_;
+  tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits);
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K);
   const CUtensorMap* bm = b_maps(W, N, K, bn);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
   tc::TmapSet tm;
   std::memcpy(tm.a, am, sizeof(tm.a));
   std::memcpy(tm.b, bm, sizeof(tm.b));
-  CK(tc::launch_gemm_tc(tm, M, N, K, tc::make_shape(bn, nt), e, d_tc_err_, stream));
+  tc::Shape sh = tc::make_shape(bn, nt);
+  sh.splits = splits;
+  CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,
+                        d_splitk_counters_ + ws_part_ * max_tiles));
   LAUNCHED();
   return LINMT_OK;
 }
@@ -163,9 +169,10 @@ int Engine::run_encoder_tc(int n, int Smax) {
         e.h_f32 = (l == L - 1) ? s.hs + (size_t)pos * Hp : nullptr;
         e.hf_row_stride = (long long)opt.max_src_len * Hp;
         e.row_len = d_len_; e.pos = pos; e.nt = nt_;
-        stream = sl;  // tc_gemm launches on the member stream
+        stream = sl;  // tc_gemm launches on the member stream, with this layer's slice of the split-K workspace
+        ws_part_ = l; ws_parts_ = L;
         rc = tc_gemm(ts.encp[in][l], 0, B, m.p_enc_w[l], n, 4 * Hp, 2 * Hp, e);
-        stream = main_stream;
+        stream = main_stream; ws_part_ = 0; ws_parts_ = 1;
         if (rc == LINMT_OK) CK(cudaEventRecord(enc_events_[l][pos % kRing], sl));
       }
     }

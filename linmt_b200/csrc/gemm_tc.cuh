@@ -54,6 +54,7 @@ struct Shape {
   int stage_bytes;
   int smem_bytes;
   int drain;     // k-blocks between drains of the leading accumulator
+  int splits;    // split-K factor (1 = none)
 };
 inline Shape make_shape(int bn, int nt) {
   Shape s;
@@ -63,6 +64,7 @@ inline Shape make_shape(int bn, int nt) {
   if (s.stages > kMaxStages) s.stages = kMaxStages;
   s.smem_bytes = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
   s.drain = kDrainDefault;
+  s.splits = 1;
   return s;
 }
 
@@ -327,7 +329,7 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
 template <int NT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, int kDrainEvery, Epi epi,
-               int* __restrict__ err_flag) {
+               int* __restrict__ err_flag, int splits, float* __restrict__ ws, int* __restrict__ tile_counters) {
   constexpr int NP = num_products(NT);
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -341,7 +343,10 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
-  const int nkb = K / BK;
+  // split-K: this CTA covers k-blocks [kb0, kb0 + nkb) of the K / BK blocks
+  const int nkb_total = K / BK;
+  const int kb0 = (int)((long long)nkb_total * blockIdx.z / splits);
+  const int nkb = (int)((long long)nkb_total * (blockIdx.z + 1) / splits) - kb0;
   const uint32_t accum_bar = bars + 8u * (2 * STAGES);
   const uint32_t main_full = accum_bar + 8u, main_free = accum_bar + 16u;
   const int ndrain = (nkb + kDrainEvery - 1) / kDrainEvery;
@@ -380,7 +385,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      if (lane < 2 * NT) tma_load_2d(st + dst_off, map, kb * BK, ycoord, fb);
+      if (lane < 2 * NT) tma_load_2d(st + dst_off, map, (kb0 + kb) * BK, ycoord, fb);
       st += STAGE_BYTES; fb += 8u; eb += 8u;
       if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
     }
@@ -439,6 +444,18 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     const int row = m0 + q * 32 + lane;
     const uint32_t astride = (uint32_t)acc_stride(BN);
     const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16);
+    // with split-K the tile's partial sum goes to the workspace; the last CTA of the tile adds them up
+    float* wrow = ws ? ws + ((size_t)blockIdx.z * ((size_t)gridDim.x * BM) + (size_t)row) * (size_t)N : nullptr;
+    auto emit = [&](int c0, const float* v) {
+      if (row < M && n0 + c0 < N) {
+        if (splits == 1) epi(row, n0 + c0, v);
+        else {
+          float4* dst = reinterpret_cast<float4*>(wrow + n0 + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+      }
+    };
     if (NP == 1) {
       if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
         tc_fence_after();
@@ -446,7 +463,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         for (int c0 = half * 16; c0 < BN; c0 += 32) {
           float v[16];
           tmem_ld16(lane_base + (uint32_t)c0, v);
-          if (row < M && n0 + c0 < N) epi(row, n0 + c0, v);
+          emit(c0, v);
         }
       }
     } else {
@@ -487,16 +504,52 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
             tmem_ld16(lane_base + astride + (uint32_t)c0, sm);
 #pragma unroll
             for (int i = 0; i < 16; ++i) macc[ci][i] += sm[i];
-            if (row < M && n0 + c0 < N) epi(row, n0 + c0, macc[ci]);
+            emit(c0, macc[ci]);
           }
         }
       }
     }
   }
+  if (splits > 1) __threadfence();  // partial sums visible before this CTA takes its ticket
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_acc, TMEM_COLS);
   if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
+  if (splits > 1) {
+    // The CTA that arrives last at this tile sums the partial tiles in split order (a fixed
+    // order: results do not depend on which CTA that is) and runs the fused epilogue.
+    __shared__ int s_last;
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0) {
+      const int ticket = atomicAdd(&tile_counters[tile], 1);
+      s_last = (ticket == splits - 1) ? 1 : 0;
+      if (s_last) tile_counters[tile] = 0;  // ready for the next launch
+      __threadfence();
+    }
+    __syncthreads();
+    if (s_last && warp >= 2) {
+      const int q = warp & 3, half = (warp - 2) >> 2;
+      const int row = m0 + q * 32 + lane;
+      if (row < M) {
+        const size_t zstride = (size_t)gridDim.x * BM * (size_t)N;
+        const float* p0 = ws + (size_t)row * (size_t)N + n0;
+        for (int c0 = half * 16; c0 < BN && n0 + c0 < N; c0 += 32) {
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+          for (int z = 0; z < splits; ++z) {
+            const float4* src = reinterpret_cast<const float4*>(p0 + (size_t)z * zstride + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 t = __ldcg(src + i);
+              v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
+            }
+          }
+          epi(row, n0 + c0, v);
+        }
+      }
+    }
+  }
 }
 
 // ---- fp32 -> bf16 planes ---------------------------------------------------------------------
@@ -537,23 +590,25 @@ inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows,
 
 template <int NT, class Epi>
 inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
-                                     cudaStream_t st) {
+                                     cudaStream_t st, float* ws, int* counters) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
-  dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn);
-  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, sh.drain > 0 ? sh.drain : kDrainDefault, epi, err_flag);
+  const int splits = (sh.splits > 1 && ws && counters) ? sh.splits : 1;
+  dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
+  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, sh.drain > 0 ? sh.drain : kDrainDefault, epi, err_flag,
+                                                                  splits, splits > 1 ? ws : nullptr, counters);
   return cudaGetLastError();
 }
 template <class Epi>
 inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
-                                  cudaStream_t st) {
-  if (sh.nt == 3) return launch_gemm_tc_nt<3, Epi>(tm, M, N, K, sh, epi, err_flag, st);
-  if (sh.nt == 2) return launch_gemm_tc_nt<2, Epi>(tm, M, N, K, sh, epi, err_flag, st);
-  return launch_gemm_tc_nt<1, Epi>(tm, M, N, K, sh, epi, err_flag, st);
+                                  cudaStream_t st, float* ws = nullptr, int* counters = nullptr) {
+  if (sh.nt == 3) return launch_gemm_tc_nt<3, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  if (sh.nt == 2) return launch_gemm_tc_nt<2, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  return launch_gemm_tc_nt<1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
 }
 
 // Tile width that fills the SMs best for an M x N problem: the smallest makespan
@@ -571,6 +626,34 @@ inline int pick_bn(int M, int N, int n_sm) {
     if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
   }
   return best;
+}
+
+// Tile width AND split-K factor from a small cost model (times in ns per k-block, measured):
+// a k-block costs the larger of the issuing thread's time (~58 ns per MMA, whatever its width)
+// and the tensor pipe's (128 x bn x 16 MACs at 4096 MAC/clk); a launch takes
+// waves * (k-blocks-per-CTA of those + ~8-13 us of prologue/epilogue per tile), plus the cost of
+// writing and re-reading partial tiles when K is split (only worth it for tiles up to 176 wide).
+// ws_floats bounds the split-K workspace (splits * padded rows * N floats).
+inline void pick_shape(int M, int N, int K, int nt, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out) {
+  const int mt = (M + BM - 1) / BM;
+  const int nkb = K / BK;
+  const int np = num_products(nt);
+  double best = 1e30;
+  int best_bn = 256, best_s = 1;
+  for (int bn = 256; bn >= 48; bn -= 16) {
+    const long tiles = (long)mt * ((N + bn - 1) / bn);
+    const double per_kb = 2.0 * np * (58.0 > bn * 0.254 ? 58.0 : bn * 0.254);
+    for (int s = 1; s <= 8; ++s) {
+      if (s > 1 && (bn > 176 || nkb / s < 4 || tiles > max_tiles || (size_t)s * mt * BM * (size_t)N > ws_floats)) break;
+      const long waves = (tiles * s + n_sm - 1) / n_sm;
+      const double kb_per_cta = (double)((nkb + s - 1) / s);
+      // per tile: prologue, pipeline fill and epilogue (~8 us + 20 ns per column); per split: the partial-tile traffic
+      const double cost = waves * (kb_per_cta * per_kb + 8000.0 + bn * 20.0) + (s > 1 ? 4000.0 + 2000.0 * s + bn * 10.0 * (s + 1) : 0.0);
+      if (cost < best - 1e-9) { best = cost; best_bn = bn; best_s = s; }
+    }
+  }
+  *bn_out = best_bn;
+  *splits_out = best_s;
 }
 
 }  // namespace tc

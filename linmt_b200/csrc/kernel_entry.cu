@@ -61,10 +61,16 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
       if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, 256)) return LINMT_ECUDA;
     }
     tc::TcEpiF32 e{nullptr, dy.as<float>(), Np, 0};
-    const int bn = tc::pick_bn(R, Np, 148);
+    int bn = 0, splits = 1;
+    const size_t ws_floats = (size_t)16 << 20;
+    tc::pick_shape(R, Np, Kp, nt, 148, ws_floats, 4096, &bn, &splits);
+    DevBuf dws, dcnt;
+    KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
     for (int t = 0; t < nt; ++t)
       if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn)) return LINMT_ECUDA;
-    cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, tc::make_shape(bn, nt), e, derr.as<int>(), 0);
+    tc::Shape sh = tc::make_shape(bn, nt);
+    sh.splits = splits;
+    cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>());
     KCK(le);
     KCK(cudaDeviceSynchronize());
     int herr = 0;
@@ -103,13 +109,16 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
 // engine's own choice), nt planes and at most max_stages shared-memory stages (0 = all that fit).
 int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
                       float* ms_out, int32_t device) {
-  int drain = 0;
-  if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }  // tuning: hundreds digit = drain interval
+  int drain = 0, force_splits = 0;
+  if (max_stages >= 10000) { force_splits = max_stages / 10000; max_stages %= 10000; }  // tuning: splits * 10000
+  if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }                 // + drain * 100 + stages
   using namespace linmt;
   if (R < 1 || K < 32 || N < 16 || nt < 1 || nt > 3 || iters < 1 || !ms_out) return LINMT_EINVAL;
   if (K % 32 || N % 16) return LINMT_EINVAL;
   KCK(cudaSetDevice(device));
-  if (bn <= 0) bn = tc::pick_bn(R, N, 148);
+  int splits = 1;
+  const size_t ws_floats = (size_t)16 << 20;
+  if (bn <= 0) tc::pick_shape(R, N, K, nt, 148, ws_floats, 4096, &bn, &splits);
   if (bn % 16 || bn > 256) return LINMT_EINVAL;
   DevBuf pa[3], pb[3], dy, derr;
   tc::Planes A{}, B{};
@@ -120,6 +129,8 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
     A.p[t] = pa[t].as<__nv_bfloat16>(); B.p[t] = pb[t].as<__nv_bfloat16>();
   }
   KCK(dy.alloc((size_t)R * N * 4)); KCK(derr.alloc(4)); KCK(cudaMemset(derr.p, 0, 4));
+  DevBuf dws, dcnt;
+  KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
   tc::TmapSet tm{};
   for (int t = 0; t < nt; ++t) {
     if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM)) return LINMT_ECUDA;
@@ -128,12 +139,13 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
   tc::Shape sh = tc::make_shape(bn, nt);
   if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
   if (drain > 0) sh.drain = drain;
+  sh.splits = force_splits > 0 ? force_splits : splits;
   tc::TcEpiF32 e{nullptr, dy.as<float>(), N, 0};
   cudaEvent_t e0, e1;
   KCK(cudaEventCreate(&e0)); KCK(cudaEventCreate(&e1));
-  for (int i = 0; i < 2; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0));
+  for (int i = 0; i < 2; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>()));
   KCK(cudaEventRecord(e0, 0));
-  for (int i = 0; i < iters; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0));
+  for (int i = 0; i < iters; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>()));
   KCK(cudaEventRecord(e1, 0));
   KCK(cudaDeviceSynchronize());
   float ms = 0.f;
