@@ -327,6 +327,9 @@ def run_ours(args):
                          "traffic": VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" else None,
                          "peak_source": peak_src, "launches": int(gemm_n),
                          "avg_launch_ms": gemm_ms / max(gemm_n, 1),
+                         "bf16_products_per_product": (1 if c.precision == "bf16" else (4 if args.gemm_path in ("auto", "tensor", "tensor2") else 0)),
+                         "tensor_pipe_tflops": (achieved * (1 if c.precision == "bf16" else 4)) if (achieved and args.gemm_path != "simt") else None,
+                         "tensor_pipe_frac": (achieved * (1 if c.precision == "bf16" else 4) / peak) if (achieved and args.gemm_path != "simt") else None,
                          "note": "achieved = algorithmic fp32 FLOPs; the fp32 path runs 4 bf16 partial products per "
                                  "product in this kernel (6 in the recurrent GEMMs), the bf16 path 1"},
             "cpu_baseline": cpu, "clocks": clocks, "gemm_path": args.gemm_path,
