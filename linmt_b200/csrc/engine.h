@@ -98,8 +98,8 @@ class Engine {
   int alloc_state_tc(TcState& s);
   int alloc_planes(tc::Planes& p, size_t rows, int ld);
   int to_planes(const std::vector<float>& host, size_t rows, int ld, tc::Planes& dst);
-  const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K);
-  const CUtensorMap* b_maps(const tc::Planes& p, int rows, int K, int bn);
+  const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K, int bk);
+  const CUtensorMap* b_maps(const tc::Planes& p, int rows, int K, int bn, int bk);
   template <class Epi>
   int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt = 0);
 

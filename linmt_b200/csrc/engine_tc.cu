@@ -71,24 +71,24 @@ int Engine::alloc_state_tc(TcState& s) {
 }
 
 // Tensor maps are built once per (buffer view, shape) and reused by every launch.
-const CUtensorMap* Engine::a_maps(const tc::Planes& p, int col0, int rows_cap, int K) {
-  auto key = std::make_tuple((const void*)(p.p[0] + col0), rows_cap, K, p.ld, (int)tc::BM);
+const CUtensorMap* Engine::a_maps(const tc::Planes& p, int col0, int rows_cap, int K, int bk) {
+  auto key = std::make_tuple((const void*)(p.p[0] + col0), rows_cap, K, p.ld, (int)tc::BM + 1000 * bk);
   auto it = tmap_cache_.find(key);
   if (it == tmap_cache_.end()) {
     std::array<CUtensorMap, 3> m{};
     for (int t = 0; t < nt_; ++t)
-      if (!tc::make_tmap(&m[t], p.p[t] + col0, rows_cap, K, p.ld, tc::BM)) return nullptr;
+      if (!tc::make_tmap(&m[t], p.p[t] + col0, rows_cap, K, p.ld, tc::BM, bk)) return nullptr;
     it = tmap_cache_.emplace(key, m).first;
   }
   return it->second.data();
 }
-const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn) {
-  auto key = std::make_tuple((const void*)p.p[0], rows, K, p.ld, bn);
+const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn, int bk) {
+  auto key = std::make_tuple((const void*)p.p[0], rows, K, p.ld, bn + 1000 * bk);
   auto it = tmap_cache_.find(key);
   if (it == tmap_cache_.end()) {
     std::array<CUtensorMap, 3> m{};
     for (int t = 0; t < nt_; ++t)
-      if (!tc::make_tmap(&m[t], p.p[t], rows, K, p.ld, bn)) return nullptr;
+      if (!tc::make_tmap(&m[t], p.p[t], rows, K, p.ld, bn, bk)) return nullptr;
     it = tmap_cache_.emplace(key, m).first;
   }
   return it->second.data();
@@ -102,13 +102,16 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   const size_t ws_floats = kSplitKWsFloats / ws_parts_;
   const int max_tiles = kSplitKMaxTiles / ws_parts_;
   tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits);
-  const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K);
-  const CUtensorMap* bm = b_maps(W, N, K, bn);
+  // one plane (bf16 precision): 64-deep stages with 128-byte rows halve the per-k-block overheads
+  // (measured 1.5x on the gate GEMMs); with split operands only 32-deep stages leave room for a ring
+  const int bk = (nt == 1) ? 64 : 32;
+  const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K, bk);
+  const CUtensorMap* bm = b_maps(W, N, K, bn, bk);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
   tc::TmapSet tm;
   std::memcpy(tm.a, am, sizeof(tm.a));
   std::memcpy(tm.b, bm, sizeof(tm.b));
-  tc::Shape sh = tc::make_shape(bn, nt);
+  tc::Shape sh = tc::make_shape(bn, nt, bk);
   sh.splits = splits;
   CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,
                         d_splitk_counters_ + ws_part_ * max_tiles));

@@ -49,6 +49,7 @@ constexpr int kDrainDefault = 4;       // k-blocks of the leading product per TM
 
 struct Shape {
   int bn;        // tile width
+  int bk;        // K depth of a stage in bf16 elements: 32 (64-byte rows) or 64 (128-byte rows)
   int nt;        // planes per operand
   int stages;
   int stage_bytes;
@@ -56,10 +57,10 @@ struct Shape {
   int drain;     // k-blocks between drains of the leading accumulator
   int splits;    // split-K factor (1 = none)
 };
-inline Shape make_shape(int bn, int nt) {
+inline Shape make_shape(int bn, int nt, int bk = BK) {
   Shape s;
-  s.bn = bn; s.nt = nt;
-  s.stage_bytes = nt * (A_BYTES + bn * BK * 2);
+  s.bn = bn; s.nt = nt; s.bk = bk;
+  s.stage_bytes = nt * (BM * bk * 2 + bn * bk * 2);
   s.stages = SMEM_BUDGET / s.stage_bytes;
   if (s.stages > kMaxStages) s.stages = kMaxStages;
   s.smem_bytes = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -137,15 +138,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 64 bytes (BK bf16) with
-// the 64-byte swizzle TMA wrote: 8-row groups are 512 bytes apart.
+// the 64-byte swizzle TMA wrote (8-row groups 512 bytes apart), or 128-byte rows with the
+// 128-byte swizzle (groups 1024 bytes apart).
 //   bits 0-13 start address >> 4 | 16-29 leading byte offset >> 4 (unused here) |
 //   32-45 stride byte offset >> 4 | 46-47 descriptor version (1) | 61-63 swizzle (4 = 64 B)
+template <int BKT>
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)(512u >> 4) << 32;
+  d |= (uint64_t)((8u * BKT * 2u) >> 4) << 32;   // 8-row groups: 512 bytes apart (64-byte rows) or 1024 (128-byte rows)
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)4 << 61;
+  d |= (uint64_t)(BKT == 64 ? 2 : 4) << 61;      // swizzle: 128 bytes / 64 bytes
   return d;
 }
 // Instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9, 10-12 = 1),
@@ -326,11 +329,13 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
 }
 
 // ---- kernel -------------------------------------------------------------------------------
-template <int NT, class Epi>
+template <int NT, int BKT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, int kDrainEvery, Epi epi,
                int* __restrict__ err_flag, int splits, float* __restrict__ ws, int* __restrict__ tile_counters) {
   constexpr int NP = num_products(NT);
+  constexpr int A_BYTES = BM * BKT * 2;   // one plane of the A tile of a stage (shadows the 32-deep constant)
+  constexpr int BK = BKT;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // stage tiles need 1024-byte alignment
@@ -399,8 +404,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(fb, ph, &s_abort)) break;
         tc_fence_after();
-        const uint64_t a0 = make_desc(st);                        // plane 0 of A, k-step 0
-        const uint64_t b0 = make_desc(st + NT * A_BYTES);         // plane 0 of B, k-step 0
+        const uint64_t a0 = make_desc<BKT>(st);                        // plane 0 of A, k-step 0
+        const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);         // plane 0 of B, k-step 0
         if (NP == 1) {
           // plain bf16: one accumulation chain
 #pragma unroll
@@ -576,39 +581,48 @@ inline EncodeTiledFn encode_fn() {
 
 // Tensor map of a K-major bf16 matrix [rows][ld] (K columns used), box = BK x box_rows,
 // 64-byte swizzle.  Rows past `rows` and columns past `K` read as zero.
-inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows) {
+inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows,
+                      int bk = BK) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {K, rows};
   cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)bk, box_rows};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NT, class Epi>
+template <int NT, int BKT, class Epi>
 inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                      cudaStream_t st, float* ws, int* counters) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, BKT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
   const int splits = (sh.splits > 1 && ws && counters) ? sh.splits : 1;
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
-  gemm_tc_kernel<NT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, sh.drain > 0 ? sh.drain : kDrainDefault, epi, err_flag,
+  int drain = (sh.drain > 0 ? sh.drain : kDrainDefault) * 32 / BKT;
+  if (drain < 1) drain = 1;
+  gemm_tc_kernel<NT, BKT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, drain, epi, err_flag,
                                                                   splits, splits > 1 ? ws : nullptr, counters);
   return cudaGetLastError();
 }
 template <class Epi>
 inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                   cudaStream_t st, float* ws = nullptr, int* counters = nullptr) {
-  if (sh.nt == 3) return launch_gemm_tc_nt<3, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
-  if (sh.nt == 2) return launch_gemm_tc_nt<2, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
-  return launch_gemm_tc_nt<1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  if (sh.bk == 64) {
+    if (sh.nt == 2) return launch_gemm_tc_nt<2, 64, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    if (sh.nt == 1) return launch_gemm_tc_nt<1, 64, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    return cudaErrorInvalidValue;  // three planes of 128-byte rows leave room for one stage only
+  }
+  if (sh.nt == 3) return launch_gemm_tc_nt<3, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  if (sh.nt == 2) return launch_gemm_tc_nt<2, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  return launch_gemm_tc_nt<1, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
 }
 
 // Tile width that fills the SMs best for an M x N problem: the smallest makespan

@@ -1,5 +1,6 @@
 // kernel_entry.cu -- single-kernel entry points of the C ABI (host pointers), used by the
 // parity tests to check one kernel at a time against the CPU checker.
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -55,9 +56,11 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     tc::split_planes_kernel<<<256, 256>>>(dx.as<float>(), A, nt, xp.size());
     tc::split_planes_kernel<<<1024, 256>>>(dw.as<float>(), B, nt, wt.size());
     KCK(cudaGetLastError());
+    const char* bk_env = std::getenv("LINMT_TC_BK");   // test knob: stage depth 64 (128-byte rows) for <= 2 planes
+    const int bk = (bk_env && std::atoi(bk_env) == 64 && nt <= 2) ? 64 : 32;
     tc::TmapSet tm{};
     for (int t = 0; t < nt; ++t) {
-      if (!tc::make_tmap(&tm.a[t], A.p[t], R, Kp, Kp, tc::BM)) return LINMT_ECUDA;
+      if (!tc::make_tmap(&tm.a[t], A.p[t], R, Kp, Kp, tc::BM, bk)) return LINMT_ECUDA;
       if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, 256)) return LINMT_ECUDA;
     }
     tc::TcEpiF32 e{nullptr, dy.as<float>(), Np, 0};
@@ -67,8 +70,8 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     DevBuf dws, dcnt;
     KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
     for (int t = 0; t < nt; ++t)
-      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn)) return LINMT_ECUDA;
-    tc::Shape sh = tc::make_shape(bn, nt);
+      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn, bk)) return LINMT_ECUDA;
+    tc::Shape sh = tc::make_shape(bn, nt, bk);
     sh.splits = splits;
     cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>());
     KCK(le);
@@ -109,7 +112,8 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
 // engine's own choice), nt planes and at most max_stages shared-memory stages (0 = all that fit).
 int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
                       float* ms_out, int32_t device) {
-  int drain = 0, force_splits = 0;
+  int drain = 0, force_splits = 0, bk = 32;
+  if (bn >= 1000) { bk = 64; bn -= 1000; }  // tuning: bn + 1000 = 128-byte rows
   if (max_stages >= 10000) { force_splits = max_stages / 10000; max_stages %= 10000; }  // tuning: splits * 10000
   if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }                 // + drain * 100 + stages
   using namespace linmt;
@@ -133,10 +137,10 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
   KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
   tc::TmapSet tm{};
   for (int t = 0; t < nt; ++t) {
-    if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM)) return LINMT_ECUDA;
-    if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn)) return LINMT_ECUDA;
+    if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM, bk)) return LINMT_ECUDA;
+    if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn, bk)) return LINMT_ECUDA;
   }
-  tc::Shape sh = tc::make_shape(bn, nt);
+  tc::Shape sh = tc::make_shape(bn, nt, bk);
   if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
   if (drain > 0) sh.drain = drain;
   sh.splits = force_splits > 0 ? force_splits : splits;
