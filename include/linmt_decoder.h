@@ -168,6 +168,14 @@ int linmt_set_kernel_timing(linmt_engine* e, int32_t on);
  * string valid until the next call on the same handle. */
 const char* linmt_translate(linmt_engine* e, const char* sentence);
 
+/* File-mode decoding: one source sentence per line of `in_path`; writes the n-best
+ * translations of every sentence to `out_path` in input order.  Replaces
+ * EnsembleFactory::DecodeFile (src/decoder.h:1702-1776), Decoder::OutputKBestHypotheses
+ * (src/decoder.h:529-699) and InputFilePreprocess::UnintFile
+ * (src/input_file_preprocess.cc:1485-1572).  Needs an engine created from a config file; sentences
+ * are decoded in length-sorted batches of --batch-size. */
+int linmt_decode_file(linmt_engine* e, const char* in_path, const char* out_path);
+
 /* ------------------------------------------------------------------------------------
  * 3. Single-kernel entry points (host pointers) used by the parity tests.
  * ------------------------------------------------------------------------------------ */

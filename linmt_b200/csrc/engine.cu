@@ -379,7 +379,7 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
     const size_t smem = sizeof(float) * (win + 8);
-    attention_kernel<<<rows, 128, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
+    attention_kernel<<<rows, 256, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
                                                   opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
                                                   tc::Planes{}, 0);
     LAUNCHED();
@@ -433,8 +433,8 @@ int Engine::step_tail(int t, int rows) {
   }
   {
     BeamState bs{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
-    const size_t smem = (size_t)k * kk * 16;
-    beam_select_kernel<<<n_act, 128, smem, stream>>>(bs, d_cand_idx_, d_cand_logp_, d_eos_logp_, d_steps_, d_orig_, t, k,
+    const size_t smem = (size_t)k * kk * 24 + 16;
+    beam_select_kernel<<<n_act, 256, smem, stream>>>(bs, d_cand_idx_, d_cand_logp_, d_eos_logp_, d_steps_, d_orig_, t, k,
                                                      opt.penalty, opt.diversity, trace_dev_);
     LAUNCHED();
   }

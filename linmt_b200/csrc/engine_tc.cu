@@ -254,7 +254,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
     const size_t smem = sizeof(float) * (win + 8);
-    attention_kernel<<<rows, 128, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, nullptr, H, Hp, k,
+    attention_kernel<<<rows, 256, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, nullptr, H, Hp, k,
                                                   opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
                                                   ts.panel_top, nt_);
     LAUNCHED();

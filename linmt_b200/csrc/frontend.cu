@@ -381,6 +381,100 @@ const char* linmt_translate(linmt_engine* h, const char* sentence) {
   return e.result_buf.c_str();
 }
 
+// File-mode decoding on top of the batch API: EnsembleFactory::DecodeFile (src/decoder.h:1702-1776)
+// with Decoder::OutputKBestHypotheses (src/decoder.h:529-699) and InputFilePreprocess::UnintFile
+// (src/input_file_preprocess.cc:1485-1572).  One source sentence per input line; per sentence the
+// n-best hypotheses one per line (words, then " |||| score |||| alignments |||| unk-alignments"
+// when print-decoding-info is on; scores with three decimals as the reference's file stream prints
+// them, src/decoder.h:267), followed by a line of sixteen '=' when nbest != 1.  Sentences are
+// decoded in length-sorted batches of --batch-size and written back in input order; a sentence
+// longer than --longest-sent yields an empty line (the reference's file preprocessing drops it,
+// src/input_file_preprocess.cc:1430-1438).
+int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path) {
+  using namespace linmt;
+  if (!h || !in_path || !out_path) return LINMT_EINVAL;
+  Engine& e = h->eng;
+  std::ifstream in(in_path);
+  if (!in) { e.err = std::string("can not open ") + in_path; return LINMT_EIO; }
+  std::vector<std::vector<int32_t>> sents;
+  std::string line;
+  while (std::getline(in, line)) {
+    const size_t cut = line.find(" |||| ");
+    if (cut != std::string::npos) line = line.substr(0, cut);
+    std::vector<int32_t> ids;
+    std::istringstream iss(line);
+    std::string w;
+    while (iss >> w) {
+      auto it = std::lower_bound(e.src_words_sorted.begin(), e.src_words_sorted.end(), std::make_pair(w, INT32_MIN));
+      ids.push_back((it != e.src_words_sorted.end() && it->first == w) ? it->second : 0);
+    }
+    if ((int)ids.size() > e.opt.max_src_len) ids.clear();
+    sents.push_back(std::move(ids));
+  }
+  const int n_all = (int)sents.size();
+  std::vector<int> order;
+  for (int i = 0; i < n_all; ++i) if (!sents[i].empty()) order.push_back(i);
+  auto steps_of = [&](int i) {
+    int st = std::min((int)(e.opt.max_ratio * (int)sents[i].size()), e.longest_sentence - 2);  // src/decoder.h:1806
+    return st < 0 ? 0 : st;
+  };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return steps_of(a) > steps_of(b); });
+  std::vector<std::string> results(n_all);
+  const int nb = e.opt.nbest, B = e.opt.max_batch;
+  const bool info = e.opt.print_info != 0;
+  const bool want_align = info && e.print_align_scores;
+  for (size_t b0 = 0; b0 < order.size(); b0 += B) {
+    const int n = (int)std::min<size_t>(B, order.size() - b0);
+    std::vector<int32_t> ids, off(1, 0), steps;
+    int Tm = 0;
+    for (int i = 0; i < n; ++i) {
+      const auto& sv = sents[order[b0 + i]];
+      ids.insert(ids.end(), sv.begin(), sv.end());
+      off.push_back((int32_t)ids.size());
+      steps.push_back(steps_of(order[b0 + i]));
+      Tm = std::max(Tm, steps.back());
+    }
+    const int max_len = Tm + 2;
+    std::vector<int32_t> tok((size_t)n * nb * max_len), len((size_t)n * nb), vit((size_t)n * nb * max_len, -1);
+    std::vector<float> score((size_t)n * nb), align;
+    if (want_align) align.resize((size_t)n * nb * max_len * e.opt.max_src_len);
+    int rc = e.decode_host(ids.data(), off.data(), n, steps.data(), max_len, tok.data(), len.data(), score.data(), vit.data(),
+                           want_align ? align.data() : nullptr, nullptr);
+    if (rc != LINMT_OK) return rc;
+    for (int i = 0; i < n; ++i) {
+      const int S = off[i + 1] - off[i];
+      std::string out;
+      for (int q = 0; q < nb; ++q) {
+        const size_t ob = (size_t)i * nb + q;
+        if (len[ob] == 0) continue;
+        // one hypothesis through the sentence formatter, then the score re-printed with three decimals
+        int32_t one_len = len[ob];
+        std::string hyp = format_result(e, S, 1, max_len, &tok[ob * max_len], &one_len, &score[ob], &vit[ob * max_len],
+                                        want_align ? &align[ob * max_len * e.opt.max_src_len] : nullptr, e.opt.max_src_len);
+        if (info) {
+          const size_t p1 = hyp.find(" |||| ");
+          if (p1 != std::string::npos) {
+            const size_t p2 = hyp.find(" ||||", p1 + 6);
+            char buf[64];
+            std::snprintf(buf, sizeof buf, "%.3f", score[ob]);
+            if (p2 != std::string::npos) hyp = hyp.substr(0, p1 + 6) + buf + hyp.substr(p2);
+          }
+        }
+        out += hyp + "\n";
+      }
+      if (nb != 1) out += "================\n";
+      results[order[b0 + i]] = out;
+    }
+  }
+  std::ofstream outf(out_path);
+  if (!outf) { e.err = std::string("can not open ") + out_path; return LINMT_EIO; }
+  for (int i = 0; i < n_all; ++i) {
+    if (results[i].empty()) outf << (nb != 1 ? "\n================\n" : "\n");
+    else outf << results[i];
+  }
+  return LINMT_OK;
+}
+
 // ---- the reference's exported pair (src/decoder_sentence.cu:844-873) ---------------------
 static linmt_engine* g_singleton = nullptr;
 static char* g_result = nullptr;

@@ -147,8 +147,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   ctx  [rows][Hp] fp32 and/or ctx_planes (bf16 planes, columns [0,Hp) of the panel)
 //   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
 //   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
-// grid = rows, block = 128, dynamic smem = (win + 8) floats
-static __global__ void __launch_bounds__(128) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+// grid = rows, block = 256, dynamic smem = (win + 8) floats
+static __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
@@ -196,26 +196,36 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
     if (lane == 0) e[w] = acc;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    // AlignmentReductionKernel, deep_rnn_kernel.h:1197-1241 (max starts at 0, no
-    // renormalisation after the Gaussian)
+  if (warp == 0) {
+    // AlignmentReductionKernel, deep_rnn_kernel.h:1197-1241 (max starts at 0, no renormalisation
+    // after the Gaussian), one lane per window position instead of one thread per beam
     float mx = 0.f;
-    for (int w = 0; w < W; ++w) if (e[w] > mx) mx = e[w];
+    for (int w = lane; w < W; w += 32) mx = fmaxf(mx, e[w]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.f;
-    for (int w = 0; w < W; ++w) { e[w] = expf(e[w] - mx); sum += e[w]; }
+    for (int w = lane; w < W; w += 32) { const float ev = expf(e[w] - mx); e[w] = ev; sum += ev; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float sigma_sq = ((float)D * (float)D) / 4.0f;
     const float pt = s_pt;
-    float best = 0.f; int besti = -1;
-    for (int w = 0; w < W; ++w) {
+    float best = 0.f; int besti = 0x7fffffff;
+    for (int w = lane; w < W; w += 32) {
       float a = e[w];
       if (mode == 0) {
         const float tmp = expf((-1 * powf(pt - (float)(lo + w), 2.0f)) / (2 * sigma_sq));
         if (0 != sum) a = (a / sum) * tmp;
       } else if (0 != sum) a = a / sum;
       e[w] = a;
-      if (a > best) { best = a; besti = lo + w; }  // viterbi vote, src/decoder.h:1948-1962
+      if (a > best) { best = a; besti = lo + w; }  // viterbi vote, src/decoder.h:1948-1962 (first maximum)
     }
-    if (rec_lo) { rec_lo[r] = lo; rec_vit[r] = besti; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0 && rec_lo) { rec_lo[r] = lo; rec_vit[r] = (best > 0.f) ? besti : -1; }
   }
   __syncthreads();
   if (rec_align)
@@ -232,8 +242,7 @@ static __global__ void __launch_bounds__(128) attention_kernel(const float* __re
     if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
     if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
       const size_t idx = (size_t)r * ctx_planes.ld + j;
-      tc::split_store(ctx_planes, nt, idx, acc.x); tc::split_store(ctx_planes, nt, idx + 1, acc.y);
-      tc::split_store(ctx_planes, nt, idx + 2, acc.z); tc::split_store(ctx_planes, nt, idx + 3, acc.w);
+      tc::split_store4(ctx_planes, nt, idx, acc.x, acc.y, acc.z, acc.w);
     }
   }
 }
@@ -298,7 +307,7 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   // ---- pass 2: sum of exponentials, candidates ----
   float ssum = 0.f;
   auto visit = [&](float v, int i) {
-    ssum += expf(v - rmax);
+    ssum += __expf(v - rmax);  // arguments in [-few, 0]: ~1e-7 relative on the sum of V terms
     if (v >= tau) {
       const int pos = atomicAdd(&s_count, 1);
       if (pos < kTopkCap) { s_cv[pos] = v; s_ci[pos] = i; }
@@ -450,8 +459,8 @@ struct TraceDev {
   const int32_t* force_tok; const int32_t* force_parent; const float* force_score;
   int Tm;
 };
-// grid = active sentences, block = 128, dynamic smem = k*kk*(4+4+4+4) bytes
-static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_logp,
+// grid = active sentences, block = 256, dynamic smem = k*kk*24 + 8 bytes
+static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_logp,
                                    const float* __restrict__ eos_logp, const int32_t* __restrict__ steps,
                                    const int32_t* __restrict__ orig, int t, int k, float penalty, float diversity,
                                    TraceDev tr) {
@@ -462,6 +471,7 @@ static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, c
   int* cb = reinterpret_cast<int*>(cs + ncap);   // beam
   int* cv = cb + ncap;                           // vocab id
   int* order = cv + ncap;                        // sorted position -> candidate
+  unsigned long long* key = reinterpret_cast<unsigned long long*>(order + ncap);  // sortable (score, beam, vocab)
   const int sent = blockIdx.x;
   const int T = steps[sent];
   const int r0 = sent * k;
@@ -494,6 +504,13 @@ static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, c
     cs[c] = (lp + bs.score[r0 + b]) - rank_penalty;
     cb[c] = b; cv[c] = v;
     order[c] = c;  // overwritten by the ranking below; keeps every entry valid even for NaN scores
+    {
+      // one 64-bit key, larger = earlier: score descending, then beam ascending, then vocabulary id ascending
+      const unsigned int fb = __float_as_uint(cs[c]);
+      const unsigned int ord = (fb & 0x80000000u) ? ~fb : (fb | 0x80000000u);
+      const unsigned int low = 0xFFFFFFFFu - (((unsigned int)b << 24) | ((unsigned int)v & 0xFFFFFFu));
+      key[c] = ((unsigned long long)ord << 32) | low;
+    }
     if (tr.cand_tok) {
       const size_t off = ((((size_t)osent * tr.Tm + t) * k + b) * kk) + q;
       tr.cand_tok[off] = v; tr.cand_logp[off] = lp;
@@ -501,20 +518,19 @@ static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, c
   }
   __syncthreads();
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    const float s = cs[c]; const int b = cb[c], v = cv[c];
+    const unsigned long long kc = key[c];
     int pos = 0;
-    for (int d = 0; d < n; ++d) {
-      const float s2 = cs[d];
-      if (s2 > s || (s2 == s && (cb[d] < b || (cb[d] == b && cv[d] < v)))) ++pos;
-    }
+    for (int d = 0; d < n; ++d) pos += (key[d] > kc) ? 1 : 0;
     order[pos] = c;
   }
   __syncthreads();
+  // The walk itself is serial (START is skipped, EOS leaves the beam without taking a slot), but it
+  // only touches shared memory; every global write happens afterwards, one thread per slot.
+  __shared__ int s_ntok[kMaxBeam + 1], s_npar[kMaxBeam + 1];
+  __shared__ float s_nscore[kMaxBeam + 1];
   if (threadIdx.x == 0) {
     int ns = 0;
     int nf = bs.fin_n[sent];
-    int32_t* ht = bs.hist_tok + (size_t)t * bs.R;
-    int32_t* hp = bs.hist_parent + (size_t)t * bs.R;
     for (int p = 0; p < n && ns < k; ++p) {
       const int c = order[p];
       const int v = cv[c];
@@ -528,23 +544,23 @@ static __global__ void __launch_bounds__(128) beam_select_kernel(BeamState bs, c
         }
         continue;
       }
-      bs.tok[r0 + ns] = v; bs.parent[r0 + ns] = cb[c]; bs.score[r0 + ns] = cs[c] + penalty;
+      s_ntok[ns] = v; s_npar[ns] = cb[c]; s_nscore[ns] = cs[c] + penalty;
       ++ns;
     }
-    for (; ns < k; ++ns) { bs.tok[r0 + ns] = kUnk; bs.parent[r0 + ns] = 0; bs.score[r0 + ns] = kDeadScore; }
+    for (; ns < k; ++ns) { s_ntok[ns] = kUnk; s_npar[ns] = 0; s_nscore[ns] = kDeadScore; }
     bs.fin_n[sent] = nf;
-    for (int b = 0; b < k; ++b) {
-      if (tr.surv_tok) {
-        const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
-        tr.surv_tok[off] = bs.tok[r0 + b]; tr.surv_parent[off] = bs.parent[r0 + b]; tr.surv_score[off] = bs.score[r0 + b];
-      }
-      if (tr.force_tok) {
-        const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
-        bs.tok[r0 + b] = tr.force_tok[off]; bs.parent[r0 + b] = tr.force_parent[off]; bs.score[r0 + b] = tr.force_score[off];
-      }
-      ht[r0 + b] = bs.tok[r0 + b];
-      hp[r0 + b] = bs.parent[r0 + b];
-    }
+  }
+  __syncthreads();
+  if (threadIdx.x < k) {
+    const int b = threadIdx.x;
+    int ntok = s_ntok[b], npar = s_npar[b];
+    float nscore = s_nscore[b];
+    const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
+    if (tr.surv_tok) { tr.surv_tok[off] = ntok; tr.surv_parent[off] = npar; tr.surv_score[off] = nscore; }
+    if (tr.force_tok) { ntok = tr.force_tok[off]; npar = tr.force_parent[off]; nscore = tr.force_score[off]; }
+    bs.tok[r0 + b] = ntok; bs.parent[r0 + b] = npar; bs.score[r0 + b] = nscore;
+    bs.hist_tok[(size_t)t * bs.R + r0 + b] = ntok;
+    bs.hist_parent[(size_t)t * bs.R + r0 + b] = npar;
   }
 }
 

@@ -143,6 +143,14 @@ class DecoderSentence:
             raise LinmtError("Init was not called")
         return self._lib.linmt_translate(self._h, input_sentence.encode()).decode()
 
+    def DecodeFile(self, in_path: str, out_path: str) -> None:
+        """File-mode decoding (src/decoder.h:1702-1776): one sentence per line in, n-best per sentence out."""
+        if self._h is None:
+            raise LinmtError("Init was not called")
+        rc = self._lib.linmt_decode_file(self._h, in_path.encode(), out_path.encode())
+        if rc != 0:
+            raise LinmtError(f"linmt_decode_file failed ({rc}): {self._lib.linmt_last_error(self._h).decode()}")
+
     def close(self):
         if self._h:
             self._lib.linmt_destroy(self._h)

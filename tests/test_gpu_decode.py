@@ -273,3 +273,42 @@ def test_ensemble_of_three(oracle, cuda_lib, c1, mode, gemm_path):
         a, b = one.decode(sents, trace=True), single.decode(sents, trace=True)
         np.testing.assert_allclose(a["cand_logp"][:, 0, 0], b["cand_logp"][:, 0, 0], rtol=1e-5, atol=1e-5)
         one.close(); single.close()
+
+
+def test_file_mode_matches_checker(oracle, cuda_lib, tmp_path):
+    """linmt_decode_file (the reference's --decoding file mode: src/decoder.h:1702-1776, 529-699):
+    n-best lines per sentence in input order, sixteen '=' between sentences, three-decimal scores,
+    an over-long sentence gives an empty entry."""
+    from linmt_b200 import decoder, modelfile
+    d = synth.ModelDesc(2, 32, 60, 50, 1)
+    blob = synth.make_blob(d, 9)
+    mp, cp = tmp_path / "model.nmt", tmp_path / "dec.config"
+    modelfile.write_model(str(mp), d, blob, binary=True)
+    modelfile.write_config(str(cp), [str(mp)], beam_size=3, nbest=2, longest_sent=20, lp_alpha=0.65, cp_beta=0.2,
+                           print_decoding_info=1, batch_size=2)
+    src = modelfile.default_vocab(d.Vs, "src")
+    tgt = modelfile.default_vocab(d.V, "tgt")
+    rng = np.random.default_rng(3)
+    id_lists = [list(rng.integers(1, d.Vs, size=n)) for n in (7, 3, 30, 12, 5)]
+    (tmp_path / "in.txt").write_text("\n".join(" ".join(src[i] for i in ids) for ids in id_lists) + "\n")
+    ds = decoder.DecoderSentence()
+    ds.Init(str(cp))
+    ds.DecodeFile(str(tmp_path / "in.txt"), str(tmp_path / "out.txt"))
+    ds.close()
+    blocks = (tmp_path / "out.txt").read_text().split("================\n")
+    assert len(blocks) == len(id_lists) + 1 and blocks[-1] == ""
+    for ids, block in zip(id_lists, blocks):
+        if len(ids) > 24:                     # longer than --longest-sent + 4
+            assert block == "\n"
+            continue
+        S = len(ids)
+        sents = synth.Sentences(np.array(ids, np.int32), np.array([0, S], np.int32), np.array([min(int(1.5 * S), 22)], np.int32))
+        o = oracle.decode(d, [blob], sents, beam=3, nbest=2, cp_beta=0.2, print_info=1)
+        lines = block.rstrip("\n").split("\n")
+        assert len(lines) == int((o["len"][0] > 0).sum())
+        for q, ln in enumerate(lines):
+            n = int(o["len"][0, q])
+            fields = ln.split(" |||| ")
+            assert fields[0] == " ".join(tgt[t] for t in o["tok"][0, q, 1:n - 1])
+            assert abs(float(fields[1]) - float(o["score"][0, q])) <= 1.5e-3
+            assert len(fields[1].split(".")[1]) == 3
