@@ -15,8 +15,8 @@
 //
 // One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) is a launch parameter so
 // the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues the TMA
-// loads, warp 1 owns TMEM and issues the MMAs, warps 2..9 run the epilogue (tcgen05.ld ->
-// registers -> fused math -> global).  The single issuing threads are the critical path of a
+// loads, warp 1 owns TMEM and issues the MMAs, warps 2..17 run the epilogue (tcgen05.ld ->
+// registers -> fused math -> global; four warps per TMEM lane quadrant, interleaved column chunks).  The single issuing threads are the critical path of a
 // narrow tile, so their loops carry descriptors forward by constant increments and everything
 // that can be is a compile-time constant; the waiting epilogue warps sleep between polls.
 // A ring of shared-memory stages is handed back and forth with mbarriers; every wait is
@@ -33,7 +33,8 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 32;             // bf16 elements per stage row = 64 bytes -> 64-byte swizzle
 constexpr int UMMA_K = 16;         // bf16 elements per tcgen05.mma
-constexpr int kThreads = 320;       // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kEpiWarps = 16;        // epilogue warps: four per TMEM lane quadrant
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
 
 struct alignas(64) TmapSet {
@@ -361,7 +362,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
     mbar_init(accum_bar, 1);
     mbar_init(main_full, 1);
-    mbar_init(main_free, 8);  // one arrival per epilogue warp
+    mbar_init(main_free, kEpiWarps);  // one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -442,9 +443,11 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       umma_commit(accum_bar);
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the two warps of a lane quadrant
-    // take alternate 16-column chunks
+    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the warps of a lane quadrant take
+    // interleaved 16-column chunks
     const int q = warp & 3;
+    constexpr int kParts = kEpiWarps / 4;       // warps sharing a lane quadrant take interleaved 16-column chunks
+    constexpr int kChunks = 16 / kParts;        // chunks per warp for the widest tile (256 columns)
     const int half = (warp - 2) >> 2;
     const int row = m0 + q * 32 + lane;
     const uint32_t astride = (uint32_t)acc_stride(BN);
@@ -465,7 +468,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = half * 16; c0 < BN; c0 += 32) {
+        for (int c0 = half * 16; c0 < BN; c0 += 16 * kParts) {
           float v[16];
           tmem_ld16(lane_base + (uint32_t)c0, v);
           emit(c0, v);
@@ -475,9 +478,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       // Two-level accumulation of the leading product: the tensor core rounds toward zero on
       // every accumulate (measured: a bias of -0.5 ulp per MMA, growing with K), so its chain is
       // kept to kDrainEvery k-blocks and the partial sums are added here in fp32 round-to-nearest.
-      float macc[8][16];
+      float macc[kChunks][16];
 #pragma unroll
-      for (int ci = 0; ci < 8; ++ci)
+      for (int ci = 0; ci < kChunks; ++ci)
 #pragma unroll
         for (int i = 0; i < 16; ++i) macc[ci][i] = 0.f;
       bool ok = true;
@@ -486,8 +489,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int ci = 0; ci < 8; ++ci) {
-          const int c0 = half * 16 + ci * 32;
+        for (int ci = 0; ci < kChunks; ++ci) {
+          const int c0 = half * 16 + ci * 16 * kParts;
           if (c0 < BN) {
             float w[16];
             tmem_ld16(lane_base + (uint32_t)c0, w);
@@ -502,8 +505,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       if (ok && mbar_wait(accum_bar, 0, &s_abort)) {
         tc_fence_after();
 #pragma unroll
-        for (int ci = 0; ci < 8; ++ci) {
-          const int c0 = half * 16 + ci * 32;
+        for (int ci = 0; ci < kChunks; ++ci) {
+          const int c0 = half * 16 + ci * 16 * kParts;
           if (c0 < BN) {
             float sm[16];
             tmem_ld16(lane_base + astride + (uint32_t)c0, sm);
@@ -538,7 +541,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       if (row < M) {
         const size_t zstride = (size_t)gridDim.x * BM * (size_t)N;
         const float* p0 = ws + (size_t)row * (size_t)N + n0;
-        for (int c0 = half * 16; c0 < BN && n0 + c0 < N; c0 += 32) {
+        for (int c0 = half * 16; c0 < BN && n0 + c0 < N; c0 += 16 * (kEpiWarps / 4)) {
           float v[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
