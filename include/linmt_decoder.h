@@ -122,6 +122,7 @@ typedef struct linmt_trace {
   const int32_t* force_tok;
   const int32_t* force_parent;
   const float* force_score;
+  float* gold_logp;   /* [n][Tm][k]: log p of the forced token of each slot (needs force_*), may be NULL */
 } linmt_trace;
 
 /* Decodes n independent sentences.  Replaces EnsembleFactory<T>::DecodeSentence
@@ -167,6 +168,15 @@ int linmt_set_kernel_timing(linmt_engine* e, int32_t on);
  * Needs an engine created from a config file (vocabularies).  Returns a library-owned
  * string valid until the next call on the same handle. */
 const char* linmt_translate(linmt_engine* e, const char* sentence);
+
+/* Force-decoding / scoring: log-probability of given target sentences under the model
+ * (the reference's --force-decoding path, src/deep_rnn.h:1490-1568, src/dispatcher.cu:699-752).
+ *   tgt_ids, tgt_off  target token ids per sentence WITHOUT START / EOS
+ *   out_logprob [n]   sum over the m_i tokens and the closing EOS of log p(token | source, prefix)
+ *   out_token_logp    optional [n][max_tgt + 1]: the per-token terms (EOS last), zero padded
+ * Every sentence needs 1 <= m_i <= max_steps. */
+int linmt_score_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* src_off, const int32_t* tgt_ids,
+                      const int32_t* tgt_off, int32_t n, float* out_logprob, float* out_token_logp, int32_t max_tgt);
 
 /* File-mode decoding: one source sentence per line of `in_path`; writes the n-best
  * translations of every sentence to `out_path` in input order.  Replaces

@@ -23,7 +23,8 @@ class OptionsC(C.Structure):
 class TraceC(C.Structure):
     _fields_ = [("cand_tok", C.c_void_p), ("cand_logp", C.c_void_p), ("surv_tok", C.c_void_p),
                 ("surv_parent", C.c_void_p), ("surv_score", C.c_void_p), ("final_logp", C.c_void_p),
-                ("force_tok", C.c_void_p), ("force_parent", C.c_void_p), ("force_score", C.c_void_p)]
+                ("force_tok", C.c_void_p), ("force_parent", C.c_void_p), ("force_score", C.c_void_p),
+                ("gold_logp", C.c_void_p)]
 
 
 class StatsC(C.Structure):
@@ -35,7 +36,7 @@ class StatsC(C.Structure):
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",
            "linmt_create_from_weights", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
            "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
-           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file"]
+           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch"]
 
 _lib = None
 
@@ -81,5 +82,6 @@ def load():
     lib.linmt_k_gemm_time.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_float), C.c_int32]
     lib.linmt_gemm_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.linmt_decode_file.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
+    lib.linmt_score_batch.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]
     _lib = lib
     return lib

@@ -275,7 +275,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   DA(d_fin_t_, (size_t)B * fin_cap); DA(d_fin_b_, (size_t)B * fin_cap); DA(d_fin_n_, B);
   DA(d_fin_score_, (size_t)B * fin_cap); DA(d_fin_final_, (size_t)B * fin_cap);
   if (nm > 1) DA(d_combined_, (size_t)R * Vp);
-  DA(d_cand_idx_, (size_t)R * kk); DA(d_cand_logp_, (size_t)R * kk); DA(d_eos_logp_, R);
+  DA(d_cand_idx_, (size_t)R * kk); DA(d_cand_logp_, (size_t)R * kk); DA(d_eos_logp_, R); DA(d_row_stats_, 2 * (size_t)R);
   if (o.print_info) {
     DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
   }
@@ -415,7 +415,10 @@ int Engine::step_tail(int t, int rows) {
   DevState& s = states_[0];
   const int n_act = rows / k;
   {
-    TopkOut o{d_cand_idx_, d_cand_logp_, d_eos_logp_};
+    TopkOut o{d_cand_idx_, d_cand_logp_, d_eos_logp_, d_row_stats_};
+    trace_dev_.logits = (n_models == 1) ? s.logits : d_combined_;
+    trace_dev_.ld_logits = Vp;
+    trace_dev_.row_stats = d_row_stats_;
     if (n_models == 1) {
       CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream));
     } else {
@@ -488,6 +491,7 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     trace_dev_.surv_score = trace_dev->surv_score; trace_dev_.final_logp = trace_dev->final_logp;
     trace_dev_.force_tok = trace_dev->force_tok; trace_dev_.force_parent = trace_dev->force_parent;
     trace_dev_.force_score = trace_dev->force_score; trace_dev_.Tm = trace_Tm;
+    trace_dev_.gold_logp = trace_dev->gold_logp;
   }
   gemm_ev_used_ = 0;
   int rc = use_tc_ ? run_encoder_tc(n, Smax) : run_encoder(n, Smax);
@@ -596,6 +600,7 @@ int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, c
       if ((rc = mk(n_s, 4, trace->surv_parent ? trace->surv_parent + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_parent))) return rc;
       if ((rc = mk(n_s, 4, trace->surv_score ? trace->surv_score + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_score))) return rc;
       if ((rc = mk(n_f, 4, trace->final_logp ? trace->final_logp + (size_t)c0 * k : nullptr, nullptr, (void**)&td.final_logp))) return rc;
+      if ((rc = mk(n_s, 4, trace->gold_logp ? trace->gold_logp + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.gold_logp))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_tok ? trace->force_tok + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_tok))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_parent ? trace->force_parent + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_parent))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_score ? trace->force_score + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_score))) return rc;
@@ -687,6 +692,56 @@ int linmt_decode_batch_device(linmt_engine* e, const int32_t* d_src_ids, const i
                               nullptr, nullptr, 0);
   if (rc) return rc;
   return e->eng.finish_timing();
+}
+
+int linmt_score_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* src_off, const int32_t* tgt_ids,
+                      const int32_t* tgt_off, int32_t n, float* out_logprob, float* out_token_logp, int32_t max_tgt) {
+  if (!e || !src_ids || !src_off || !tgt_ids || !tgt_off || !out_logprob || n < 0) return LINMT_EINVAL;
+  Engine& g = e->eng;
+  if (g.n_models > 1 && g.opt.ensemble_mode != LINMT_ENS_PROB_MEAN) { g.err = "scoring supports single models and prob_mean ensembles"; return LINMT_EINVAL; }
+  const int k = g.k;
+  int Tm = 0;
+  std::vector<int32_t> steps(n);
+  for (int i = 0; i < n; ++i) {
+    steps[i] = tgt_off[i + 1] - tgt_off[i];
+    if (steps[i] < 1 || steps[i] > g.opt.max_steps) { g.err = "target length outside 1..max_steps"; return LINMT_ELIMIT; }
+    Tm = std::max(Tm, steps[i]);
+  }
+  if (out_token_logp && max_tgt < Tm) { g.err = "max_tgt smaller than the longest target"; return LINMT_EINVAL; }
+  // every beam slot is forced to the given token: slot b continues slot b
+  std::vector<int32_t> ftok((size_t)n * Tm * k, 2), fpar((size_t)n * Tm * k, 0);
+  std::vector<float> fscore((size_t)n * Tm * k, 0.f), gold((size_t)n * Tm * k, 0.f), fin((size_t)n * k, 0.f);
+  for (int i = 0; i < n; ++i)
+    for (int t = 0; t < steps[i]; ++t)
+      for (int b = 0; b < k; ++b) {
+        const size_t off = ((size_t)i * Tm + t) * k + b;
+        ftok[off] = tgt_ids[tgt_off[i] + t];
+        fpar[off] = b;
+      }
+  linmt_trace tr{};
+  tr.force_tok = ftok.data(); tr.force_parent = fpar.data(); tr.force_score = fscore.data();
+  tr.gold_logp = gold.data(); tr.final_logp = fin.data();
+  const int max_len = Tm + 2, nb = g.opt.nbest;
+  std::vector<int32_t> tok((size_t)n * nb * max_len), len((size_t)n * nb);
+  std::vector<float> score((size_t)n * nb);
+  int rc = g.decode_host(src_ids, src_off, n, steps.data(), max_len, tok.data(), len.data(), score.data(), nullptr, nullptr, &tr);
+  if (rc != LINMT_OK) return rc;
+  for (int i = 0; i < n; ++i) {
+    float sum = 0.f;
+    for (int t = 0; t < steps[i]; ++t) {
+      const float lp = gold[((size_t)i * Tm + t) * k];
+      sum += lp;
+      if (out_token_logp) out_token_logp[(size_t)i * (max_tgt + 1) + t] = lp;
+    }
+    const float le = fin[(size_t)i * k];
+    sum += le;
+    if (out_token_logp) {
+      out_token_logp[(size_t)i * (max_tgt + 1) + steps[i]] = le;
+      for (int t = steps[i] + 1; t <= max_tgt; ++t) out_token_logp[(size_t)i * (max_tgt + 1) + t] = 0.f;
+    }
+    out_logprob[i] = sum;
+  }
+  return LINMT_OK;
 }
 
 int linmt_get_stats(const linmt_engine* e, linmt_stats* out) {

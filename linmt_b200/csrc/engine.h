@@ -139,7 +139,7 @@ class Engine {
   float *d_fin_score_ = nullptr, *d_fin_final_ = nullptr;
   float* d_combined_ = nullptr;  // [R][Vp] ensemble-combined log-values (n_models > 1)
   int32_t* d_cand_idx_ = nullptr;
-  float *d_cand_logp_ = nullptr, *d_eos_logp_ = nullptr;
+  float *d_cand_logp_ = nullptr, *d_eos_logp_ = nullptr, *d_row_stats_ = nullptr;
   // alignment records (print_info)
   float* d_rec_align_ = nullptr;
   int32_t *d_rec_lo_ = nullptr, *d_rec_vit_ = nullptr;

@@ -97,7 +97,7 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
   DevBuf dl, di, dp, de;
   KCK(dl.alloc(lp.size() * 4)); KCK(di.alloc((size_t)R * kk * 4)); KCK(dp.alloc((size_t)R * kk * 4)); KCK(de.alloc((size_t)R * 4));
   KCK(cudaMemcpy(dl.p, lp.data(), lp.size() * 4, cudaMemcpyHostToDevice));
-  TopkOut o{di.as<int32_t>(), dp.as<float>(), de.as<float>()};
+  TopkOut o{di.as<int32_t>(), dp.as<float>(), de.as<float>(), nullptr};
   KCK(launch_softmax_topk(dl.as<float>(), Vp, V, kk, R, o, 1, 0));
   KCK(cudaDeviceSynchronize());
   KCK(cudaMemcpy(idx, di.p, (size_t)R * kk * 4, cudaMemcpyDeviceToHost));

@@ -259,6 +259,7 @@ struct TopkOut {
   int32_t* idx;    // [rows][kk]
   float* logp;     // [rows][kk]
   float* eos_logp; // [rows]
+  float* row_stats; // [rows][2] = (max, log sum exp(z - max)) of the row, may be null
 };
 __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
 
@@ -327,6 +328,7 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
     for (int w = 0; w < 8; ++w) bs += s_red[w];
     s_lse = normalise ? logf(bs) : -rmax;   // normalise = 0: the row already holds log-probabilities
     if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
+    if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
   }
   __syncthreads();
   const float rlse = s_lse;
@@ -458,6 +460,8 @@ struct TraceDev {
   int32_t* cand_tok; float* cand_logp; int32_t* surv_tok; int32_t* surv_parent; float* surv_score; float* final_logp;
   const int32_t* force_tok; const int32_t* force_parent; const float* force_score;
   int Tm;
+  float* gold_logp;          // [n][Tm][k] log-probability of the forced token of every slot (scoring)
+  const float* logits; int ld_logits; const float* row_stats;   // what gold_logp is computed from
 };
 // grid = active sentences, block = 256, dynamic smem = k*kk*24 + 8 bytes
 static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_logp,
@@ -557,7 +561,14 @@ static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, c
     float nscore = s_nscore[b];
     const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
     if (tr.surv_tok) { tr.surv_tok[off] = ntok; tr.surv_parent[off] = npar; tr.surv_score[off] = nscore; }
-    if (tr.force_tok) { ntok = tr.force_tok[off]; npar = tr.force_parent[off]; nscore = tr.force_score[off]; }
+    if (tr.force_tok) {
+      ntok = tr.force_tok[off]; npar = tr.force_parent[off]; nscore = tr.force_score[off];
+      if (tr.gold_logp && tr.logits) {
+        const int prow = r0 + (npar >= 0 && npar < k ? npar : 0);
+        const int gt = ntok >= 0 ? ntok : 0;
+        tr.gold_logp[off] = (tr.logits[(size_t)prow * tr.ld_logits + gt] - tr.row_stats[2 * prow]) - tr.row_stats[2 * prow + 1];
+      }
+    }
     bs.tok[r0 + b] = ntok; bs.parent[r0 + b] = npar; bs.score[r0 + b] = nscore;
     bs.hist_tok[(size_t)t * bs.R + r0 + b] = ntok;
     bs.hist_parent[(size_t)t * bs.R + r0 + b] = npar;

@@ -114,6 +114,23 @@ class Decoder:
                                                  C.c_void_p(d_score_ptr))
         self._check(rc, "linmt_decode_batch_device")
 
+    def score(self, sents, targets):
+        """Force-decoding: log p(target | source) per sentence and per token (EOS last).
+        ``targets`` = list of id sequences without START / EOS."""
+        n = sents.n
+        ids = np.ascontiguousarray(sents.ids, np.int32)
+        off = np.ascontiguousarray(sents.off, np.int32)
+        tl = [len(t) for t in targets]
+        toff = np.zeros(n + 1, np.int32)
+        toff[1:] = np.cumsum(tl)
+        tids = np.ascontiguousarray(np.concatenate([np.asarray(t, np.int32) for t in targets]), np.int32)
+        mt = max(tl)
+        total = np.zeros(n, np.float32)
+        per_tok = np.zeros((n, mt + 1), np.float32)
+        rc = self._lib.linmt_score_batch(self._h, _ptr(ids), _ptr(off), _ptr(tids), _ptr(toff), n, _ptr(total), _ptr(per_tok), mt)
+        self._check(rc, "linmt_score_batch")
+        return total, per_tok
+
     def stats(self):
         s = _lib.StatsC()
         self._lib.linmt_get_stats(self._h, C.byref(s))

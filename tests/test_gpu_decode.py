@@ -312,3 +312,62 @@ def test_file_mode_matches_checker(oracle, cuda_lib, tmp_path):
             assert fields[0] == " ".join(tgt[t] for t in o["tok"][0, q, 1:n - 1])
             assert abs(float(fields[1]) - float(o["score"][0, q])) <= 1.5e-3
             assert len(fields[1].split(".")[1]) == 3
+
+
+import functools
+
+
+@functools.lru_cache(maxsize=1)
+def _c4_blob():
+    return synth.configs()["C4"].blobs()[0]
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_c4_shape_subset(oracle, cuda_lib, precision):
+    """The large-vocabulary configuration (4 x 1024, 80k vocabulary, beam 5, global dot attention):
+    3 sentences against the checker, fp32 at the fp32 bar and bf16 at the bf16 bar."""
+    from parity import ATOL_BF16
+    from linmt_b200 import decoder
+    c = synth.configs()["C4"]
+    blob = _c4_blob()
+    sents = c.sentences(8).subset(range(3))
+    kw = dict(beam=c.beam, nbest=1, lp_alpha=0.65, cp_beta=0.0, attention="global_dot", precision=precision)
+    o = oracle.decode(c.desc, [blob], sents, trace=True, **kw)
+    dec = decoder.Decoder(c.desc, [blob], max_batch=4, max_src_len=104, max_steps=170, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    if precision == "fp32":
+        worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
+        assert worst <= RTOL_FP32 and bad == 0, (worst, bad, skipped, compared)
+        free = dec.decode(sents)
+        assert token_identity(free, o, sents.n) >= 0.66
+    else:
+        early = []
+        for i in range(sents.n):
+            err = np.abs(forced["cand_logp"][i, :16] - o["cand_logp"][i, :16])
+            err[0, 1:] = 0
+            early.append(err.ravel())
+        early = np.concatenate(early)
+        assert (early <= ATOL_BF16).mean() >= 0.99, float((early <= ATOL_BF16).mean())
+    dec.close()
+
+
+def test_force_decoding_scores(oracle, cuda_lib, c1):
+    """linmt_score_batch (the reference's force-decoding): scoring the checker's own greedy output
+    must give back, token by token, the log-probabilities the checker assigned while producing it;
+    and the score of any first token equals the full first-step distribution's entry."""
+    from linmt_b200 import decoder
+    c, blob, sents = c1
+    o = oracle.decode(c.desc, [blob], sents, beam=1, nbest=1, lp_alpha=0.0, cp_beta=0.0, min_ratio=0.0, trace=True, full_logp=True)
+    dec = _decoder(c, blob, beam=3, lp_alpha=0.0, cp_beta=0.0)
+    targets = [list(o["surv_tok"][i, :int(sents.steps[i]), 0]) for i in range(sents.n)]
+    total, per_tok = dec.score(sents, targets)
+    for i in range(sents.n):
+        T = int(sents.steps[i])
+        pick = [int(np.nonzero(o["cand_tok"][i, t, 0] == targets[i][t])[0][0]) for t in range(T)]
+        ref = np.concatenate([[o["cand_logp"][i, t, 0, pick[t]] for t in range(T)], [o["final_logp"][i, 0]]])
+        np.testing.assert_allclose(per_tok[i, :T + 1], ref, rtol=RTOL_FP32)
+        assert abs(total[i] - ref.sum()) <= RTOL_FP32 * abs(ref.sum())
+    # an arbitrary (not top-ranked) first token
+    total1, per1 = dec.score(sents, [[7] for _ in range(sents.n)])
+    np.testing.assert_allclose(per1[:, 0], o["logp_full"][:, 0, 0, 7], rtol=RTOL_FP32)
+    dec.close()
