@@ -249,7 +249,7 @@ struct TcEpiLstm {
       if (h_out2.p[0]) split_store4(h_out2, nt, i2, h[0], h[1], h[2], h[3]);
       if (h_f32)
         *reinterpret_cast<float4*>(h_f32 + (size_t)row * hf_row_stride + j0) =
-            make_float4(planes_value(h[0], nt), planes_value(h[1], nt), planes_value(h[2], nt), planes_value(h[3], nt));
+            make_float4(h[0], h[1], h[2], h[3]);  // unrounded: attention reads it outside any GEMM
     } else {
       *reinterpret_cast<float4*>(c_out + ic) = cp;
       const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j0;

@@ -18,7 +18,7 @@ def token_identity(a, b, n):
     return same / max(n, 1)
 
 
-def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_len=None, D=10):
+def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_len=None, D=10, t_lo=0, t_hi=None):
     """Engine ran with its beam forced to the checker's survivors: every step's per-beam
     top-(k+1) must then agree.
 
@@ -29,6 +29,11 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
     ``pt_eps`` of an integer n whose window edge lies inside the sentence (n > D or n + D < S),
     the hypothesis and its descendants are left out of the comparison (and counted); everything
     else must agree.
+
+    Only steps t_lo <= t < t_hi are compared (all by default).  On the seeded random weights the
+    recurrence amplifies rounding noise by about 2x every 10 steps (the fp32 checker against the
+    float64 restatement: 1e-6 at step 0, 1e-4 near step 70, 1e-2 near step 150), so the fp32
+    tolerance can only be asked of the first ~60 steps of a long sentence.
 
     Returns (max relative log-prob error, mismatches that are not near-ties, row-steps left out,
     row-steps compared)."""
@@ -46,6 +51,8 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
                 S = int(src_len[i]) if src_len is not None else 10 ** 9
                 taint = taint | ((frac < pt_eps) & ((nn > D) | (nn + D < S)))
             cols = 1 if t == 0 else k
+            if t < t_lo or (t_hi is not None and t >= t_hi):
+                cols = 0
             for b in range(cols):
                 if taint[b]:
                     skipped += 1
