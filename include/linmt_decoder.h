@@ -40,10 +40,12 @@ enum { LINMT_OK = 0, LINMT_EINVAL = 1, LINMT_ECUDA = 2, LINMT_EIO = 3, LINMT_ENO
 enum { LINMT_ATT_LOCAL_P_GENERAL = 0, LINMT_ATT_GLOBAL_GENERAL = 1, LINMT_ATT_GLOBAL_DOT = 2 };
 enum { LINMT_ENS_PROB_MEAN = 0, LINMT_ENS_LOGPROB_MEAN = 1 };
 enum { LINMT_PREC_FP32 = 0, LINMT_PREC_BF16 = 1 };
-/* GEMM kernel family.  SIMT = fp32 CUDA-core kernels (exact fp32 arithmetic).  TENSOR = tcgen05
- * tensor-core kernels; with fp32 precision every operand is split into three bf16 planes
- * (fp32-class accuracy), TENSOR2 uses two planes (error ~2^-17 per product, faster). */
-enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3 };
+/* GEMM kernel family.  SIMT = fp32 CUDA-core kernels (fp32 FMA arithmetic).  TENSOR = tcgen05
+ * tensor-core kernels; with fp32 precision every operand is held as an fp16 pair x ~ a0 + 2^-11 a1
+ * (22 mantissa bits, three partial products per product, fp32-class accuracy; operands must be
+ * below 65504 in magnitude).  TENSOR3 = three bf16 planes (six partial products, same accuracy,
+ * no range limit), TENSOR2 = two bf16 planes (error ~2^-17 per product).  AUTO = TENSOR. */
+enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3, LINMT_GEMM_TENSOR3 = 4 };
 
 /* Model dimensions: first five of the nine integers on line 1 of a model file
  * (src/decoder.h:1202-1210). */
@@ -158,10 +160,14 @@ typedef struct linmt_stats {
   float last_decode_ms;
   float last_gemm_ms;     /* time inside the dominant (vocabulary) GEMM launches, if timing is on */
   int32_t last_gemm_launches;
-  int32_t reserved;
+  int32_t last_rec_gemm_launches; /* decoder LSTM-stack GEMM launches of the last call, if timing is on */
+  float last_rec_gemm_ms;         /* time inside them */
+  float reserved;
+  double last_rec_gemm_flops;     /* their algorithmic flops: 2 * rows * 4H * K per launch */
 } linmt_stats;
 int linmt_get_stats(const linmt_engine* e, linmt_stats* out);
-/* 1 = bracket every vocabulary-GEMM launch with CUDA events (for roofline measurements). */
+/* 1 = bracket every vocabulary-GEMM launch and every decoder LSTM stack with CUDA events
+ * (for roofline measurements). */
 int linmt_set_kernel_timing(linmt_engine* e, int32_t on);
 
 /* Sentence API on a handle: DecoderSentence::Process (src/decoder_sentence.cu:40-49).

@@ -30,7 +30,8 @@ class TraceC(C.Structure):
 class StatsC(C.Structure):
     _fields_ = [("kernel_launches", C.c_int64), ("decoder_row_steps", C.c_int64), ("sentence_steps", C.c_int64),
                 ("last_decode_ms", C.c_float), ("last_gemm_ms", C.c_float), ("last_gemm_launches", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("last_rec_gemm_launches", C.c_int32), ("last_rec_gemm_ms", C.c_float), ("reserved", C.c_float),
+                ("last_rec_gemm_flops", C.c_double)]
 
 
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",

@@ -57,6 +57,7 @@ Engine::~Engine() {
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
   for (auto e : gemm_ev_) cudaEventDestroy(e);
+  for (auto e : rec_ev_) cudaEventDestroy(e);
   for (auto& v : enc_events_) for (auto e : v) cudaEventDestroy(e);
   if (enc_start_ev_) cudaEventDestroy(enc_start_ev_);
   for (auto st : enc_streams_) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
@@ -116,6 +117,13 @@ BlobView view_blob(const linmt_model_desc& d, const float* p) {
 
 int Engine::pack_model(const float* blob, DevModel& m) {
   const BlobView bv = view_blob(desc, blob);
+  if (use_tc_ && fmt_ == 1) {
+    // the fp16 pair cannot hold a weight beyond fp16's range (nor a NaN); trained weights are orders of magnitude below it
+    const size_t nf = (size_t)linmt_blob_floats(&desc);
+    for (size_t i = 0; i < nf; ++i)
+      if (!(std::fabs(blob[i]) <= 60000.0f))
+        return fail(LINMT_EINVAL, "a weight is not finite or exceeds 60000 in magnitude: use gemm_path tensor3 or simt for this model");
+  }
   std::vector<float> host;
   auto upload = [&](float** dst, size_t n) -> int {
     DA(*dst, n);
@@ -223,11 +231,13 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (nm > 8) return fail(LINMT_ELIMIT, "at most 8 ensemble members");
   if (nm > 1 && o.print_info) return fail(LINMT_EINVAL, "alignment output (print_info) is not available with ensembles");
   if (o.precision != LINMT_PREC_FP32 && o.precision != LINMT_PREC_BF16) return fail(LINMT_EINVAL, "bad precision");
-  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR2) return fail(LINMT_EINVAL, "bad gemm_path");
+  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR3) return fail(LINMT_EINVAL, "bad gemm_path");
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
-  nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR2 ? 2 : 3);
+  // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
+  fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR)) ? 1 : 0;
+  nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR3 ? 3 : 2);
   // The vocabulary product feeds only the softmax of its own step (nothing recurrent), so two
   // planes (error ~2^-17 per product, ~3e-7 relative on a log-probability) are enough there:
   // measured parity on the 64-sentence reference configuration is unchanged and the GEMM is 1.3x faster.
@@ -343,6 +353,7 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     LAUNCHED();
   }
   // 2. LSTM stack
+  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   for (int l = 0; l < L; ++l) {
     ASegs a{};
     a.seg_k = Hp;
@@ -356,7 +367,9 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     e.row_len = nullptr; e.pos = 0; e.ld = Hp;
     CK(gemm_simt(a, m.dec_w[l], m.dec_ldw[l], rows, 4 * Hp, a.nseg * Hp, e, stream));
     LAUNCHED();
+    if (kernel_timing) rec_flops_ += 2.0 * rows * 4.0 * H * (double)(a.nseg * H);
   }
+  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   float* htop = s.h_cur[L - 1];
   // 3. attention projections
   const float* u_alt = nullptr;
@@ -395,17 +408,10 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
   {
     ASegs a{}; a.ptr[0] = s.htilde; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
     EpiBias e{m.voc_b, s.logits, Vp};
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (kernel_timing) {
-      if (gemm_ev_used_ + 2 > gemm_ev_.size()) {
-        for (int i = 0; i < 2; ++i) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); gemm_ev_.push_back(ev); }
-      }
-      e0 = gemm_ev_[gemm_ev_used_++]; e1 = gemm_ev_[gemm_ev_used_++];
-      CK(cudaEventRecord(e0, stream));
-    }
+    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
     CK(gemm_simt(a, m.voc_w, Hp, rows, Vp, Hp, e, stream));
     LAUNCHED();
-    if (kernel_timing) CK(cudaEventRecord(e1, stream));
+    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
   }
   return LINMT_OK;
 }
@@ -493,7 +499,7 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     trace_dev_.force_score = trace_dev->force_score; trace_dev_.Tm = trace_Tm;
     trace_dev_.gold_logp = trace_dev->gold_logp;
   }
-  gemm_ev_used_ = 0;
+  gemm_ev_used_ = 0; rec_ev_used_ = 0; rec_flops_ = 0.0;
   int rc = use_tc_ ? run_encoder_tc(n, Smax) : run_encoder(n, Smax);
   if (rc) return rc;
   // the encoder's final states sit in buffer (Smax & 1)
@@ -538,6 +544,21 @@ int Engine::finish_timing() {
     CK(cudaEventElapsedTime(&ms, gemm_ev_[i], gemm_ev_[i + 1]));
     stats.last_gemm_ms += ms;
   }
+  stats.last_rec_gemm_ms = 0.f;
+  stats.last_rec_gemm_launches = (int)(rec_ev_used_ / 2) * L;
+  stats.last_rec_gemm_flops = rec_flops_;
+  for (size_t i = 0; i + 1 < rec_ev_used_; i += 2) {
+    float ms = 0.f;
+    CK(cudaEventElapsedTime(&ms, rec_ev_[i], rec_ev_[i + 1]));
+    stats.last_rec_gemm_ms += ms;
+  }
+  return LINMT_OK;
+}
+
+int Engine::mark(std::vector<cudaEvent_t>& v, size_t& used) {
+  if (!kernel_timing) return LINMT_OK;
+  if (used == v.size()) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); v.push_back(ev); }
+  CK(cudaEventRecord(v[used++], stream));
   return LINMT_OK;
 }
 

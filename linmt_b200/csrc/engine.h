@@ -109,6 +109,7 @@ class Engine {
   std::vector<std::vector<cudaEvent_t>> enc_events_;
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
+  int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair
   int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)
   int n_sm_ = 148;
   int* d_tc_err_ = nullptr;
@@ -152,8 +153,10 @@ class Engine {
   // trace buffers (device), sized on demand
   std::vector<void*> trace_allocs_;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
-  std::vector<cudaEvent_t> gemm_ev_;
-  size_t gemm_ev_used_ = 0;
+  std::vector<cudaEvent_t> gemm_ev_, rec_ev_;   // begin/end pairs: vocabulary GEMM, decoder LSTM stack
+  size_t gemm_ev_used_ = 0, rec_ev_used_ = 0;
+  double rec_flops_ = 0.0;
+  int mark(std::vector<cudaEvent_t>& v, size_t& used);   // records the next event when kernel timing is on
 };
 
 // host-side weight packing

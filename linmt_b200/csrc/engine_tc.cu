@@ -23,6 +23,7 @@ namespace linmt {
 int Engine::alloc_planes(tc::Planes& p, size_t rows, int ld) {
   p = tc::Planes{};
   p.ld = ld;
+  p.fmt = fmt_;
   for (int t = 0; t < nt_; ++t) {
     void* q = nullptr;
     const size_t bytes = rows * (size_t)ld * sizeof(__nv_bfloat16);
@@ -101,17 +102,21 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   int bn = 0, splits = 1;
   const size_t ws_floats = kSplitKWsFloats / ws_parts_;
   const int max_tiles = kSplitKMaxTiles / ws_parts_;
-  tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits);
+  tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits, fmt_);
   // one plane (bf16 precision): 64-deep stages with 128-byte rows halve the per-k-block overheads
   // (measured 1.5x on the gate GEMMs); with split operands only 32-deep stages leave room for a ring
-  const int bk = (nt == 1) ? 64 : 32;
+  // the f16 pair: 64-deep stages as well, except for a weight matrix far larger than L2 under
+  // the widest tiles, where only two such stages fit and four 32-deep ones hide DRAM latency better
+  // (vocabulary GEMM: 143 us against 149 us)
+  int bk = (nt == 1) ? 64 : 32;
+  if (fmt_ == 1 && K % 64 == 0) bk = (bn >= 240 && (size_t)N * K * 4 > ((size_t)96 << 20)) ? 32 : 64;
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K, bk);
   const CUtensorMap* bm = b_maps(W, N, K, bn, bk);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
   tc::TmapSet tm;
   std::memcpy(tm.a, am, sizeof(tm.a));
   std::memcpy(tm.b, bm, sizeof(tm.b));
-  tc::Shape sh = tc::make_shape(bn, nt, bk);
+  tc::Shape sh = tc::make_shape(bn, nt, bk, fmt_);
   sh.splits = splits;
   CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,
                         d_splitk_counters_ + ws_part_ * max_tiles));
@@ -226,6 +231,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     LAUNCHED();
   }
   // 2. LSTM stack
+  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   for (int l = 0; l < L; ++l) {
     tc::TcEpiLstm e{};
     e.bias = m.dec_b[l]; e.c_prev = s.c_prev[l]; e.ldc = Hp; e.c_out = s.c_cur[l];
@@ -238,7 +244,9 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     const int K = (l == 0 && feed) ? 3 * Hp : 2 * Hp;
     int rc = tc_gemm(hprev_planes(l), 0, R, m.p_dec_w[l], rows, 4 * Hp, K, e);
     if (rc) return rc;
+    if (kernel_timing) rec_flops_ += 2.0 * rows * 4.0 * H * (double)((K / Hp) * H);
   }
+  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   // 3. attention projections: tanh(W_p h) | W_a^T h
   const float* u_alt = nullptr;
   if (opt.attention_mode != LINMT_ATT_GLOBAL_DOT) {
@@ -268,16 +276,10 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   // 6. logits
   {
     tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (kernel_timing) {
-      if (gemm_ev_used_ + 2 > gemm_ev_.size())
-        for (int i = 0; i < 2; ++i) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); gemm_ev_.push_back(ev); }
-      e0 = gemm_ev_[gemm_ev_used_++]; e1 = gemm_ev_[gemm_ev_used_++];
-      CK(cudaEventRecord(e0, stream));
-    }
+    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
     int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e, nt_vocab_);
     if (rc) return rc;
-    if (kernel_timing) CK(cudaEventRecord(e1, stream));
+    if ((rc = mark(gemm_ev_, gemm_ev_used_))) return rc;
   }
   return LINMT_OK;
 }

@@ -111,6 +111,7 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
     if (*v == "auto") c.opt.gemm_path = LINMT_GEMM_AUTO;
     else if (*v == "simt") c.opt.gemm_path = LINMT_GEMM_SIMT;
     else if (*v == "tensor") c.opt.gemm_path = LINMT_GEMM_TENSOR;
+    else if (*v == "tensor3") c.opt.gemm_path = LINMT_GEMM_TENSOR3;
     else { err = "--gemm-path must be auto, simt or tensor"; return false; }
   }
   if (auto v = get("--batch-size")) c.opt.max_batch = std::atoi(v->c_str());

@@ -13,6 +13,12 @@
 // second one (their truncation is 2^-8 smaller in absolute terms); the epilogue adds the two.
 // Measured against a float64 product this gives the error of an fp32 FMA loop.
 //
+// Plane format 1 ("f16 pair") reaches the same accuracy with half the tensor work: x ~ a0 + 2^-11 a1
+// with a0 = fp16(x), a1 = fp16((x - a0) * 2^11) -- two 11-bit mantissas, 22 bits in all, the
+// residual scaled back into fp16's normal range -- and three partial products a0b0 (own
+// accumulator), a0b1 + a1b0 (second accumulator, weighted 2^-11 when the two are added); the dropped
+// a1b1 weighs 2^-22.  Operands must stay below fp16's largest finite value (65504).
+//
 // One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) is a launch parameter so
 // the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues the TMA
 // loads, warp 1 owns TMEM and issues the MMAs, warps 2..17 run the epilogue (tcgen05.ld ->
@@ -24,6 +30,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -52,15 +59,16 @@ struct Shape {
   int bn;        // tile width
   int bk;        // K depth of a stage in bf16 elements: 32 (64-byte rows) or 64 (128-byte rows)
   int nt;        // planes per operand
+  int fmt;       // 0 = bf16 planes, 1 = f16 pair
   int stages;
   int stage_bytes;
   int smem_bytes;
   int drain;     // k-blocks between drains of the leading accumulator
   int splits;    // split-K factor (1 = none)
 };
-inline Shape make_shape(int bn, int nt, int bk = BK) {
+inline Shape make_shape(int bn, int nt, int bk = BK, int fmt = 0) {
   Shape s;
-  s.bn = bn; s.nt = nt; s.bk = bk;
+  s.bn = bn; s.nt = nt; s.bk = bk; s.fmt = fmt;
   s.stage_bytes = nt * (BM * bk * 2 + bn * bk * 2);
   s.stages = SMEM_BUDGET / s.stage_bytes;
   if (s.stages > kMaxStages) s.stages = kMaxStages;
@@ -154,17 +162,36 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 }
 // Instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9, 10-12 = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__host__ __device__ inline uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// f16 operands (plane format 1) have format code 0 in both fields.
+__host__ __device__ inline uint32_t make_idesc(int m, int n, int fmt = 0) {
+  const uint32_t ab = fmt ? 0u : ((1u << 7) | (1u << 10));
+  return (1u << 4) | ab | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---- operand planes -----------------------------------------------------------------------
 // An activation or weight matrix as NT bf16 planes with a common leading dimension.
+// fmt 0: p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1).
+// fmt 1: two planes holding fp16 bit patterns, p0 = fp16(x), p1 = fp16((x - p0) * 2048).
 struct Planes {
   __nv_bfloat16* p[3];
   int ld;
+  int fmt;
 };
+constexpr float kF16PairScale = 2048.0f;             // 2^11: the residual plane's scale
+constexpr float kF16PairInvScale = 1.0f / 2048.0f;
+__device__ __forceinline__ void f16_pair(float x, unsigned short& h0, unsigned short& h1) {
+  const __half a0 = __float2half_rn(x);
+  h0 = __half_as_ushort(a0);
+  h1 = __half_as_ushort(__float2half_rn((x - __half2float(a0)) * kF16PairScale));
+}
 __device__ __forceinline__ void split_store(const Planes& pl, int nt, size_t idx, float x) {
+  if (pl.fmt == 1) {
+    unsigned short h0, h1;
+    f16_pair(x, h0, h1);
+    reinterpret_cast<unsigned short*>(pl.p[0])[idx] = h0;
+    reinterpret_cast<unsigned short*>(pl.p[1])[idx] = h1;
+    return;
+  }
   const __nv_bfloat16 b0 = __float2bfloat16_rn(x);
   pl.p[0][idx] = b0;
   if (nt > 1) {
@@ -186,6 +213,14 @@ __device__ __forceinline__ float planes_value(float x, int nt) {
 // Four consecutive values as bf16 planes with one 8-byte store per plane (idx a multiple of 4).
 __device__ __forceinline__ void split_store4(const Planes& pl, int nt, size_t idx, float x0, float x1, float x2, float x3) {
   const float x[4] = {x0, x1, x2, x3};
+  if (pl.fmt == 1) {
+    unsigned short h0[4], h1[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f16_pair(x[i], h0[i], h1[i]);
+    *reinterpret_cast<uint2*>(pl.p[0] + idx) = make_uint2((uint32_t)h0[0] | ((uint32_t)h0[1] << 16), (uint32_t)h0[2] | ((uint32_t)h0[3] << 16));
+    *reinterpret_cast<uint2*>(pl.p[1] + idx) = make_uint2((uint32_t)h1[0] | ((uint32_t)h1[1] << 16), (uint32_t)h1[2] | ((uint32_t)h1[3] << 16));
+    return;
+  }
   float r[4];
   __nv_bfloat16 b[4];
 #pragma unroll
@@ -304,13 +339,21 @@ struct TcEpiF32 {
 __host__ __device__ inline int acc_stride(int bn) { return (bn + 31) & ~31; }
 
 // Partial products (plane of A, plane of B): the small cross terms first, the leading p0p0 last.
-__host__ __device__ constexpr int num_products(int nt) { return nt == 1 ? 1 : (nt == 2 ? 4 : 6); }
+// The first argument is a product-set code: the plane count for bf16 planes, kF16PairCode for the f16 pair.
+constexpr int kF16PairCode = 4;
+__host__ __device__ constexpr int product_code(int nt, int fmt) { return fmt ? kF16PairCode : nt; }
+__host__ __device__ constexpr int num_products(int nt) { return nt == 1 ? 1 : (nt == 2 ? 4 : (nt == kF16PairCode ? 3 : 6)); }
 __host__ __device__ constexpr int prod_a(int nt, int p) {
-  return nt == 3 ? (p == 0 ? 2 : (p == 2 || p == 3) ? 1 : 0) : (nt == 2 ? (p < 2 ? 1 : 0) : 0);
+  return nt == kF16PairCode ? (p == 0 ? 1 : 0)
+                            : nt == 3 ? (p == 0 ? 2 : (p == 2 || p == 3) ? 1 : 0) : (nt == 2 ? (p < 2 ? 1 : 0) : 0);
 }
 __host__ __device__ constexpr int prod_b(int nt, int p) {
-  return nt == 3 ? (p == 1 ? 2 : (p == 2 || p == 4) ? 1 : 0) : (nt == 2 ? ((p == 0 || p == 2) ? 1 : 0) : 0);
+  return nt == kF16PairCode ? (p == 1 ? 1 : 0)
+                            : nt == 3 ? (p == 1 ? 2 : (p == 2 || p == 4) ? 1 : 0) : (nt == 2 ? ((p == 0 || p == 2) ? 1 : 0) : 0);
 }
+static_assert(num_products(kF16PairCode) == 3 && prod_a(kF16PairCode, 0) == 1 && prod_b(kF16PairCode, 0) == 0 &&
+              prod_a(kF16PairCode, 1) == 0 && prod_b(kF16PairCode, 1) == 1 && prod_a(kF16PairCode, 2) == 0 &&
+              prod_b(kF16PairCode, 2) == 0, "f16 pair products: (1,0)(0,1)(0,0)");
 static_assert(prod_a(3, 0) == 2 && prod_b(3, 0) == 0 && prod_a(3, 1) == 0 && prod_b(3, 1) == 2 && prod_a(3, 2) == 1 &&
               prod_b(3, 2) == 1 && prod_a(3, 3) == 1 && prod_b(3, 3) == 0 && prod_a(3, 4) == 0 && prod_b(3, 4) == 1 &&
               prod_a(3, 5) == 0 && prod_b(3, 5) == 0, "NT=3 products: (2,0)(0,2)(1,1)(1,0)(0,1)(0,0)");
@@ -330,11 +373,12 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
 }
 
 // ---- kernel -------------------------------------------------------------------------------
-template <int NT, int BKT, class Epi>
+template <int NT, int BKT, int FMT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, int kDrainEvery, Epi epi,
                int* __restrict__ err_flag, int splits, float* __restrict__ ws, int* __restrict__ tile_counters) {
-  constexpr int NP = num_products(NT);
+  constexpr int PC = product_code(NT, FMT);
+  constexpr int NP = num_products(PC);
   constexpr int A_BYTES = BM * BKT * 2;   // one plane of the A tile of a stage (shadows the 32-deep constant)
   constexpr int BK = BKT;
   extern __shared__ unsigned char smem_raw[];
@@ -397,7 +441,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN);
+      const uint32_t idesc = make_idesc(BM, BN, FMT);
       const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
       const uint64_t bstep = (uint64_t)(B_BYTES >> 4);           // one B plane, in descriptor units (16 bytes)
       int s = 0; uint32_t ph = 0;
@@ -418,8 +462,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
           for (int ks = 0; ks < BK / UMMA_K; ++ks) {
 #pragma unroll
             for (int p = 0; p < NP - 1; ++p) {
-              const uint64_t ad = a0 + (uint64_t)(((prod_a(NT, p) * A_BYTES) >> 4) + ks * 2);
-              const uint64_t bd = b0 + (uint64_t)prod_b(NT, p) * bstep + (uint64_t)(ks * 2);
+              const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
+              const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
               umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
             }
           }
@@ -511,7 +555,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
             float sm[16];
             tmem_ld16(lane_base + astride + (uint32_t)c0, sm);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) macc[ci][i] += sm[i];
+            for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
             emit(c0, macc[ci]);
           }
         }
@@ -598,12 +642,12 @@ inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NT, int BKT, class Epi>
+template <int NT, int BKT, int FMT, class Epi>
 inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                      cudaStream_t st, float* ws, int* counters) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, BKT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, BKT, FMT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
     if (e != cudaSuccess) return e;
     attr_done = true;
   }
@@ -611,21 +655,26 @@ inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, con
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
   int drain = (sh.drain > 0 ? sh.drain : kDrainDefault) * 32 / BKT;
   if (drain < 1) drain = 1;
-  gemm_tc_kernel<NT, BKT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, drain, epi, err_flag,
+  gemm_tc_kernel<NT, BKT, FMT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, drain, epi, err_flag,
                                                                   splits, splits > 1 ? ws : nullptr, counters);
   return cudaGetLastError();
 }
 template <class Epi>
 inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                   cudaStream_t st, float* ws = nullptr, int* counters = nullptr) {
+  if (sh.fmt == 1) {
+    if (sh.nt != 2) return cudaErrorInvalidValue;
+    if (sh.bk == 64) return launch_gemm_tc_nt<2, 64, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    return launch_gemm_tc_nt<2, 32, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  }
   if (sh.bk == 64) {
-    if (sh.nt == 2) return launch_gemm_tc_nt<2, 64, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
-    if (sh.nt == 1) return launch_gemm_tc_nt<1, 64, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    if (sh.nt == 2) return launch_gemm_tc_nt<2, 64, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    if (sh.nt == 1) return launch_gemm_tc_nt<1, 64, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
     return cudaErrorInvalidValue;  // three planes of 128-byte rows leave room for one stage only
   }
-  if (sh.nt == 3) return launch_gemm_tc_nt<3, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
-  if (sh.nt == 2) return launch_gemm_tc_nt<2, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
-  return launch_gemm_tc_nt<1, 32, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  if (sh.nt == 3) return launch_gemm_tc_nt<3, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  if (sh.nt == 2) return launch_gemm_tc_nt<2, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+  return launch_gemm_tc_nt<1, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
 }
 
 // Tile width that fills the SMs best for an M x N problem: the smallest makespan
@@ -651,10 +700,38 @@ inline int pick_bn(int M, int N, int n_sm) {
 // waves * (k-blocks-per-CTA of those + ~8-13 us of prologue/epilogue per tile), plus the cost of
 // writing and re-reading partial tiles when K is split (only worth it for tiles up to 176 wide).
 // ws_floats bounds the split-K workspace (splits * padded rows * N floats).
-inline void pick_shape(int M, int N, int K, int nt, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out) {
+// The f16 pair runs 64-deep stages (128-byte rows) and is bound by shared-memory bandwidth rather
+// than by the tensor pipe: per k-block a CTA writes planes * (128 + bn) * 128 bytes (TMA) and the
+// twelve MMAs read 128 * 32 + bn * 32 bytes each, at 128 bytes per clock (measured slopes:
+// 770 ns per k-block at bn = 176, 1040 ns at bn = 256); per tile ~6 us + 12 ns per column of
+// prologue and epilogue; a split costs the partial tile's round trip.
+inline void pick_shape_f16(int M, int N, int K, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out) {
+  const int mt = (M + BM - 1) / BM;
+  const int nkb = K / 64;
+  double best = 1e30;
+  int best_bn = 256, best_s = 1;
+  for (int bn = 256; bn >= 64; bn -= 16) {
+    const long tiles = (long)mt * ((N + bn - 1) / bn);
+    const double smem_ns = (12.0 * (BM * 32 + bn * 32) + 2.0 * (BM + bn) * 128.0) / 128.0 / 1.84;
+    const double issue_ns = 12.0 * 50.0;
+    const double per_kb = smem_ns > issue_ns ? smem_ns : issue_ns;
+    for (int s = 1; s <= 6; ++s) {
+      if (s > 1 && (bn > 208 || nkb / s < 2 || tiles > max_tiles || (size_t)s * mt * BM * (size_t)N > ws_floats)) break;
+      const long waves = (tiles * s + n_sm - 1) / n_sm;
+      const double kb_per_cta = (double)((nkb + s - 1) / s);
+      const double cost = waves * (kb_per_cta * per_kb + 6000.0 + bn * 12.0) + (s > 1 ? 4000.0 + 2000.0 * s + bn * 10.0 * (s + 1) : 0.0);
+      if (cost < best - 1e-9) { best = cost; best_bn = bn; best_s = s; }
+    }
+  }
+  *bn_out = best_bn;
+  *splits_out = best_s;
+}
+
+inline void pick_shape(int M, int N, int K, int nt, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out, int fmt = 0) {
+  if (fmt == 1 && K % 64 == 0) { pick_shape_f16(M, N, K, n_sm, ws_floats, max_tiles, bn_out, splits_out); return; }
   const int mt = (M + BM - 1) / BM;
   const int nkb = K / BK;
-  const int np = num_products(nt);
+  const int np = num_products(product_code(nt, fmt));
   double best = 1e30;
   int best_bn = 256, best_s = 1;
   for (int bn = 256; bn >= 48; bn -= 16) {

@@ -26,7 +26,8 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
   using namespace linmt;
   if (!X || !W || !Y || R < 1 || K < 1 || N < 1) return LINMT_EINVAL;
   if (gemm_path == LINMT_GEMM_SIMT && precision != LINMT_PREC_FP32) return LINMT_EINVAL;
-  if (gemm_path != LINMT_GEMM_SIMT && gemm_path != LINMT_GEMM_TENSOR && gemm_path != LINMT_GEMM_TENSOR2) return LINMT_EINVAL;
+  if (gemm_path != LINMT_GEMM_SIMT && gemm_path != LINMT_GEMM_TENSOR && gemm_path != LINMT_GEMM_TENSOR2 &&
+      gemm_path != LINMT_GEMM_TENSOR3) return LINMT_EINVAL;
   KCK(cudaSetDevice(device));
   const int Kp = round_up(K, 64), Np = round_up(N, 128);
   std::vector<float> xp((size_t)R * Kp, 0.f), wt((size_t)Np * Kp, 0.f);
@@ -43,10 +44,11 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     KCK(gemm_simt(a, dw.as<float>(), Kp, R, Np, Kp, e, 0));
     KCK(cudaDeviceSynchronize());
   } else {
-    const int nt = (precision == LINMT_PREC_BF16) ? 1 : (gemm_path == LINMT_GEMM_TENSOR2 ? 2 : 3);
+    const int fmt = (precision == LINMT_PREC_FP32 && gemm_path == LINMT_GEMM_TENSOR) ? 1 : 0;
+    const int nt = (precision == LINMT_PREC_BF16) ? 1 : (gemm_path == LINMT_GEMM_TENSOR3 ? 3 : 2);
     DevBuf pa[3], pb[3], derr;
     tc::Planes A{}, B{};
-    A.ld = Kp; B.ld = Kp;
+    A.ld = Kp; B.ld = Kp; A.fmt = fmt; B.fmt = fmt;
     for (int t = 0; t < nt; ++t) {
       KCK(pa[t].alloc(xp.size() * 2)); KCK(pb[t].alloc(wt.size() * 2));
       A.p[t] = pa[t].as<__nv_bfloat16>(); B.p[t] = pb[t].as<__nv_bfloat16>();
@@ -57,7 +59,7 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     tc::split_planes_kernel<<<1024, 256>>>(dw.as<float>(), B, nt, wt.size());
     KCK(cudaGetLastError());
     const char* bk_env = std::getenv("LINMT_TC_BK");   // test knob: stage depth 64 (128-byte rows) for <= 2 planes
-    const int bk = (bk_env && std::atoi(bk_env) == 64 && nt <= 2) ? 64 : 32;
+    const int bk = (fmt == 1 || (bk_env && std::atoi(bk_env) == 64 && nt <= 2)) ? 64 : 32;
     tc::TmapSet tm{};
     for (int t = 0; t < nt; ++t) {
       if (!tc::make_tmap(&tm.a[t], A.p[t], R, Kp, Kp, tc::BM, bk)) return LINMT_ECUDA;
@@ -66,12 +68,12 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     tc::TcEpiF32 e{nullptr, dy.as<float>(), Np, 0};
     int bn = 0, splits = 1;
     const size_t ws_floats = (size_t)16 << 20;
-    tc::pick_shape(R, Np, Kp, nt, 148, ws_floats, 4096, &bn, &splits);
+    tc::pick_shape(R, Np, Kp, nt, 148, ws_floats, 4096, &bn, &splits, fmt);
     DevBuf dws, dcnt;
     KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
     for (int t = 0; t < nt; ++t)
       if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn, bk)) return LINMT_ECUDA;
-    tc::Shape sh = tc::make_shape(bn, nt, bk);
+    tc::Shape sh = tc::make_shape(bn, nt, bk, fmt);
     sh.splits = splits;
     cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>());
     KCK(le);
@@ -117,16 +119,18 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
   if (max_stages >= 10000) { force_splits = max_stages / 10000; max_stages %= 10000; }  // tuning: splits * 10000
   if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }                 // + drain * 100 + stages
   using namespace linmt;
+  int fmt = 0;
+  if (nt == tc::kF16PairCode) { fmt = 1; nt = 2; }   // nt = 4: the f16 pair format
   if (R < 1 || K < 32 || N < 16 || nt < 1 || nt > 3 || iters < 1 || !ms_out) return LINMT_EINVAL;
   if (K % 32 || N % 16) return LINMT_EINVAL;
   KCK(cudaSetDevice(device));
   int splits = 1;
   const size_t ws_floats = (size_t)16 << 20;
-  if (bn <= 0) tc::pick_shape(R, N, K, nt, 148, ws_floats, 4096, &bn, &splits);
+  if (bn <= 0) tc::pick_shape(R, N, K, nt, 148, ws_floats, 4096, &bn, &splits, fmt);
   if (bn % 16 || bn > 256) return LINMT_EINVAL;
   DevBuf pa[3], pb[3], dy, derr;
   tc::Planes A{}, B{};
-  A.ld = K; B.ld = K;
+  A.ld = K; B.ld = K; A.fmt = fmt; B.fmt = fmt;
   for (int t = 0; t < nt; ++t) {
     KCK(pa[t].alloc((size_t)R * K * 2)); KCK(pb[t].alloc((size_t)N * K * 2));
     KCK(cudaMemset(pa[t].p, 0x3c, (size_t)R * K * 2)); KCK(cudaMemset(pb[t].p, 0x3c, (size_t)N * K * 2));
@@ -140,10 +144,16 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
     if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM, bk)) return LINMT_ECUDA;
     if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn, bk)) return LINMT_ECUDA;
   }
-  tc::Shape sh = tc::make_shape(bn, nt, bk);
+  tc::Shape sh = tc::make_shape(bn, nt, bk, fmt);
   if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
   if (drain > 0) sh.drain = drain;
   sh.splits = force_splits > 0 ? force_splits : splits;
+  {
+    // a forced split must fit the workspace and the tile counters, as the engine's own choice does
+    const size_t mt = (size_t)((R + tc::BM - 1) / tc::BM), ntile = (size_t)((N + bn - 1) / bn);
+    if (sh.splits > 1 && ((size_t)sh.splits * mt * tc::BM * (size_t)N > ws_floats || mt * ntile > 4096 || (K / bk) / sh.splits < 1))
+      return LINMT_ELIMIT;
+  }
   tc::TcEpiF32 e{nullptr, dy.as<float>(), N, 0};
   cudaEvent_t e0, e1;
   KCK(cudaEventCreate(&e0)); KCK(cudaEventCreate(&e1));

@@ -47,10 +47,11 @@ def test_softmax_topk_ties_lowest_index(oracle, cuda_lib):
 
 
 @pytest.mark.parametrize("R,K,N", [(12, 128, 512), (72, 1000, 30000), (768, 3000, 4000), (131, 257, 391)])
-@pytest.mark.parametrize("path,prec,tol", [("tensor", "fp32", 1e-6), ("tensor2", "fp32", 4e-6), ("tensor", "bf16", 4e-3)])
+@pytest.mark.parametrize("path,prec,tol", [("tensor", "fp32", 1e-6), ("tensor3", "fp32", 1e-6), ("tensor2", "fp32", 4e-6), ("tensor", "bf16", 4e-3)])
 def test_gemm_tensor_vs_checker(oracle, cuda_lib, R, K, N, path, prec, tol):
-    """tcgen05 GEMM on bf16 planes against a float64 product: three planes give the error of an
-    fp32 FMA loop, two planes ~2^-17 per product, one plane is plain bf16."""
+    """tcgen05 GEMM on split operands against a float64 product: the fp16 pair (default) and three
+    bf16 planes give the error of an fp32 FMA loop, two bf16 planes ~2^-17 per product, one plane is
+    plain bf16."""
     from linmt_b200 import decoder
     rng = np.random.default_rng(R + K + N)
     X = rng.uniform(-1, 1, (R, K)).astype(np.float32)
