@@ -66,13 +66,20 @@ struct Shape {
   int drain;     // k-blocks between drains of the leading accumulator
   int splits;    // split-K factor (1 = none)
 };
+// Dynamic shared memory of a launch: the stage ring (which the epilogue warps reuse as their
+// staging areas once the accumulator is complete, kEpiStagingBytes in all), alignment slack, barriers.
+constexpr int kEpiStagingBytes = kEpiWarps * 9728;
+__host__ __device__ inline int ring_bytes(int stages, int stage_bytes) {
+  return stages * stage_bytes > kEpiStagingBytes ? stages * stage_bytes : kEpiStagingBytes;
+}
+inline int shape_smem_bytes(int stages, int stage_bytes) { return ring_bytes(stages, stage_bytes) + 1024 + 256; }
 inline Shape make_shape(int bn, int nt, int bk = BK, int fmt = 0) {
   Shape s;
   s.bn = bn; s.nt = nt; s.bk = bk; s.fmt = fmt;
   s.stage_bytes = nt * (BM * bk * 2 + bn * bk * 2);
   s.stages = SMEM_BUDGET / s.stage_bytes;
   if (s.stages > kMaxStages) s.stages = kMaxStages;
-  s.smem_bytes = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  s.smem_bytes = shape_smem_bytes(s.stages, s.stage_bytes);
   s.drain = kDrainDefault;
   s.splits = 1;
   return s;
@@ -240,10 +247,31 @@ __device__ __forceinline__ void split_store4(const Planes& pl, int nt, size_t id
   }
 }
 
-// Activation functions: the libm-accurate forms, as on the CUDA-core path (the approximate
-// ex2/rcp forms were measured to save only ~2% of a decode).
-__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + expf(-x)); }
-__device__ __forceinline__ float tanh_fast(float x) { return tanhf(x); }
+// Activation functions of the fused epilogues.  The hardware exponential (ex2.approx, 2 ulp) and
+// reciprocal keep the ABSOLUTE error of both below ~1.5e-7 -- what the matrix products that consume h
+// care about -- at a third of the instructions of expf / tanhf; around zero, where
+// 1 - 2 / (1 + e^2x) would cancel, tanh uses its odd series instead (relative error < 1e-7 for |x| < 0.25).
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float x2 = x * x;
+  // x - x^3/3 + 2x^5/15 - 17x^7/315 + 62x^9/2835
+  float p = fmaf(x2, 62.0f / 2835.0f, -17.0f / 315.0f);
+  p = fmaf(x2, p, 2.0f / 15.0f);
+  p = fmaf(x2, p, -1.0f / 3.0f);
+  p = fmaf(x2 * x, p, x);
+  const float big = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x));
+  return x2 < 0.0625f ? p : big;
+}
+
+// Per-warp staging area of the epilogue (lives in the idle pipeline stages once the accumulator is
+// complete): the tcgen05.ld layout gives every lane one ROW of the tile, so a direct store touches
+// 32 different lines per instruction; staging a block of up to 64 columns and storing it back
+// with consecutive lanes on consecutive addresses cuts the memory-pipe passes 4-8x (measured: the
+// epilogue was 7.6-7.9 us of a 29-36 us tile).
+constexpr int kEpiBlockChunks = 4;                       // 16-column chunks a warp owns at most
+constexpr int kEpiScratchStride = 68;                    // floats per staged row (64 + 4: conflict-free float4 rows)
+constexpr int kEpiScratchBytes = kEpiStagingBytes / kEpiWarps;   // per warp: 32 x 68 floats, or the LSTM epilogue's c | h planes | h
+static_assert(kEpiScratchBytes >= 32 * kEpiScratchStride * 4 && kEpiScratchBytes >= (32 * 20 + 3 * 32 * 12 + 32 * 20) * 4, "staging area");
 
 // LSTM cell update on gate-interleaved columns (see EpiLstm in gemm_simt.cuh for the math and
 // the reference kernels it replaces).  A call covers 16 columns = 4 hidden units, so every
@@ -297,6 +325,95 @@ struct TcEpiLstm {
         }
     }
   }
+  // A warp's block: rows row0 .. row0+31 (lane = row), nch chunks of 16 accumulator columns from
+  // col_first, i.e. nu = 4 * nch hidden units from j_first = col_first / 4.  v[ci] = chunk ci of
+  // this lane's row.  sbuf = this warp's staging area.  c_prev comes in and c goes out through
+  // the staging area with consecutive lanes on consecutive addresses; h goes out as planes the
+  // same way.  Rows past their length (encoder) keep c and copy h_prev.
+  static constexpr bool kHasBlock = true;
+  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf) const {
+    const int nq = nch;                      // float4 groups (4 hidden units each) per row
+    const int j_first = col_first >> 2;
+    const int row = row0 + lane;
+    const bool valid = row < M;
+    const bool active = valid && ((row_len == nullptr) || (pos < row_len[row]));
+    float* cs = sbuf;                                            // [32][20] floats: c_prev in, c out
+    unsigned short* hs = reinterpret_cast<unsigned short*>(sbuf + 32 * 20);   // [planes][32][24] 16-bit
+    float* hf = sbuf + 32 * 20 + 3 * 32 * 12;                    // [32][20] floats: h in fp32 (only if h_f32)
+    // c_prev: coalesced load into the staging area
+    for (int s = lane; s < 32 * nq; s += 32) {
+      const int r = s / nq, g = s - r * nq;
+      if (row0 + r < M)
+        *reinterpret_cast<float4*>(cs + r * 20 + 4 * g) =
+            *reinterpret_cast<const float4*>(c_prev + (size_t)(row0 + r) * ldc + j_first + 4 * g);
+    }
+    __syncwarp();
+    if (active) {
+#pragma unroll
+      for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
+        if (ci < nch) {
+          const float4 cp = *reinterpret_cast<const float4*>(cs + lane * 20 + 4 * ci);
+          const float cpv[4] = {cp.x, cp.y, cp.z, cp.w};
+          float c[4], h[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float4 b = *reinterpret_cast<const float4*>(bias + col_first + 16 * ci + 4 * u);
+            const float gi = sigmoid_fast(v[ci][4 * u + 0] + b.x);
+            const float gf = sigmoid_fast(v[ci][4 * u + 1] + b.y);
+            const float gg = tanh_fast(v[ci][4 * u + 2] + b.z);
+            const float go = sigmoid_fast(v[ci][4 * u + 3] + b.w);
+            c[u] = gf * cpv[u] + gi * gg;
+            h[u] = go * tanh_fast(c[u]);
+          }
+          *reinterpret_cast<float4*>(cs + lane * 20 + 4 * ci) = make_float4(c[0], c[1], c[2], c[3]);
+          if (h_f32) *reinterpret_cast<float4*>(hf + lane * 20 + 4 * ci) = make_float4(h[0], h[1], h[2], h[3]);
+          // planes of h: 4 units = 8 bytes per plane
+          unsigned short q0[4], q1[4], q2[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (h_out1.fmt == 1) { f16_pair(h[u], q0[u], q1[u]); q2[u] = 0; }
+            else {
+              const __nv_bfloat16 b0 = __float2bfloat16_rn(h[u]);
+              const float r1 = h[u] - __bfloat162float(b0);
+              const __nv_bfloat16 b1 = __float2bfloat16_rn(r1);
+              q0[u] = __bfloat16_as_ushort(b0); q1[u] = __bfloat16_as_ushort(b1);
+              q2[u] = __bfloat16_as_ushort(__float2bfloat16_rn(r1 - __bfloat162float(b1)));
+            }
+          }
+          *reinterpret_cast<uint2*>(hs + (0 * 32 + lane) * 24 + 4 * ci) = make_uint2(q0[0] | ((uint32_t)q0[1] << 16), q0[2] | ((uint32_t)q0[3] << 16));
+          if (nt > 1) *reinterpret_cast<uint2*>(hs + (1 * 32 + lane) * 24 + 4 * ci) = make_uint2(q1[0] | ((uint32_t)q1[1] << 16), q1[2] | ((uint32_t)q1[3] << 16));
+          if (nt > 2) *reinterpret_cast<uint2*>(hs + (2 * 32 + lane) * 24 + 4 * ci) = make_uint2(q2[0] | ((uint32_t)q2[1] << 16), q2[2] | ((uint32_t)q2[3] << 16));
+        }
+      }
+    } else if (valid) {
+      // past the end of this row's sentence: c stays (already staged), h = h_prev
+      const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j_first;
+      for (int t = 0; t < nt; ++t)
+        for (int g = 0; g < nch; ++g)
+          *reinterpret_cast<uint2*>(hs + (t * 32 + lane) * 24 + 4 * g) = *reinterpret_cast<const uint2*>(h_prev.p[t] + ip + 4 * g);
+    }
+    const unsigned active_mask = __ballot_sync(0xffffffffu, active);
+    __syncwarp();
+    // coalesced stores
+    for (int s = lane; s < 32 * nq; s += 32) {
+      const int r = s / nq, g = s - r * nq;
+      if (row0 + r < M) {
+        *reinterpret_cast<float4*>(c_out + (size_t)(row0 + r) * ldc + j_first + 4 * g) = *reinterpret_cast<const float4*>(cs + r * 20 + 4 * g);
+        if (h_f32 && ((active_mask >> r) & 1u))
+          *reinterpret_cast<float4*>(h_f32 + (size_t)(row0 + r) * hf_row_stride + j_first + 4 * g) = *reinterpret_cast<const float4*>(hf + r * 20 + 4 * g);
+      }
+    }
+    for (int t = 0; t < nt; ++t)
+      for (int s = lane; s < 32 * nq; s += 32) {
+        const int r = s / nq, g = s - r * nq;
+        if (row0 + r < M) {
+          const uint2 hv = *reinterpret_cast<const uint2*>(hs + (t * 32 + r) * 24 + 4 * g);
+          *reinterpret_cast<uint2*>(h_out1.p[t] + (size_t)(row0 + r) * h_out1.ld + h1_col0 + j_first + 4 * g) = hv;
+          if (h_out2.p[0]) *reinterpret_cast<uint2*>(h_out2.p[t] + (size_t)(row0 + r) * h_out2.ld + h2_col0 + j_first + 4 * g) = hv;
+        }
+      }
+    __syncwarp();
+  }
 };
 
 // out = tanh(acc + bias) as bf16 planes (the attentional state).
@@ -304,6 +421,8 @@ struct TcEpiBiasTanh {
   const float* bias;
   Planes out; int col_off;
   int nt;
+  static constexpr bool kHasBlock = false;
+  __device__ __forceinline__ void block(int, int, int, int, int, float (*)[16], float*) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
     const size_t idx = (size_t)row * out.ld + col_off + col0;
 #pragma unroll
@@ -332,6 +451,36 @@ struct TcEpiF32 {
       if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
       *reinterpret_cast<float4*>(o + 4 * q) = r;
     }
+  }
+  // Block form (see TcEpiLstm::block): bias / tanh in registers, the block of up to 64 columns
+  // staged per row, then stored with a row's 16 float4 on consecutive lanes.
+  static constexpr bool kHasBlock = true;
+  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf) const {
+#pragma unroll
+    for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
+      if (ci < nch) {
+        const int col0 = col_first + 16 * ci;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float4 r = make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]);
+          if (bias) {
+            const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
+            r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+          }
+          if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
+          *reinterpret_cast<float4*>(sbuf + lane * kEpiScratchStride + 16 * ci + 4 * q) = r;
+        }
+      }
+    }
+    __syncwarp();
+    const int nq = 4 * nch;   // float4 per row
+    for (int s = lane; s < 32 * nq; s += 32) {
+      const int r = s / nq, g = s - r * nq;
+      if (row0 + r < M)
+        *reinterpret_cast<float4*>(out + (size_t)(row0 + r) * ld + col_first + 4 * g) =
+            *reinterpret_cast<const float4*>(sbuf + r * kEpiScratchStride + 4 * g);
+    }
+    __syncwarp();
   }
 };
 
@@ -372,6 +521,21 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
   return true;
 }
 
+// Phase timestamps for tuning builds only (-DLINMT_TC_PROF): slot s of CTA c at g_tc_prof[c * 8 + s].
+#ifdef LINMT_TC_PROF
+__device__ unsigned long long* g_tc_prof = nullptr;
+__device__ __forceinline__ void tc_prof(int slot) {
+  if (g_tc_prof) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_tc_prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+  }
+}
+#define TC_PROF(slot) tc_prof(slot)
+#else
+#define TC_PROF(slot) ((void)0)
+#endif
+
 // ---- kernel -------------------------------------------------------------------------------
 template <int NT, int BKT, int FMT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -387,8 +551,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   unsigned char* base_ptr = smem_raw + (base - raw);
   const int B_BYTES = BN * BK * 2;
   const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
-  const uint32_t bars = base + STAGES * STAGE_BYTES;  // full[STAGES], empty[STAGES], accum
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 3));
+  const int RING = ring_bytes(STAGES, STAGE_BYTES);
+  const uint32_t bars = base + RING;  // full[STAGES], empty[STAGES], accum, main_full, main_free
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + RING + 8 * (2 * STAGES + 3));
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -402,6 +567,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   const int ndrain = (nkb + kDrainEvery - 1) / kDrainEvery;
 
   if (threadIdx.x == 0) {
+    TC_PROF(0);
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
     mbar_init(accum_bar, 1);
@@ -415,6 +581,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  if (threadIdx.x == 0) TC_PROF(1);
 
   if (warp == 0) {
     // Producer.  A TMA instruction costs its issuing thread ~150 ns whatever the box size
@@ -449,6 +616,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(fb, ph, &s_abort)) break;
         tc_fence_after();
+        if (kb == 0) TC_PROF(2);
         const uint64_t a0 = make_desc<BKT>(st);                        // plane 0 of A, k-step 0
         const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);         // plane 0 of B, k-step 0
         if (NP == 1) {
@@ -484,45 +652,65 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         st += STAGE_BYTES; fb += 8u; eb += 8u;
         if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
       }
+      TC_PROF(3);
       umma_commit(accum_bar);
     }
   } else {
-    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the warps of a lane quadrant take
-    // interleaved 16-column chunks
+    // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the four warps of a lane quadrant
+    // own consecutive blocks of up to four 16-column chunks
     const int q = warp & 3;
-    constexpr int kParts = kEpiWarps / 4;       // warps sharing a lane quadrant take interleaved 16-column chunks
-    constexpr int kChunks = 16 / kParts;        // chunks per warp for the widest tile (256 columns)
-    const int half = (warp - 2) >> 2;
-    const int row = m0 + q * 32 + lane;
+    constexpr int kParts = kEpiWarps / 4;
+    constexpr int kChunks = kEpiBlockChunks;
+    static_assert(kParts * kChunks * 16 >= 256, "a quadrant's warps cover the widest tile");
+    const int part = (warp - 2) >> 2;
+    const int row0 = m0 + q * 32;
+    const int row = row0 + lane;
+    const int nchunks = BN >> 4;
+    const int cpw = (nchunks + kParts - 1) / kParts;            // chunks per warp
+    const int ch0 = part * cpw;                                  // this warp's first chunk
+    int nmine = nchunks - ch0; nmine = nmine < 0 ? 0 : (nmine > cpw ? cpw : nmine);
+    {
+      // columns past N (the last tile of a row of tiles) are not this warp's business
+      const int left = (N - (n0 + ch0 * 16) + 15) >> 4;
+      if (left < nmine) nmine = left < 0 ? 0 : left;
+    }
     const uint32_t astride = (uint32_t)acc_stride(BN);
-    const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16);
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(ch0 * 16);
+    float* sbuf = reinterpret_cast<float*>(base_ptr + (warp - 2) * kEpiScratchBytes);
     // with split-K the tile's partial sum goes to the workspace; the last CTA of the tile adds them up
     float* wrow = ws ? ws + ((size_t)blockIdx.z * ((size_t)gridDim.x * BM) + (size_t)row) * (size_t)N : nullptr;
-    auto emit = [&](int c0, const float* v) {
-      if (row < M && n0 + c0 < N) {
-        if (splits == 1) epi(row, n0 + c0, v);
-        else {
-          float4* dst = reinterpret_cast<float4*>(wrow + n0 + c0);
+    float macc[kChunks][16];
+    auto finish = [&]() {
+      if (splits == 1) {
+        if (Epi::kHasBlock) {
+          if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf);
+        } else if (row < M) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int ci = 0; ci < kChunks; ++ci)
+            if (ci < nmine) epi(row, n0 + (ch0 + ci) * 16, macc[ci]);
         }
+      } else if (row < M) {
+#pragma unroll
+        for (int ci = 0; ci < kChunks; ++ci)
+          if (ci < nmine) {
+            float4* dst = reinterpret_cast<float4*>(wrow + n0 + (ch0 + ci) * 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(macc[ci][4 * i], macc[ci][4 * i + 1], macc[ci][4 * i + 2], macc[ci][4 * i + 3]);
+          }
       }
     };
     if (NP == 1) {
       if (mbar_wait_sleepy(accum_bar, 0, &s_abort)) {
         tc_fence_after();
-#pragma unroll 1
-        for (int c0 = half * 16; c0 < BN; c0 += 16 * kParts) {
-          float v[16];
-          tmem_ld16(lane_base + (uint32_t)c0, v);
-          emit(c0, v);
-        }
+#pragma unroll
+        for (int ci = 0; ci < kChunks; ++ci)
+          if (ci < nmine) tmem_ld16(lane_base + (uint32_t)(ci * 16), macc[ci]);
+        finish();
       }
     } else {
       // Two-level accumulation of the leading product: the tensor core rounds toward zero on
       // every accumulate (measured: a bias of -0.5 ulp per MMA, growing with K), so its chain is
       // kept to kDrainEvery k-blocks and the partial sums are added here in fp32 round-to-nearest.
-      float macc[kChunks][16];
 #pragma unroll
       for (int ci = 0; ci < kChunks; ++ci)
 #pragma unroll
@@ -534,10 +722,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         tc_fence_after();
 #pragma unroll
         for (int ci = 0; ci < kChunks; ++ci) {
-          const int c0 = half * 16 + ci * 16 * kParts;
-          if (c0 < BN) {
+          if (ci < nmine) {
             float w[16];
-            tmem_ld16(lane_base + (uint32_t)c0, w);
+            tmem_ld16(lane_base + (uint32_t)(ci * 16), w);
 #pragma unroll
             for (int i = 0; i < 16; ++i) macc[ci][i] += w[i];
           }
@@ -548,24 +735,26 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       }
       if (ok && mbar_wait(accum_bar, 0, &s_abort)) {
         tc_fence_after();
+        if (threadIdx.x == 64) TC_PROF(4);
 #pragma unroll
         for (int ci = 0; ci < kChunks; ++ci) {
-          const int c0 = half * 16 + ci * 16 * kParts;
-          if (c0 < BN) {
+          if (ci < nmine) {
             float sm[16];
-            tmem_ld16(lane_base + astride + (uint32_t)c0, sm);
+            tmem_ld16(lane_base + astride + (uint32_t)(ci * 16), sm);
 #pragma unroll
             for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
-            emit(c0, macc[ci]);
           }
         }
+        finish();
       }
     }
   }
+  if (threadIdx.x == 64) TC_PROF(5);
   if (splits > 1) __threadfence();  // partial sums visible before this CTA takes its ticket
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_acc, TMEM_COLS);
+  if (threadIdx.x == 0) TC_PROF(6);
   if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
   if (splits > 1) {
     // The CTA that arrives last at this tile sums the partial tiles in split order (a fixed

@@ -145,7 +145,7 @@ int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, i
     if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn, bk)) return LINMT_ECUDA;
   }
   tc::Shape sh = tc::make_shape(bn, nt, bk, fmt);
-  if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = sh.stages * sh.stage_bytes + 1280; }
+  if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = tc::shape_smem_bytes(sh.stages, sh.stage_bytes); }
   if (drain > 0) sh.drain = drain;
   sh.splits = force_splits > 0 ? force_splits : splits;
   {

@@ -227,8 +227,9 @@ def test_bf16_against_fp32_token_identity(oracle, cuda_lib):
 def test_c2_whole_batch_against_golden(cuda_lib, gemm_path, min_identical):
     """The reference decode configuration at full size (64 sentences, beam 12, 4 x 1000, 30k
     vocabulary), free-running, against the checker's committed hypotheses: token-identical 1-best
-    for nearly every sentence (measured: 64/64 on the tensor-core path, 60/64 on the CUDA-core
-    path, whose longer fp32 FMA chains are slightly noisier), scores within 1e-4 where identical."""
+    for nearly every sentence (measured: 63-64 of 64 on the tensor-core path depending on the
+    rounding of the epilogue's activation functions, 60/64 on the CUDA-core path, whose longer fp32
+    FMA chains are slightly noisier), scores within 1e-4 where identical."""
     from linmt_b200 import decoder
     c = synth.configs()["C2"]
     g = np.load(os.path.join(GOLD, "c2_batch64.npz"))
