@@ -235,6 +235,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
+  { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
   fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR)) ? 1 : 0;
   nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR3 ? 3 : 2);
@@ -426,7 +427,7 @@ int Engine::step_tail(int t, int rows) {
     trace_dev_.ld_logits = Vp;
     trace_dev_.row_stats = d_row_stats_;
     if (n_models == 1) {
-      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream));
+      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_));
     } else {
       // EnsembleFactory::EnsemblesModels (src/decoder.h:1910-1931): mean of the members'
       // probabilities, renormalised -- written as log(mean p) so that the log-softmax of the
@@ -434,17 +435,17 @@ int Engine::step_tail(int t, int rows) {
       EnsembleRows er{};
       for (int mi = 0; mi < n_models; ++mi) er.logits[mi] = states_[mi].logits;
       er.n = n_models;
-      ensemble_combine_kernel<<<rows, 256, 0, stream>>>(er, Vp, V, opt.ensemble_mode, d_combined_);
+      CK(tc::launch_k(pdl_, ensemble_combine_kernel, dim3(rows), dim3(256), 0, stream, er, Vp, V, (int)opt.ensemble_mode, d_combined_));
       LAUNCHED();
-      CK(launch_softmax_topk(d_combined_, Vp, V, kk, rows, o, opt.ensemble_mode == LINMT_ENS_PROB_MEAN ? 1 : 0, stream));
+      CK(launch_softmax_topk(d_combined_, Vp, V, kk, rows, o, opt.ensemble_mode == LINMT_ENS_PROB_MEAN ? 1 : 0, stream, pdl_));
     }
     LAUNCHED();
   }
   {
     BeamState bs{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
     const size_t smem = (size_t)k * kk * 24 + 16;
-    beam_select_kernel<<<n_act, 256, smem, stream>>>(bs, d_cand_idx_, d_cand_logp_, d_eos_logp_, d_steps_, d_orig_, t, k,
-                                                     opt.penalty, opt.diversity, trace_dev_);
+    CK(tc::launch_k(pdl_, beam_select_kernel, dim3(n_act), dim3(256), smem, stream, bs, (const int32_t*)d_cand_idx_, (const float*)d_cand_logp_,
+                    (const float*)d_eos_logp_, (const int32_t*)d_steps_, (const int32_t*)d_orig_, t, k, opt.penalty, opt.diversity, trace_dev_));
     LAUNCHED();
   }
   CK(cudaGetLastError());

@@ -109,6 +109,8 @@ class Engine {
   std::vector<std::vector<cudaEvent_t>> enc_events_;
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
+  bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
+  bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
   int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair
   int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)
   int n_sm_ = 148;

@@ -118,6 +118,7 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   std::memcpy(tm.b, bm, sizeof(tm.b));
   tc::Shape sh = tc::make_shape(bn, nt, bk, fmt_);
   sh.splits = splits;
+  sh.pdl = (pdl_ && pdl_gemm_) ? 1 : 0;
   CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,
                         d_splitk_counters_ + ws_part_ * max_tiles));
   LAUNCHED();
@@ -146,6 +147,7 @@ int Engine::run_encoder_tc(int n, int Smax) {
     CK(cudaEventCreateWithFlags(&enc_start_ev_, cudaEventDisableTiming));
   }
   cudaStream_t main_stream = stream;
+  pdl_gemm_ = false;
   for (int mi = 0; mi < n_models; ++mi) {
     DevModel& m = models_[mi];
     DevState& s = states_[mi];
@@ -198,6 +200,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   DevState& s = states_[mi];
   TcState& ts = tc_states_[mi];
   const bool feed = desc.feed_input && t > 0;
+  pdl_gemm_ = true;
   // where h_cur of layer l lives after its GEMM: the input slot of the consumer panel
   auto hcur_planes = [&](int l) -> const tc::Planes& { return (l + 1 < L) ? ts.panel[l + 1] : ts.panel_top; };
   auto hcur_col0 = [&](int l) { return (l + 1 < L) ? 0 : Hp; };
@@ -227,7 +230,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
       add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
     jobs.n = nj;
     dim3 grid(rows, nj);
-    row_gather_kernel<<<grid, 128, 0, stream>>>(jobs, d_parent_, d_tok_, V, k, t == 0 ? 1 : 0);
+    CK(tc::launch_k(pdl_, row_gather_kernel, grid, dim3(128), 0, stream, jobs, (const int32_t*)d_parent_, (const int32_t*)d_tok_, V, k, t == 0 ? 1 : 0));
     LAUNCHED();
   }
   // 2. LSTM stack
@@ -262,9 +265,9 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
     const size_t smem = sizeof(float) * (win + 8);
-    attention_kernel<<<rows, 256, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, nullptr, H, Hp, k,
-                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
-                                                  ts.panel_top, nt_);
+    CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, 2 * Hp, u_alt, Hp, (const float*)m.vp,
+                    (const float*)s.hs, (const int32_t*)d_len_, (float*)nullptr, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
+                    (int)opt.attention_d, win, ra, rl, rv, ts.panel_top, nt_));
     LAUNCHED();
   }
   // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)

@@ -65,6 +65,7 @@ struct Shape {
   int smem_bytes;
   int drain;     // k-blocks between drains of the leading accumulator
   int splits;    // split-K factor (1 = none)
+  int pdl;       // launch with programmatic stream serialization
 };
 // Dynamic shared memory of a launch: the stage ring (which the epilogue warps reuse as their
 // staging areas once the accumulator is complete, kEpiStagingBytes in all), alignment slack, barriers.
@@ -82,7 +83,30 @@ inline Shape make_shape(int bn, int nt, int bk = BK, int fmt = 0) {
   s.smem_bytes = shape_smem_bytes(s.stages, s.stage_bytes);
   s.drain = kDrainDefault;
   s.splits = 1;
+  s.pdl = 0;
   return s;
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start (prologue, loads of
+// constant data) while its predecessor in the stream is still finishing; it must not touch
+// anything the predecessor writes or reads-then-overwrites before pdl_wait() returns.  Every
+// kernel of the decoder step announces itself with pdl_launch_dependents() at its start, so the
+// next kernel's CTAs take over SMs as this kernel's last CTAs leave them.  Without the launch
+// attribute both calls do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -556,6 +580,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + RING + 8 * (2 * STAGES + 3));
   __shared__ int s_abort;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;  // M fastest: the CTAs sharing a weight tile run together
   // split-K: this CTA covers k-blocks [kb0, kb0 + nkb) of the K / BK blocks
@@ -592,9 +617,20 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     const CUtensorMap* map = reinterpret_cast<const CUtensorMap*>(&tm) + (is_a ? t : 3 + t);  // a[3] then b[3]
     const uint32_t dst_off = is_a ? (uint32_t)(t * A_BYTES) : (uint32_t)(NT * A_BYTES + t * B_BYTES);
     const int ycoord = is_a ? m0 : n0;
-    int s = 0; uint32_t ph = 0;
-    uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
-    for (int kb = 0; kb < nkb; ++kb) {
+    // First trip round the ring: the weight tiles do not depend on the previous kernel, so they
+    // are requested before pdl_wait() and only the activation tiles after it.
+    const int npre = nkb < STAGES ? nkb : STAGES;
+    for (int kb = 0; kb < npre; ++kb) {
+      if (lane == 0) mbar_expect_tx(bars + 8u * kb, (uint32_t)STAGE_BYTES);
+      __syncwarp();
+      if (!is_a && lane < 2 * NT) tma_load_2d(base + kb * STAGE_BYTES + dst_off, map, (kb0 + kb) * BK, ycoord, bars + 8u * kb);
+    }
+    pdl_wait();   // the activations are the previous kernel's output
+    if (is_a)
+      for (int kb = 0; kb < npre; ++kb) tma_load_2d(base + kb * STAGE_BYTES + dst_off, map, (kb0 + kb) * BK, ycoord, bars + 8u * kb);
+    int s = npre == STAGES ? 0 : npre; uint32_t ph = npre == STAGES ? 1u : 0u;
+    uint32_t st = base + s * STAGE_BYTES, fb = bars + 8u * s, eb = bars + 8u * (STAGES + s);
+    for (int kb = npre; kb < nkb; ++kb) {
       int ok = 1;
       if (lane == 0) {
         ok = mbar_wait(eb, ph ^ 1u, &s_abort) ? 1 : 0;
@@ -679,6 +715,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     float* sbuf = reinterpret_cast<float*>(base_ptr + (warp - 2) * kEpiScratchBytes);
     // with split-K the tile's partial sum goes to the workspace; the last CTA of the tile adds them up
     float* wrow = ws ? ws + ((size_t)blockIdx.z * ((size_t)gridDim.x * BM) + (size_t)row) * (size_t)N : nullptr;
+    pdl_wait();   // before the first global access of these warps (the hardware wait is over long before)
     float macc[kChunks][16];
     auto finish = [&]() {
       if (splits == 1) {
@@ -844,9 +881,8 @@ inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, con
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
   int drain = (sh.drain > 0 ? sh.drain : kDrainDefault) * 32 / BKT;
   if (drain < 1) drain = 1;
-  gemm_tc_kernel<NT, BKT, FMT, Epi><<<grid, kThreads, sh.smem_bytes, st>>>(tm, M, N, K, sh.bn, sh.stages, drain, epi, err_flag,
-                                                                  splits, splits > 1 ? ws : nullptr, counters);
-  return cudaGetLastError();
+  return launch_k(sh.pdl != 0, gemm_tc_kernel<NT, BKT, FMT, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, sh.bn,
+                  sh.stages, drain, epi, err_flag, splits, splits > 1 ? ws : (float*)nullptr, counters);
 }
 template <class Epi>
 inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,

@@ -87,6 +87,8 @@ struct GatherJobs {
 };
 static __global__ void row_gather_kernel(GatherJobs jobs, const int32_t* __restrict__ parent, const int32_t* __restrict__ tok,
                                          int vocab, int k, int src_per_sentence) {
+  tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
+  tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   const int r = blockIdx.x;
   const GatherJob& jb = jobs.j[blockIdx.y];
   long long srow;
@@ -153,6 +155,8 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
                                  int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt) {
+  tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
+  tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   extern __shared__ float sm[];
   float* e = sm;            // [win]
   float* red = sm + win;    // [8]
@@ -271,6 +275,8 @@ __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { ret
 constexpr int kTopkCap = 1024;
 static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
                                                                   int normalise) {
+  tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
+  tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   __shared__ float s_tmax[256];
   __shared__ float s_cv[kTopkCap];
   __shared__ int s_ci[kTopkCap];
@@ -282,17 +288,53 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   const int warp = tid >> 5, lane = tid & 31;
   const float* z = logits + (size_t)r * ld;
   const int V4 = V & ~3;
-  // ---- pass 1: maxima ----
+  // ---- pass 1: maxima (four independent 16-byte loads in flight per thread) ----
   float m = -INFINITY;
-  for (int i = tid * 4; i < V4; i += 256 * 4) {
-    const float4 q = *reinterpret_cast<const float4*>(z + i);
-    m = fmaxf(fmaxf(m, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
+  {
+    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+    int i = tid * 4;
+    for (; i + 3 * 1024 < V4; i += 4 * 1024) {
+      const float4 q0 = *reinterpret_cast<const float4*>(z + i);
+      const float4 q1 = *reinterpret_cast<const float4*>(z + i + 1024);
+      const float4 q2 = *reinterpret_cast<const float4*>(z + i + 2048);
+      const float4 q3 = *reinterpret_cast<const float4*>(z + i + 3072);
+      m0 = fmaxf(fmaxf(m0, q0.x), fmaxf(q0.y, fmaxf(q0.z, q0.w)));
+      m1 = fmaxf(fmaxf(m1, q1.x), fmaxf(q1.y, fmaxf(q1.z, q1.w)));
+      m2 = fmaxf(fmaxf(m2, q2.x), fmaxf(q2.y, fmaxf(q2.z, q2.w)));
+      m3 = fmaxf(fmaxf(m3, q3.x), fmaxf(q3.y, fmaxf(q3.z, q3.w)));
+    }
+    for (; i < V4; i += 1024) {
+      const float4 q = *reinterpret_cast<const float4*>(z + i);
+      m0 = fmaxf(fmaxf(m0, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
+    }
+    m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
   }
   for (int i = V4 + tid; i < V; i += 256) m = fmaxf(m, z[i]);
   s_tmax[tid] = m;
   if (tid == 0) s_count = 0;
   __syncthreads();
-  {
+  if (kk <= 32) {
+    // Threshold from 32 group maxima (group = the 8 threads with the same lane): each is an
+    // element of the row and the groups are disjoint, so at least kk elements reach the kk-th
+    // largest of them; it is a little lower than the kk-th largest thread maximum (a few more
+    // candidates to rank) and costs one warp ~100 instructions instead of 256 x 256 compares.
+    if (warp == 0) {
+      float g = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) g = fmaxf(g, s_tmax[w * 32 + lane]);
+      float bm = g;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+      int rank = 0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float o = __shfl_sync(0xffffffffu, g, j);
+        rank += (o > g || (o == g && j < lane)) ? 1 : 0;
+      }
+      if (rank == kk - 1) s_tau = g;
+      if (lane == 0) s_max = bm;
+    }
+  } else {
     int rank = 0;
     float bm = -INFINITY;
     for (int j = 0; j < 256; ++j) {
@@ -383,9 +425,8 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
 }
 
 inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, int normalise,
-                                       cudaStream_t st) {
-  softmax_topk_kernel<<<rows, 256, 0, st>>>(logits, ld, V, kk, out, normalise);
-  return cudaGetLastError();
+                                       cudaStream_t st, bool pdl = false) {
+  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, kk, out, normalise);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -398,6 +439,8 @@ struct EnsembleRows {
   int n;
 };
 static __global__ void __launch_bounds__(256) ensemble_combine_kernel(EnsembleRows er, int ld, int V, int mode, float* __restrict__ out) {
+  tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
+  tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   __shared__ float s_red[8];
   __shared__ float s_max[8], s_lse[8];
   const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -468,6 +511,8 @@ static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, c
                                    const float* __restrict__ eos_logp, const int32_t* __restrict__ steps,
                                    const int32_t* __restrict__ orig, int t, int k, float penalty, float diversity,
                                    TraceDev tr) {
+  tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
+  tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   extern __shared__ unsigned char smraw[];
   const int kk = k + 1;
   const int ncap = k * kk;
