@@ -235,6 +235,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
+  { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
   fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR)) ? 1 : 0;

@@ -101,7 +101,7 @@ class Engine {
   const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K, int bk);
   const CUtensorMap* b_maps(const tc::Planes& p, int rows, int K, int bn, int bk);
   template <class Epi>
-  int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt = 0);
+  int tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt = 0, int drain = 0);
 
   bool use_tc_ = false;
   // encoder wavefront: one stream per layer, a small ring of events per layer
@@ -110,6 +110,7 @@ class Engine {
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
+  bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
   int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair
   int nt_vocab_ = 0;  // planes used by the vocabulary GEMM (0 = nt_)

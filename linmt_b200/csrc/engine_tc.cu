@@ -97,7 +97,7 @@ const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn, 
 
 // C[M][N] = A[:, a_col0 : a_col0+K] . W[N][K]^T with the tile width chosen for this shape.
 template <class Epi>
-int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt) {
+int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt, int drain) {
   if (nt <= 0 || nt > nt_) nt = nt_;
   int bn = 0, splits = 1;
   const size_t ws_floats = kSplitKWsFloats / ws_parts_;
@@ -118,7 +118,15 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   std::memcpy(tm.b, bm, sizeof(tm.b));
   tc::Shape sh = tc::make_shape(bn, nt, bk, fmt_);
   sh.splits = splits;
+  if (drain > 0) sh.drain = drain;
   sh.pdl = (pdl_ && pdl_gemm_) ? 1 : 0;
+  // many waves of tiles whose leading product is one chain: one persistent CTA per SM
+  const long tiles = (long)((M + tc::BM - 1) / tc::BM) * ((N + bn - 1) / bn);
+  if (persist_ && nt == 2 && splits == 1 && drain >= K / 32 && tiles > n_sm_) {
+    CK(tc::launch_gemm_tc_persist(tm, M, N, K, sh, e, d_tc_err_, stream, n_sm_));
+    LAUNCHED();
+    return LINMT_OK;
+  }
   CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,
                         d_splitk_counters_ + ws_part_ * max_tiles));
   LAUNCHED();
@@ -280,7 +288,11 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   {
     tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
     if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
-    int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e, nt_vocab_);
+    // Logits feed only the softmax of their own step: the tensor core's truncation bias over one
+    // K = Hp chain (~32 ulp of the accumulator, 2e-7 relative on a log-probability) does not
+    // accumulate over steps as it does through the recurrent products, so this GEMM runs its
+    // leading product as one chain (no intermediate drains: 5 % faster).
+    int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e, nt_vocab_, Hp / 32);
     if (rc) return rc;
     if ((rc = mark(gemm_ev_, gemm_ev_used_))) return rc;
   }

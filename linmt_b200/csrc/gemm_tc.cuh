@@ -830,6 +830,174 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   }
 }
 
+// ---- persistent variant for many-wave GEMMs whose leading product is one chain ----------------
+// One CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tile fastest, so
+// CTAs working at the same time share weight tiles in L2).  The TMA ring and the MMA issue run on
+// across tile boundaries; the epilogue warps copy a finished accumulator pair to registers, hand
+// TMEM back at once, and write their tile to memory while the tensor core is already on the next
+// one -- the ~7 us of prologue and epilogue that every tile of a multi-wave launch used to pay is
+// paid once per CTA.  (Direct row-per-lane stores here: the staging area of the one-tile kernel
+// is the stage ring, which is busy; the last tile of a CTA, with the ring idle, uses it.)
+// Split operands only (NP > 1), no split-K, no intermediate drains.
+template <int NT, int BKT, int FMT, class Epi>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, Epi epi,
+                       int* __restrict__ err_flag) {
+  constexpr int PC = product_code(NT, FMT);
+  constexpr int NP = num_products(PC);
+  static_assert(NP > 1, "split operands only");
+  constexpr int A_BYTES = BM * BKT * 2;
+  constexpr int BK = BKT;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const int B_BYTES = BN * BK * 2;
+  const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
+  const int RING = ring_bytes(STAGES, STAGE_BYTES);
+  const uint32_t bars = base + RING;   // full[STAGES], empty[STAGES], accum_full, tmem_free
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + RING + 8 * (2 * STAGES + 3));
+  __shared__ int s_abort;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = (M + BM - 1) / BM;
+  const int ntile = mt * ((N + BN - 1) / BN);
+  const int nkb = K / BK;
+  const uint32_t accum_full = bars + 8u * (2 * STAGES);
+  const uint32_t tmem_free = accum_full + 8u;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
+    mbar_init(accum_full, 1);
+    mbar_init(tmem_free, kEpiWarps);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    const bool is_a = lane < NT;
+    const int t = is_a ? lane : lane - NT;
+    const CUtensorMap* map = reinterpret_cast<const CUtensorMap*>(&tm) + (is_a ? t : 3 + t);
+    const uint32_t dst_off = is_a ? (uint32_t)(t * A_BYTES) : (uint32_t)(NT * A_BYTES + t * B_BYTES);
+    int s = 0; uint32_t ph = 0;
+    uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
+    pdl_wait();
+    bool live = true;
+    for (int tile = blockIdx.x; tile < ntile && live; tile += gridDim.x) {
+      const int ycoord = is_a ? (tile % mt) * BM : (tile / mt) * BN;
+      for (int kb = 0; kb < nkb; ++kb) {
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(eb, ph ^ 1u, &s_abort) ? 1 : 0;
+          if (ok) mbar_expect_tx(fb, (uint32_t)STAGE_BYTES);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { live = false; break; }
+        if (lane < 2 * NT) tma_load_2d(st + dst_off, map, kb * BK, ycoord, fb);
+        st += STAGE_BYTES; fb += 8u; eb += 8u;
+        if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN, FMT);
+      const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
+      const uint64_t bstep = (uint64_t)(B_BYTES >> 4);
+      int s = 0; uint32_t ph = 0;
+      uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
+      bool live = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < ntile && live; tile += gridDim.x, ++it) {
+        // the epilogue warps have copied the previous tile's accumulators out
+        if (it > 0) {
+          if (!mbar_wait(tmem_free, (uint32_t)((it - 1) & 1), &s_abort)) break;
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(fb, ph, &s_abort)) { live = false; break; }
+          tc_fence_after();
+          const uint64_t a0 = make_desc<BKT>(st);
+          const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+#pragma unroll
+            for (int p = 0; p < NP - 1; ++p) {
+              const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
+              const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
+              umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
+            }
+          }
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks)
+            umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (kb | ks) ? 1u : 0u);
+          umma_commit(eb);
+          st += STAGE_BYTES; fb += 8u; eb += 8u;
+          if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
+        }
+        umma_commit(accum_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    constexpr int kParts = kEpiWarps / 4;
+    constexpr int kChunks = kEpiBlockChunks;
+    const int part = (warp - 2) >> 2;
+    const int nchunks = BN >> 4;
+    const int cpw = (nchunks + kParts - 1) / kParts;
+    const int ch0 = part * cpw;
+    const uint32_t astride = (uint32_t)acc_stride(BN);
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(ch0 * 16);
+    float* sbuf = reinterpret_cast<float*>(base_ptr + (warp - 2) * kEpiScratchBytes);
+    pdl_wait();
+    int it = 0;
+    for (int tile = blockIdx.x; tile < ntile; tile += gridDim.x, ++it) {
+      const int m0 = (tile % mt) * BM, n0 = (tile / mt) * BN;
+      const int row0 = m0 + q * 32;
+      int nmine = nchunks - ch0; nmine = nmine < 0 ? 0 : (nmine > cpw ? cpw : nmine);
+      {
+        const int left = (N - (n0 + ch0 * 16) + 15) >> 4;
+        if (left < nmine) nmine = left < 0 ? 0 : left;
+      }
+      if (!mbar_wait_sleepy(accum_full, (uint32_t)(it & 1), &s_abort)) break;
+      tc_fence_after();
+      float macc[kChunks][16];
+#pragma unroll
+      for (int ci = 0; ci < kChunks; ++ci) {
+        if (ci < nmine) {
+          float sm[16];
+          tmem_ld16(lane_base + (uint32_t)(ci * 16), macc[ci]);
+          tmem_ld16(lane_base + astride + (uint32_t)(ci * 16), sm);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_free);   // the tensor core may start the next tile
+      const bool last = tile + (int)gridDim.x >= ntile;
+      if (last && Epi::kHasBlock) {
+        // the ring is idle from here on: stage and store coalesced
+        if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf);
+      } else if (row0 + lane < M) {
+#pragma unroll
+        for (int ci = 0; ci < kChunks; ++ci)
+          if (ci < nmine) epi(row0 + lane, n0 + (ch0 + ci) * 16, macc[ci]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_acc, TMEM_COLS);
+  if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
+}
+
 // ---- fp32 -> bf16 planes ---------------------------------------------------------------------
 static __global__ void split_planes_kernel(const float* __restrict__ src, Planes dst, int nt, size_t n) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -900,6 +1068,32 @@ inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const 
   if (sh.nt == 3) return launch_gemm_tc_nt<3, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
   if (sh.nt == 2) return launch_gemm_tc_nt<2, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
   return launch_gemm_tc_nt<1, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+}
+
+// Persistent launch (see gemm_tc_persist_kernel): fp16 pair or two bf16 planes, no split-K.
+template <class Epi>
+inline cudaError_t launch_gemm_tc_persist(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
+                                          cudaStream_t st, int n_sm) {
+  if (sh.nt != 2 || K % sh.bk) return cudaErrorInvalidValue;
+  const int tiles = ((M + BM - 1) / BM) * ((N + sh.bn - 1) / sh.bn);
+  const dim3 grid(tiles < n_sm ? tiles : n_sm);
+#define LINMT_PERSIST_CASE(BKV, FMTV)                                                                                        \
+  {                                                                                                                          \
+    static bool done = false;                                                                                                \
+    if (!done) {                                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<2, BKV, FMTV, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           SMEM_BUDGET + 1280);                                                              \
+      if (e != cudaSuccess) return e;                                                                                        \
+      done = true;                                                                                                           \
+    }                                                                                                                        \
+    return launch_k(sh.pdl != 0, gemm_tc_persist_kernel<2, BKV, FMTV, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, \
+                    sh.bn, sh.stages, epi, err_flag);                                                                        \
+  }
+  if (sh.fmt == 1 && sh.bk == 64) LINMT_PERSIST_CASE(64, 1)
+  if (sh.fmt == 1) LINMT_PERSIST_CASE(32, 1)
+  if (sh.bk == 64) LINMT_PERSIST_CASE(64, 0)
+  LINMT_PERSIST_CASE(32, 0)
+#undef LINMT_PERSIST_CASE
 }
 
 // Tile width that fills the SMs best for an M x N problem: the smallest makespan
