@@ -31,8 +31,11 @@ from linmt_b200 import synth  # noqa: E402
 METRIC = "decoded target tokens/sec, beam 12, 4x1000 LSTM"
 UNIT = "tokens/s"
 FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
-# DRAM bytes of one vocabulary-GEMM launch from an ncu capture (see profiles/); None = not captured
-VOCAB_GEMM_TRAFFIC_BYTES = 259.5e6  # dram read 191.4 MB + write 68.1 MB, profiles/vocab_gemm_tensor_path_C2.md (tensor path, 768 rows)
+# DRAM bytes of one launch at 768 rows from ncu captures (see profiles/): read + write
+VOCAB_GEMM_TRAFFIC_BYTES = 185.7e6  # 131.1 MB + 54.6 MB, profiles/vocab_gemm_tensor_path_C2.md (algorithmic 218 MB; logits partly still in L2)
+# gate GEMM: 66.7 MB measured at K = 3072 (profiles/gate_gemm_tensor_path_C2.md, algorithmic 69.1 MB); the three
+# K = 2048 layers scaled by their algorithmic bytes (49.2 MB): average of the four launches of a stack
+GATE_GEMM_TRAFFIC_BYTES = (66.7e6 + 3 * 66.7e6 * 49.2 / 69.1) / 4
 
 
 WORKLOADS = {
@@ -334,10 +337,11 @@ def run_ours(args):
                             "tensor_pipe_* counts; the bf16 path runs 1"}
 
         r_voc = roof("vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path)", flops_local, gemm_ms, gemm_n,
-                     (4 if args.gemm_path in ("tensor2", "tensor3") else 3) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and tensor else None)
+                     (4 if args.gemm_path in ("tensor2", "tensor3") else 3) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
         r_rec = roof("decoder LSTM gate GEMMs [rows,2H|3H]x[.,4H], fused cell update (" + args.gemm_path + " path)",
                      rec["flops"], rec["ms"], rec["n"],
-                     {"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1, None)
+                     {"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1,
+                     GATE_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
         dominant, other = (r_rec, r_voc) if rec["ms"] >= gemm_ms else (r_voc, r_rec)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:

@@ -382,3 +382,31 @@ def test_force_decoding_scores(oracle, cuda_lib, c1):
     total1, per1 = dec.score(sents, [[7] for _ in range(sents.n)])
     np.testing.assert_allclose(per1[:, 0], o["logp_full"][:, 0, 0, 7], rtol=RTOL_FP32)
     dec.close()
+
+
+def test_launch_variants_give_identical_bits(cuda_lib):
+    """The overlapped launch forms change scheduling, never arithmetic: with programmatic dependent
+    launch off, and with the persistent vocabulary GEMM off, a decode of 24 sentences of the
+    reference configuration returns the same tokens and the same score bits."""
+    from linmt_b200 import decoder
+    c = synth.configs()["C2"]
+    blob = c.blobs()[0]
+    sents = c.sentences().subset(range(24))   # 288 rows: several waves of vocabulary tiles -> persistent kernel
+    outs = []
+    for env in ({}, {"LINMT_PDL": "0"}, {"LINMT_TC_PERSIST": "0"}):
+        old = {k: os.environ.get(k) for k in env}
+        os.environ.update(env)
+        try:
+            dec = decoder.Decoder(c.desc, [blob], beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                                  max_batch=24, max_src_len=64, max_steps=100)
+            outs.append(dec.decode(sents))
+            dec.close()
+        finally:
+            for k, v in old.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+    for o in outs[1:]:
+        assert (o["tok"] == outs[0]["tok"]).all() and (o["len"] == outs[0]["len"]).all()
+        assert (o["score"] == outs[0]["score"]).all()
