@@ -27,6 +27,23 @@ extern "C" {
 void python_decoder_init(char* msg);
 char* python_decoder_do_job(char* sentence);
 
+/* UNK post-processing, the pair the reference's wrapper and server call right after
+ * python_decoder_do_job (src/postprocess_unks.h:89-92, definitions src/postprocess_unks.cc:716-752;
+ * callers server/LiNMT-python-wrapper.py:24-33, server/LiNMT-server.py:52-57).  Host string code.
+ * `msg` = config file with --phrase-table ("src ||| tgt ||| x" lines), --stopword and --end-punct
+ * (tab-separated "tag<TAB>word" lines) and optional --rm-oov-mode; init exits on a missing file as
+ * the reference does.  do_job takes the source line (optionally "words |||| {generalizations}") and
+ * the decoder's "words |||| score |||| alignments |||| unk alignments |||| a/a/a ..." line and
+ * returns the final words; the string belongs to the library until the next call. */
+void python_unk_init(char* msg);
+char* python_unk_do_job(char* src_sentence, char* translation);
+/* The same on a handle, returning the whole line with its "||||" fields
+ * (PostProcessUnks::Init / Process, src/postprocess_unks.cc:14-30). */
+typedef struct linmt_unk linmt_unk;
+int linmt_unk_create(const char* config_path, linmt_unk** out);
+int linmt_unk_process(const linmt_unk* h, const char* source, const char* translation, char* out, int32_t out_cap);
+void linmt_unk_destroy(linmt_unk* h);
+
 /* ------------------------------------------------------------------------------------
  * 2. Handle-based API at the reference's numeric boundary
  *    (EnsembleFactory<T>::InitDecoderSentence, src/decoder.h:1526-1575, and

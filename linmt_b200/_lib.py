@@ -37,7 +37,8 @@ class StatsC(C.Structure):
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",
            "linmt_create_from_weights", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
            "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
-           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch"]
+           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch",
+           "python_unk_init", "python_unk_do_job", "linmt_unk_create", "linmt_unk_process", "linmt_unk_destroy"]
 
 _lib = None
 
@@ -83,6 +84,12 @@ def load():
     lib.linmt_k_gemm_time.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_float), C.c_int32]
     lib.linmt_gemm_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.linmt_decode_file.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
+    lib.python_unk_do_job.restype = C.c_char_p
+    lib.python_unk_do_job.argtypes = [C.c_char_p, C.c_char_p]
+    lib.python_unk_init.argtypes = [C.c_char_p]
+    lib.linmt_unk_create.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.linmt_unk_process.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_int32]
+    lib.linmt_unk_destroy.argtypes = [C.c_void_p]
     lib.linmt_score_batch.argtypes = [C.c_void_p] * 5 + [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]
     _lib = lib
     return lib

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblinmt_decoder.so")
-SOURCES = ["engine.cu", "engine_tc.cu", "frontend.cu", "kernel_entry.cu", "noalloc_entry.cu"]
+SOURCES = ["engine.cu", "engine_tc.cu", "frontend.cu", "kernel_entry.cu", "noalloc_entry.cu", "unk_post.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fopenmp,-O3", "--use_fast_math=false"]
 
@@ -28,7 +28,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     for src in SOURCES:
-        obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
+        obj = os.path.join(HERE, "build", os.path.splitext(src)[0] + ".o")
         cmd = ["nvcc"] + [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + \
               (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((cmd, subprocess.Popen(cmd)))
