@@ -201,6 +201,13 @@ const char* linmt_translate(linmt_engine* e, const char* sentence);
 int linmt_score_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* src_off, const int32_t* tgt_ids,
                       const int32_t* tgt_off, int32_t n, float* out_logprob, float* out_token_logp, int32_t max_tgt);
 
+/* Reads a model file in the reference's text format (header, vocabularies, matrices; the format
+ * written by DumpBestModel, src/deep_rnn.h:1972-2146, and read by LoadWeights, :1878-1969) without
+ * creating an engine: fills `desc` and, if `blob` is given, the weights in the blob layout of
+ * linmt_create_from_weights (`blob_cap` floats available).  use_cache = 1 reads / writes the raw
+ * copy "<path>.linmtcache" that makes later loads of the same unchanged text file fast.  No GPU call. */
+int linmt_read_model_file(const char* path, linmt_model_desc* desc, float* blob, uint64_t blob_cap, int32_t use_cache);
+
 /* File-mode decoding: one source sentence per line of `in_path`; writes the n-best
  * translations of every sentence to `out_path` in input order.  Replaces
  * EnsembleFactory::DecodeFile (src/decoder.h:1702-1776), Decoder::OutputKBestHypotheses

@@ -38,7 +38,7 @@ EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_option
            "linmt_create_from_weights", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
            "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
            "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch",
-           "python_unk_init", "python_unk_do_job", "linmt_unk_create", "linmt_unk_process", "linmt_unk_destroy"]
+           "linmt_read_model_file", "python_unk_init", "python_unk_do_job", "linmt_unk_create", "linmt_unk_process", "linmt_unk_destroy"]
 
 _lib = None
 
@@ -84,6 +84,7 @@ def load():
     lib.linmt_k_gemm_time.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_float), C.c_int32]
     lib.linmt_gemm_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.linmt_decode_file.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
+    lib.linmt_read_model_file.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32]
     lib.python_unk_do_job.restype = C.c_char_p
     lib.python_unk_do_job.argtypes = [C.c_char_p, C.c_char_p]
     lib.python_unk_init.argtypes = [C.c_char_p]

@@ -16,6 +16,7 @@
 #include <string>
 #include <unordered_map>
 #include <vector>
+#include <sys/stat.h>
 
 #include "engine.h"
 
@@ -56,6 +57,7 @@ struct SentenceConfig {
   std::vector<std::string> model_names;
   int longest_sentence;  // user value + 4 (src/decoder_sentence.cu:126)
   int print_align_scores;
+  int model_cache;       // 1 = keep / use a binary copy of the weights next to a text model
 };
 
 // DecoderSentence::GeneralSettings, src/decoder_sentence.cu:110-264.  Like the reference,
@@ -79,6 +81,8 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
   if (auto v = get("--nmt-model")) c.model_names = split_ws(*v);
   else { err = "you must assign --nmt-model in config file!"; return false; }
   if (c.model_names.empty()) { err = "you must assign --nmt-model in config file!"; return false; }
+  c.model_cache = 1;
+  if (auto v = get("--model-cache")) c.model_cache = std::atoi(v->c_str()) ? 1 : 0;
   if (auto v = get("--nbest")) c.opt.nbest = std::atoi(v->c_str());
   if (c.opt.beam <= 0) { err = "--beam-size cannot be <= 0!"; return false; }
   if (auto v = get("--decoding-ratio")) {
@@ -111,8 +115,9 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
     if (*v == "auto") c.opt.gemm_path = LINMT_GEMM_AUTO;
     else if (*v == "simt") c.opt.gemm_path = LINMT_GEMM_SIMT;
     else if (*v == "tensor") c.opt.gemm_path = LINMT_GEMM_TENSOR;
+    else if (*v == "tensor2") c.opt.gemm_path = LINMT_GEMM_TENSOR2;
     else if (*v == "tensor3") c.opt.gemm_path = LINMT_GEMM_TENSOR3;
-    else { err = "--gemm-path must be auto, simt or tensor"; return false; }
+    else { err = "--gemm-path must be auto, simt, tensor, tensor2 or tensor3"; return false; }
   }
   if (auto v = get("--batch-size")) c.opt.max_batch = std::atoi(v->c_str());
   if (auto v = get("--device")) c.opt.device = std::atoi(v->c_str());
@@ -130,7 +135,14 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
 // in LoadWeights order, `rows` text lines of `cols` values and one blank line each, value
 // (i,j) at column-major offset j*rows+i (src/deep_rnn_kernel.h:1543-1560).  A binary body
 // ("BINARY <count>" line followed by raw little-endian floats in the same order and layout)
-// is accepted as a faster sidecar form of the same file.
+// is accepted as a faster form of the same file.
+//
+// Parsing the text body of a full-size model (~2 GB of decimal text for 4 x 1000, 30k / 30k)
+// takes tens of seconds, so after a successful parse the weights are also written, raw, to
+// "<model>.linmtcache" (header: magic, the nine integers, size and mtime of the text file, float
+// count), and later loads of the same unchanged text file read that instead.  The cache is only
+// ever a copy: a text file with another size or mtime, or other dimensions, invalidates it; an
+// unwritable directory just means no cache.
 struct ModelFile {
   linmt_model_desc desc{};
   int header[9]{};
@@ -141,7 +153,48 @@ struct ModelFile {
 
 static bool is_sep(const std::string& s) { return s.size() > 3 && s[0] == '=' && s[1] == '=' && s[2] == '='; }
 
-bool read_model_file(const std::string& path, ModelFile& mf, bool want_weights, std::string& err) {
+static const char kCacheMagic[8] = {'L', 'I', 'N', 'M', 'T', 'B', 'I', '1'};
+struct CacheHeader {
+  char magic[8];
+  int32_t header[9];
+  int32_t pad;
+  uint64_t text_size;
+  int64_t text_mtime;
+  uint64_t n_floats;
+};
+static bool stat_text(const std::string& path, uint64_t& size, int64_t& mtime) {
+  struct stat st;
+  if (stat(path.c_str(), &st) != 0) return false;
+  size = (uint64_t)st.st_size; mtime = (int64_t)st.st_mtime;
+  return true;
+}
+static bool cache_read(const std::string& path, const int32_t* header9, std::vector<float>& blob) {
+  uint64_t size; int64_t mtime;
+  if (!stat_text(path, size, mtime)) return false;
+  FILE* c = std::fopen((path + ".linmtcache").c_str(), "rb");
+  if (!c) return false;
+  CacheHeader h;
+  bool ok = std::fread(&h, sizeof h, 1, c) == 1 && std::memcmp(h.magic, kCacheMagic, 8) == 0 &&
+            std::memcmp(h.header, header9, sizeof h.header) == 0 && h.text_size == size && h.text_mtime == mtime &&
+            h.n_floats == blob.size();
+  if (ok) ok = std::fread(blob.data(), sizeof(float), blob.size(), c) == blob.size();
+  std::fclose(c);
+  return ok;
+}
+static void cache_write(const std::string& path, const int32_t* header9, const std::vector<float>& blob) {
+  CacheHeader h{};
+  std::memcpy(h.magic, kCacheMagic, 8);
+  std::memcpy(h.header, header9, sizeof h.header);
+  if (!stat_text(path, h.text_size, h.text_mtime)) return;
+  h.n_floats = blob.size();
+  const std::string tmp = path + ".linmtcache.tmp", fin = path + ".linmtcache";
+  FILE* c = std::fopen(tmp.c_str(), "wb");
+  if (!c) return;
+  const bool ok = std::fwrite(&h, sizeof h, 1, c) == 1 && std::fwrite(blob.data(), sizeof(float), blob.size(), c) == blob.size();
+  if (std::fclose(c) != 0 || !ok || std::rename(tmp.c_str(), fin.c_str()) != 0) std::remove(tmp.c_str());
+}
+
+bool read_model_file(const std::string& path, ModelFile& mf, bool want_weights, std::string& err, bool use_cache = false) {
   FILE* f = std::fopen(path.c_str(), "rb");
   if (!f) { err = "can not open " + path + " file!"; return false; }
   std::vector<char> buf(1 << 22);
@@ -199,6 +252,9 @@ bool read_model_file(const std::string& path, ModelFile& mf, bool want_weights, 
     return true;
   }
   std::fseek(f, body, SEEK_SET);
+  int32_t header9[9];
+  for (int i = 0; i < 9; ++i) header9[i] = mf.header[i];
+  if (use_cache && cache_read(path, header9, mf.blob)) { std::fclose(f); return true; }
   // text matrices
   const int H = mf.desc.hidden, L = mf.desc.layers;
   std::vector<std::pair<int, int>> shapes;
@@ -231,6 +287,7 @@ bool read_model_file(const std::string& path, ModelFile& mf, bool want_weights, 
     dst += (size_t)rows * cols;
   }
   std::fclose(f);
+  if (use_cache) cache_write(path, header9, mf.blob);
   return true;
 }
 
@@ -320,7 +377,7 @@ int linmt_create(const char* config_path, linmt_engine** out) {
   if (!sentence_settings(kv, sc, err)) { g_front_error = err; return LINMT_EINVAL; }
   std::vector<ModelFile> mfs(sc.model_names.size());
   for (size_t i = 0; i < mfs.size(); ++i) {
-    if (!read_model_file(sc.model_names[i], mfs[i], true, err)) { g_front_error = err; return LINMT_EIO; }
+    if (!read_model_file(sc.model_names[i], mfs[i], true, err, sc.model_cache != 0)) { g_front_error = err; return LINMT_EIO; }
     if (i && std::memcmp(&mfs[i].desc, &mfs[0].desc, sizeof(linmt_model_desc)) != 0) {
       g_front_error = "ensemble members must have the same dimensions";
       return LINMT_EINVAL;
@@ -341,6 +398,19 @@ int linmt_create(const char* config_path, linmt_engine** out) {
 }
 
 const char* linmt_front_error(void) { return g_front_error.c_str(); }
+
+int linmt_read_model_file(const char* path, linmt_model_desc* desc, float* blob, uint64_t blob_cap, int32_t use_cache) {
+  if (!path || !desc) return LINMT_EINVAL;
+  linmt::ModelFile mf;
+  std::string err;
+  if (!linmt::read_model_file(path, mf, blob != nullptr, err, use_cache != 0)) { g_front_error = err; return LINMT_EIO; }
+  *desc = mf.desc;
+  if (blob) {
+    if (blob_cap < mf.blob.size()) { g_front_error = "blob buffer too small"; return LINMT_ELIMIT; }
+    std::memcpy(blob, mf.blob.data(), mf.blob.size() * sizeof(float));
+  }
+  return LINMT_OK;
+}
 
 // DecoderSentence::Process (src/decoder_sentence.cu:40-49).
 const char* linmt_translate(linmt_engine* h, const char* sentence) {

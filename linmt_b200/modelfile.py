@@ -52,3 +52,22 @@ def write_config(path: str, model_paths, **kv):
         f.write(f'param="--nmt-model"   value="{" ".join(model_paths)}"\n')
         for k, v in kv.items():
             f.write(f'param="--{k.replace("_", "-")}"   value="{v}"\n')
+
+
+def read_model(path: str, use_cache: bool = True):
+    """Model file (the reference's text format, or its binary-body variant) -> (ModelDesc, blob),
+    through the library's own reader (linmt_read_model_file; no GPU involved)."""
+    import ctypes as C
+    from . import _lib
+    lib = _lib.load()
+    d = _lib.ModelDescC()
+    rc = lib.linmt_read_model_file(path.encode(), C.byref(d), None, 0, 0)
+    if rc != 0:
+        raise RuntimeError(f"linmt_read_model_file failed ({rc})")
+    desc = ModelDesc(L=d.layers, H=d.hidden, V=d.vocab_tgt, Vs=d.vocab_src, feed_input=d.feed_input)
+    n = int(lib.linmt_blob_floats(C.byref(d)))
+    blob = np.empty(n, np.float32)
+    rc = lib.linmt_read_model_file(path.encode(), C.byref(d), blob.ctypes.data_as(C.c_void_p), n, 1 if use_cache else 0)
+    if rc != 0:
+        raise RuntimeError(f"linmt_read_model_file failed ({rc})")
+    return desc, blob

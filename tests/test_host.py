@@ -130,3 +130,38 @@ def test_sharding_two_ranks_gloo():
     assert sorted(merged) == list(range(23))
     for i in range(23):
         assert merged[i] == (int(sents.ids[sents.off[i]:sents.off[i + 1]].sum()), int(sents.steps[i]))
+
+
+def test_text_model_reader_and_cache(tmp_path):
+    """Reference text model format -> blob through the library's reader, and the raw weight cache
+    beside the text file: written on the first load, used while the text file is unchanged,
+    ignored once it changes."""
+    import os
+    import time
+    from linmt_b200 import modelfile
+    d = synth.ModelDesc(2, 24, 37, 29, 1)
+    blob = synth.make_blob(d, 9)
+    path = str(tmp_path / "m.nmt")
+    modelfile.write_model(path, d, blob)
+    desc, got = modelfile.read_model(path, use_cache=False)
+    assert (desc.L, desc.H, desc.V, desc.Vs, desc.feed_input) == (2, 24, 37, 29, 1)
+    # the text carries 8 significant digits (src/deep_rnn.h:1991): values come back to fp32 rounding
+    np.testing.assert_allclose(got, blob, rtol=2e-7, atol=0)
+    assert not os.path.exists(path + ".linmtcache")
+    _, first = modelfile.read_model(path, use_cache=True)
+    assert os.path.exists(path + ".linmtcache")
+    _, second = modelfile.read_model(path, use_cache=True)          # from the cache
+    assert (first == got).all() and (second == got).all()
+    # a changed text file (other weights, newer mtime) must not be served from the old cache
+    blob2 = synth.make_blob(d, 10)
+    modelfile.write_model(path, d, blob2)
+    os.utime(path, (time.time() + 5, time.time() + 5))
+    _, third = modelfile.read_model(path, use_cache=True)
+    np.testing.assert_allclose(third, blob2, rtol=2e-7, atol=0)
+    # the binary-body variant of the same file
+    pathb = str(tmp_path / "mb.nmt")
+    modelfile.write_model(pathb, d, blob, binary=True)
+    _, gotb = modelfile.read_model(pathb, use_cache=False)
+    assert (gotb == blob).all()
+    with pytest.raises(RuntimeError):
+        modelfile.read_model(str(tmp_path / "missing.nmt"))
