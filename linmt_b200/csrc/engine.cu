@@ -257,13 +257,6 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   Vp = round_up(V, 128);
   B = o.max_batch; R = B * k;
   win = (o.attention_mode == LINMT_ATT_LOCAL_P_GENERAL) ? 2 * o.attention_d + 1 : o.max_src_len;
-  {
-    // local attention: keep the window's states in shared memory if they fit beside everything else
-    const size_t bytes = sizeof(float) * (((size_t)win + 8 + 3) + (size_t)win * Hp);
-    att_cache_ = o.attention_mode == LINMT_ATT_LOCAL_P_GENERAL && bytes <= 160 * 1024;
-    if (att_cache_ && cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
-      att_cache_ = false;
-  }
   Tcap = o.max_steps + 1;
   fin_cap = Tcap * k;
   CK(cudaSetDevice(o.device));
@@ -400,10 +393,10 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
-    const size_t smem = sizeof(float) * (((win + 8 + 3) & ~3) + (att_cache_ ? (size_t)win * Hp : 0));
+    const size_t smem = sizeof(float) * (win + 8);
     attention_kernel<<<rows, 256, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
                                                   opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
-                                                  tc::Planes{}, 0, att_cache_ ? 1 : 0);
+                                                  tc::Planes{}, 0);
     LAUNCHED();
   }
   // 5. attentional state htilde = tanh(W_c1 ctx + W_c2 h + b)

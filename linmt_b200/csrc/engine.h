@@ -110,7 +110,6 @@ class Engine {
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
-  bool att_cache_ = false; // local attention: window states cached in shared memory between the two sweeps
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
   int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair

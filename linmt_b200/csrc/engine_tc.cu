@@ -272,18 +272,10 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
-    const size_t smem = sizeof(float) * (((win + 8 + 3) & ~3) + (att_cache_ ? (size_t)win * Hp : 0));
-    if (att_cache_) {
-      // this translation unit's copy of the kernel needs its own opt-in to more than 48 KB
-      static size_t allowed = 0;
-      if (smem > allowed) {
-        CK(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        allowed = smem;
-      }
-    }
+    const size_t smem = sizeof(float) * (win + 8);
     CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, 2 * Hp, u_alt, Hp, (const float*)m.vp,
                     (const float*)s.hs, (const int32_t*)d_len_, (float*)nullptr, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
-                    (int)opt.attention_d, win, ra, rl, rv, ts.panel_top, nt_, att_cache_ ? 1 : 0));
+                    (int)opt.attention_d, win, ra, rl, rv, ts.panel_top, nt_));
     LAUNCHED();
   }
   // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)

@@ -149,21 +149,19 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   ctx  [rows][Hp] fp32 and/or ctx_planes (bf16 planes, columns [0,Hp) of the panel)
 //   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
 //   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
-// grid = rows, block = 256, dynamic smem = (win + 8) floats (+ win * Hp floats with cache = 1)
+// grid = rows, block = 256, dynamic smem = (win + 8) floats.  (Keeping the window's states in shared
+// memory between the score sweep and the context sweep was tried: 86 KB per CTA costs the occupancy that
+// the halved L2 traffic buys, no change in the decode time.)
 static __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
-                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt, int cache) {
+                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   extern __shared__ float sm[];
   float* e = sm;            // [win]
   float* red = sm + win;    // [8]
-  // cache = 1 (local attention): the window's encoder states are kept in shared memory between the
-  // score sweep and the context sweep, [win][Hp] floats after the two small arrays: the kernel is bound
-  // by L2 bandwidth (k beams x 21 rows x 4 KB, twice) and this halves it
-  float* hc = sm + ((win + 8 + 3) & ~3);
   __shared__ float s_pt;
   __shared__ int s_lo, s_hi;
   const int r = blockIdx.x;
@@ -196,7 +194,6 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
     float acc = 0.f;
     for (int j = lane * 4; j < Hp; j += 128) {
       const float4 a = *reinterpret_cast<const float4*>(hrow + j);
-      if (cache) *reinterpret_cast<float4*>(hc + (size_t)w * Hp + j) = a;
       const float4 b = *reinterpret_cast<const float4*>(u + j);
       acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
     }
@@ -245,8 +242,7 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int w = 0; w < W; ++w) {
       const float a = e[w];
-      const float4 h4 = cache ? *reinterpret_cast<const float4*>(hc + (size_t)w * Hp + j)
-                              : *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
+      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
       acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
     }
     if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
