@@ -410,3 +410,28 @@ def test_launch_variants_give_identical_bits(cuda_lib):
     for o in outs[1:]:
         assert (o["tok"] == outs[0]["tok"]).all() and (o["len"] == outs[0]["len"]).all()
         assert (o["score"] == outs[0]["score"]).all()
+
+
+@pytest.mark.parametrize("L,H,V,Vs,beam,att", [
+    (1, 100, 999, 777, 7, "local_p_general"),       # one layer, sizes that are multiples of nothing
+    (3, 250, 5003, 4001, 20, "local_p_general"),    # wide beam
+    (5, 96, 2000, 1500, 31, "global_general"),      # deepest stack and widest beam the library takes
+    (2, 520, 3000, 3000, 3, "global_dot"),          # H just over a padding boundary
+])
+@pytest.mark.parametrize("gemm_path", ["tensor", "simt"])
+def test_odd_shapes_against_checker(oracle, cuda_lib, L, H, V, Vs, beam, att, gemm_path):
+    """Model shapes off the beaten path (depth 1..5, hidden sizes that need padding, vocabularies
+    that are not multiples of the tile sizes, beam up to 31), forced-beam check against the checker."""
+    from linmt_b200 import decoder
+    d = synth.ModelDesc(L, H, V, Vs, 1)
+    blob = synth.make_blob(d, 100 + L)
+    sents = synth.make_sentences(5, 3, 17, Vs, 1.1, 11, lambda s: int(1.5 * s) + 3)
+    kw = dict(beam=beam, nbest=2, lp_alpha=0.65, cp_beta=0.1, attention=att, print_info=1)
+    o = oracle.decode(d, [blob], sents, trace=True, **kw)
+    dec = decoder.Decoder(d, [blob], max_batch=3, max_src_len=20, max_steps=32, gemm_path=gemm_path, **kw)
+    forced = dec.decode(sents, trace=True, force=o)
+    worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
+    assert worst <= RTOL_FP32 and bad == 0, (worst, bad, skipped, compared)
+    free = dec.decode(sents)
+    assert (free["len"][:, 0] > 0).all() and np.isfinite(free["score"][:, 0]).all()
+    dec.close()
