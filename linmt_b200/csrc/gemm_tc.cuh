@@ -42,6 +42,11 @@ constexpr int BK = 32;             // bf16 elements per stage row = 64 bytes -> 
 constexpr int UMMA_K = 16;         // bf16 elements per tcgen05.mma
 constexpr int kEpiWarps = 16;        // epilogue warps: four per TMEM lane quadrant
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 TMA, warp 1 MMA, then the epilogue warps
+// The one-tile kernel has a second MMA-issuing warp after the epilogue warps: with split operands the
+// leading product and the cross terms go to different accumulators, so two threads can issue them
+// independently -- a narrow tile is bound by what ONE thread can issue (~58 ns per MMA).
+constexpr int kIssue2Warp = 2 + kEpiWarps;
+constexpr int kThreadsMain = kThreads + 32;
 constexpr unsigned long long kWaitCycles = 2000000000ull;  // ~1 s at 2 GHz
 
 struct alignas(64) TmapSet {
@@ -562,7 +567,7 @@ __device__ __forceinline__ void tc_prof(int slot) {
 
 // ---- kernel -------------------------------------------------------------------------------
 template <int NT, int BKT, int FMT, class Epi>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsMain, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, int kDrainEvery, Epi epi,
                int* __restrict__ err_flag, int splits, float* __restrict__ ws, int* __restrict__ tile_counters) {
   constexpr int PC = product_code(NT, FMT);
@@ -594,8 +599,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   if (threadIdx.x == 0) {
     TC_PROF(0);
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
-    mbar_init(accum_bar, 1);
+    // with split operands two threads issue MMAs: a stage is free, and the tile complete, when both have committed
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), NP > 1 ? 2 : 1); }
+    mbar_init(accum_bar, NP > 1 ? 2 : 1);
     mbar_init(main_full, 1);
     mbar_init(main_free, kEpiWarps);  // one arrival per epilogue warp
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -645,8 +651,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(BM, BN, FMT);
-      const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
-      const uint64_t bstep = (uint64_t)(B_BYTES >> 4);           // one B plane, in descriptor units (16 bytes)
       int s = 0; uint32_t ph = 0;
       uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
       for (int kb = 0; kb < nkb; ++kb) {
@@ -661,16 +665,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
           for (int ks = 0; ks < BK / UMMA_K; ++ks)
             umma_bf16(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (kb | ks) ? 1u : 0u);
         } else {
-          // small cross terms: one long chain in accumulator 1
-#pragma unroll
-          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-#pragma unroll
-            for (int p = 0; p < NP - 1; ++p) {
-              const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
-              const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
-              umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
-            }
-          }
+          // (the small cross terms are the other issuing warp's)
           // leading product: accumulator 0 holds only kDrainEvery k-blocks at a time; the epilogue
           // warps add each partial sum into registers and hand the accumulator back
           const int in_chunk = kb % kDrainEvery;
@@ -689,6 +684,34 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
       }
       TC_PROF(3);
+      umma_commit(accum_bar);
+    }
+  } else if (warp == kIssue2Warp) {
+    if (NP > 1 && lane == 0) {
+      // second issuer: the small cross terms, one long chain in accumulator 1
+      const uint32_t idesc = make_idesc(BM, BN, FMT);
+      const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
+      const uint64_t bstep = (uint64_t)(B_BYTES >> 4);           // one B plane, in descriptor units (16 bytes)
+      int s = 0; uint32_t ph = 0;
+      uint32_t st = base, fb = bars, eb = bars + 8u * STAGES;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(fb, ph, &s_abort)) break;
+        tc_fence_after();
+        const uint64_t a0 = make_desc<BKT>(st);
+        const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+#pragma unroll
+          for (int p = 0; p < NP - 1; ++p) {
+            const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
+            const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
+            umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
+          }
+        }
+        umma_commit(eb);
+        st += STAGE_BYTES; fb += 8u; eb += 8u;
+        if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
+      }
       umma_commit(accum_bar);
     }
   } else {
@@ -805,7 +828,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       __threadfence();
     }
     __syncthreads();
-    if (s_last && warp >= 2) {
+    if (s_last && warp >= 2 && warp < kIssue2Warp) {
       const int q = warp & 3, half = (warp - 2) >> 2;
       const int row = m0 + q * 32 + lane;
       if (row < M) {
@@ -1049,7 +1072,7 @@ inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, con
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
   int drain = (sh.drain > 0 ? sh.drain : kDrainDefault) * 32 / BKT;
   if (drain < 1) drain = 1;
-  return launch_k(sh.pdl != 0, gemm_tc_kernel<NT, BKT, FMT, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, sh.bn,
+  return launch_k(sh.pdl != 0, gemm_tc_kernel<NT, BKT, FMT, Epi>, grid, dim3(kThreadsMain), (size_t)sh.smem_bytes, st, tm, M, N, K, sh.bn,
                   sh.stages, drain, epi, err_flag, splits, splits > 1 ? ws : (float*)nullptr, counters);
 }
 template <class Epi>
