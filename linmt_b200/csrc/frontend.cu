@@ -301,7 +301,15 @@ static std::string float_to_string(float v) {  // std::stringstream << float, sr
 // Text of Decoder<T>::ObtainOneBestHypothesis's result (src/decoder.h:777-856) followed by
 // DecoderSentence::UnintSentence (src/decoder_sentence.cu:72-107).
 std::string format_result(const Engine& e, int S, int nbest, int max_len, const int32_t* tok, const int32_t* len,
-                          const float* score, const int32_t* vit, const float* align, int max_src) {
+                          const float* score, const int32_t* vit, const float* align, int max_src, bool fixed3 = false) {
+  // file mode prints every float with three decimals (the stream is set to fixed, precision 3,
+  // src/decoder.h:267); sentence mode with the stream's default six significant digits
+  auto fmt = [&](float v) {
+    if (!fixed3) return float_to_string(v);
+    char b[64];
+    std::snprintf(b, sizeof b, "%.3f", v);
+    return std::string(b);
+  };
   std::string ids_out;
   for (int q = 0; q < nbest; ++q) {
     const int n = len[q];
@@ -315,7 +323,7 @@ std::string format_result(const Engine& e, int S, int nbest, int max_len, const 
       first = false;
     }
     if (e.opt.print_info) {
-      ids_out += " |||| " + float_to_string(score[q]);
+      ids_out += " |||| " + fmt(score[q]);
       ids_out += " ||||";
       int cnt = 0;
       for (int j = 1; j < n - 1; ++j) { ++cnt; ids_out += " " + std::to_string(v[j + 1]); }
@@ -333,7 +341,7 @@ std::string format_result(const Engine& e, int S, int nbest, int max_len, const 
           ids_out += " ";
           for (int s = 0; s < S; ++s) {
             if (s) ids_out += "/";
-            ids_out += float_to_string(align[((size_t)q * max_len + (j + 1)) * max_src + s]);
+            ids_out += fmt(align[((size_t)q * max_len + (j + 1)) * max_src + s]);
           }
         }
         if (c2 == 0) ids_out += " ";
@@ -518,19 +526,10 @@ int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path
       for (int q = 0; q < nb; ++q) {
         const size_t ob = (size_t)i * nb + q;
         if (len[ob] == 0) continue;
-        // one hypothesis through the sentence formatter, then the score re-printed with three decimals
+        // one hypothesis through the sentence formatter, floats with three decimals
         int32_t one_len = len[ob];
         std::string hyp = format_result(e, S, 1, max_len, &tok[ob * max_len], &one_len, &score[ob], &vit[ob * max_len],
-                                        want_align ? &align[ob * max_len * e.opt.max_src_len] : nullptr, e.opt.max_src_len);
-        if (info) {
-          const size_t p1 = hyp.find(" |||| ");
-          if (p1 != std::string::npos) {
-            const size_t p2 = hyp.find(" ||||", p1 + 6);
-            char buf[64];
-            std::snprintf(buf, sizeof buf, "%.3f", score[ob]);
-            if (p2 != std::string::npos) hyp = hyp.substr(0, p1 + 6) + buf + hyp.substr(p2);
-          }
-        }
+                                        want_align ? &align[ob * max_len * e.opt.max_src_len] : nullptr, e.opt.max_src_len, true);
         out += hyp + "\n";
       }
       if (nb != 1) out += "================\n";

@@ -1142,26 +1142,25 @@ inline int pick_bn(int M, int N, int n_sm) {
 // waves * (k-blocks-per-CTA of those + ~8-13 us of prologue/epilogue per tile), plus the cost of
 // writing and re-reading partial tiles when K is split (only worth it for tiles up to 176 wide).
 // ws_floats bounds the split-K workspace (splits * padded rows * N floats).
-// The f16 pair runs 64-deep stages (128-byte rows) and is bound by shared-memory bandwidth rather
-// than by the tensor pipe: per k-block a CTA writes planes * (128 + bn) * 128 bytes (TMA) and the
-// twelve MMAs read 128 * 32 + bn * 32 bytes each, at 128 bytes per clock (measured slopes:
-// 770 ns per k-block at bn = 176, 1040 ns at bn = 256); per tile ~6 us + 12 ns per column of
-// prologue and epilogue; a split costs the partial tile's round trip.
+// The f16 pair with 64-deep stages, measured (two issuing threads): a k-block costs ~490 ns while the
+// issuing threads are the limit (tiles up to ~100 wide) and 120 + 3.6 * bn ns beyond (the tensor pipe at
+// its practical rate); per tile ~6 us + 12 ns per column of prologue and epilogue; a split adds ~2 us plus
+// 0.28 ns per partial-tile element that is written and read back (valid rows only).
 inline void pick_shape_f16(int M, int N, int K, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out) {
   const int mt = (M + BM - 1) / BM;
   const int nkb = K / 64;
+  const double rows_per_tile = (double)M / mt;
   double best = 1e30;
   int best_bn = 256, best_s = 1;
   for (int bn = 256; bn >= 64; bn -= 16) {
     const long tiles = (long)mt * ((N + bn - 1) / bn);
-    const double smem_ns = (12.0 * (BM * 32 + bn * 32) + 2.0 * (BM + bn) * 128.0) / 128.0 / 1.84;
-    const double issue_ns = 12.0 * 50.0;
-    const double per_kb = smem_ns > issue_ns ? smem_ns : issue_ns;
+    const double wide = 120.0 + 3.6 * bn;
+    const double per_kb = wide > 490.0 ? wide : 490.0;
     for (int s = 1; s <= 6; ++s) {
       if (s > 1 && (bn > 208 || nkb / s < 2 || tiles > max_tiles || (size_t)s * mt * BM * (size_t)N > ws_floats)) break;
       const long waves = (tiles * s + n_sm - 1) / n_sm;
       const double kb_per_cta = (double)((nkb + s - 1) / s);
-      const double cost = waves * (kb_per_cta * per_kb + 6000.0 + bn * 12.0) + (s > 1 ? 4000.0 + 2000.0 * s + bn * 10.0 * (s + 1) : 0.0);
+      const double cost = waves * (kb_per_cta * per_kb + 6000.0 + bn * 12.0) + (s > 1 ? 2000.0 + 0.28 * s * rows_per_tile * bn : 0.0);
       if (cost < best - 1e-9) { best = cost; best_bn = bn; best_s = s; }
     }
   }

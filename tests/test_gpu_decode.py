@@ -286,7 +286,7 @@ def test_file_mode_matches_checker(oracle, cuda_lib, tmp_path):
     mp, cp = tmp_path / "model.nmt", tmp_path / "dec.config"
     modelfile.write_model(str(mp), d, blob, binary=True)
     modelfile.write_config(str(cp), [str(mp)], beam_size=3, nbest=2, longest_sent=20, lp_alpha=0.65, cp_beta=0.2,
-                           print_decoding_info=1, batch_size=2)
+                           print_decoding_info=1, print_align_scores=1, batch_size=2)
     src = modelfile.default_vocab(d.Vs, "src")
     tgt = modelfile.default_vocab(d.V, "tgt")
     rng = np.random.default_rng(3)
@@ -313,6 +313,15 @@ def test_file_mode_matches_checker(oracle, cuda_lib, tmp_path):
             assert fields[0] == " ".join(tgt[t] for t in o["tok"][0, q, 1:n - 1])
             assert abs(float(fields[1]) - float(o["score"][0, q])) <= 1.5e-3
             assert len(fields[1].split(".")[1]) == 3
+            # dense alignment scores: one a/a/.../a group of S values per target word, three decimals
+            assert len(fields) == 5
+            groups = fields[4].split()
+            assert len(groups) == n - 2
+            for j, grp in enumerate(groups):
+                vals = grp.split("/")
+                assert len(vals) == S and all(len(v.split(".")[1]) == 3 for v in vals)
+                ref = o["align"][0, q, j + 2, :S]
+                assert np.abs(np.array([float(v) for v in vals]) - ref).max() <= 1.5e-3
 
 
 import functools
