@@ -100,7 +100,9 @@ template <class Epi>
 int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt, int drain) {
   if (nt <= 0 || nt > nt_) nt = nt_;
   int bn = 0, splits = 1;
-  const size_t ws_floats = kSplitKWsFloats / ws_parts_;
+  // a layer's slice of the split-K workspace: whole 256-byte units, so that every slice starts aligned for the
+  // 16-byte partial-tile stores whatever the number of layers sharing it
+  const size_t ws_floats = (kSplitKWsFloats / ws_parts_) & ~(size_t)63;
   const int max_tiles = kSplitKMaxTiles / ws_parts_;
   tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits, fmt_);
   // one plane (bf16 precision): 64-deep stages with 128-byte rows halve the per-k-block overheads
