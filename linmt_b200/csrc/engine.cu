@@ -235,6 +235,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
+  { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
@@ -288,6 +289,8 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   DA(d_fin_score_, (size_t)B * fin_cap); DA(d_fin_final_, (size_t)B * fin_cap);
   if (nm > 1) DA(d_combined_, (size_t)R * Vp);
   DA(d_cand_idx_, (size_t)R * kk); DA(d_cand_logp_, (size_t)R * kk); DA(d_eos_logp_, R); DA(d_row_stats_, 2 * (size_t)R);
+  pmax_ld_ = 4 * ((Vp + 63) / 64) + 4;
+  DA(d_pmax_, (size_t)R * pmax_ld_);
   if (o.print_info) {
     DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
   }
@@ -428,7 +431,7 @@ int Engine::step_tail(int t, int rows) {
     trace_dev_.ld_logits = Vp;
     trace_dev_.row_stats = d_row_stats_;
     if (n_models == 1) {
-      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_));
+      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_));
     } else {
       // EnsembleFactory::EnsemblesModels (src/decoder.h:1910-1931): mean of the members'
       // probabilities, renormalised -- written as log(mean p) so that the log-softmax of the

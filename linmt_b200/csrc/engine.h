@@ -110,6 +110,7 @@ class Engine {
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
+  bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
   int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair
@@ -144,6 +145,9 @@ class Engine {
   float* d_combined_ = nullptr;  // [R][Vp] ensemble-combined log-values (n_models > 1)
   int32_t* d_cand_idx_ = nullptr;
   float *d_cand_logp_ = nullptr, *d_eos_logp_ = nullptr, *d_row_stats_ = nullptr;
+  float* d_pmax_ = nullptr;   // [R][pmax_ld_] block maxima of the logits, by-product of the vocabulary GEMM
+  int pmax_ld_ = 0;
+  int pmax_slots_ = 0;        // slots the last vocabulary GEMM filled (0 = none: the softmax finds its own maxima)
   // alignment records (print_info)
   float* d_rec_align_ = nullptr;
   int32_t *d_rec_lo_ = nullptr, *d_rec_vit_ = nullptr;

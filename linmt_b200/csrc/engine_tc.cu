@@ -97,7 +97,8 @@ const CUtensorMap* Engine::b_maps(const tc::Planes& p, int rows, int K, int bn, 
 
 // C[M][N] = A[:, a_col0 : a_col0+K] . W[N][K]^T with the tile width chosen for this shape.
 template <class Epi>
-int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e, int nt, int drain) {
+int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::Planes& W, int M, int N, int K, const Epi& e_in, int nt, int drain) {
+  Epi e = e_in;
   if (nt <= 0 || nt > nt_) nt = nt_;
   int bn = 0, splits = 1;
   // a layer's slice of the split-K workspace: whole 256-byte units, so that every slice starts aligned for the
@@ -122,6 +123,13 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   sh.splits = splits;
   if (drain > 0) sh.drain = drain;
   sh.pdl = (pdl_ && pdl_gemm_) ? 1 : 0;
+  if constexpr (Epi::kHasPmax) {
+    // block maxima for the softmax: four column blocks per tile; not from the split-K fix-up path
+    if (e.pmax) {
+      if (splits > 1) { e.pmax = nullptr; pmax_slots_ = 0; }
+      else pmax_slots_ = 4 * ((N + bn - 1) / bn);
+    }
+  }
   // many waves of tiles whose leading product is one chain: one persistent CTA per SM
   const long tiles = (long)((M + tc::BM - 1) / tc::BM) * ((N + bn - 1) / bn);
   if (persist_ && nt == 2 && splits == 1 && drain >= K / 32 && tiles > n_sm_) {
@@ -289,6 +297,8 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   // 6. logits
   {
     tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
+    pmax_slots_ = 0;
+    if (n_models == 1 && pmax_on_) { e.pmax = d_pmax_; e.pmax_ld = pmax_ld_; e.n_valid = V; }
     if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
     // Logits feed only the softmax of their own step: the tensor core's truncation bias over one
     // K = Hp chain (~32 ulp of the accumulator, 2e-7 relative on a log-probability) does not

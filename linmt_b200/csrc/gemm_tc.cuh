@@ -360,7 +360,8 @@ struct TcEpiLstm {
   // the staging area with consecutive lanes on consecutive addresses; h goes out as planes the
   // same way.  Rows past their length (encoder) keep c and copy h_prev.
   static constexpr bool kHasBlock = true;
-  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf) const {
+  static constexpr bool kHasPmax = false;
+  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf, int /*slot*/) const {
     const int nq = nch;                      // float4 groups (4 hidden units each) per row
     const int j_first = col_first >> 2;
     const int row = row0 + lane;
@@ -451,7 +452,8 @@ struct TcEpiBiasTanh {
   Planes out; int col_off;
   int nt;
   static constexpr bool kHasBlock = false;
-  __device__ __forceinline__ void block(int, int, int, int, int, float (*)[16], float*) const {}
+  static constexpr bool kHasPmax = false;
+  __device__ __forceinline__ void block(int, int, int, int, int, float (*)[16], float*, int) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
     const size_t idx = (size_t)row * out.ld + col_off + col0;
 #pragma unroll
@@ -468,6 +470,10 @@ struct TcEpiF32 {
   const float* bias;  // may be null
   float* out; int ld;
   int split;          // columns < split get tanh
+  // Optional by-product for the softmax that follows a logits GEMM: the maximum of every block of up to
+  // 64 columns (tile column block `slot`) of every row, over columns < n_valid, at pmax[row * pmax_ld + slot].
+  // The softmax kernel then needs no first sweep over the row for its maximum and its top-k threshold.
+  float* pmax = nullptr; int pmax_ld = 0; int n_valid = 0;
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
     float* o = out + (size_t)row * ld + col0;
 #pragma unroll
@@ -484,7 +490,41 @@ struct TcEpiF32 {
   // Block form (see TcEpiLstm::block): bias / tanh in registers, the block of up to 64 columns
   // staged per row, then stored with a row's 16 float4 on consecutive lanes.
   static constexpr bool kHasBlock = true;
-  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf) const {
+  static constexpr bool kHasPmax = true;
+  __device__ __forceinline__ void pmax_store(int row, int M, int slot, float m) const {
+    if (pmax && row < M) pmax[(size_t)row * pmax_ld + slot] = m;
+  }
+  // the same block without staging (row-per-lane stores), for callers whose staging area is busy
+  __device__ __forceinline__ void direct_block(int row, int M, int col_first, int nch, float (*v)[16], int slot) const {
+    float m = -INFINITY;
+    if (row < M) {
+#pragma unroll
+      for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
+        if (ci < nch) {
+          const int col0 = col_first + 16 * ci;
+          float* o = out + (size_t)row * ld + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float4 r = make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]);
+            if (bias) {
+              const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
+              r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+            }
+            if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
+            *reinterpret_cast<float4*>(o + 4 * q) = r;
+            const int c = col0 + 4 * q;
+            if (c + 0 < n_valid) m = fmaxf(m, r.x);
+            if (c + 1 < n_valid) m = fmaxf(m, r.y);
+            if (c + 2 < n_valid) m = fmaxf(m, r.z);
+            if (c + 3 < n_valid) m = fmaxf(m, r.w);
+          }
+        }
+      }
+    }
+    pmax_store(row, M, slot, m);
+  }
+  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf, int slot) const {
+    float m = -INFINITY;
 #pragma unroll
     for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
       if (ci < nch) {
@@ -498,9 +538,15 @@ struct TcEpiF32 {
           }
           if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
           *reinterpret_cast<float4*>(sbuf + lane * kEpiScratchStride + 16 * ci + 4 * q) = r;
+          const int c = col0 + 4 * q;
+          if (c + 0 < n_valid) m = fmaxf(m, r.x);
+          if (c + 1 < n_valid) m = fmaxf(m, r.y);
+          if (c + 2 < n_valid) m = fmaxf(m, r.z);
+          if (c + 3 < n_valid) m = fmaxf(m, r.w);
         }
       }
     }
+    pmax_store(row0 + lane, M, slot, m);
     __syncwarp();
     const int nq = 4 * nch;   // float4 per row
     for (int s = lane; s < 32 * nq; s += 32) {
@@ -743,7 +789,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     auto finish = [&]() {
       if (splits == 1) {
         if (Epi::kHasBlock) {
-          if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf);
+          const int slot = (int)blockIdx.y * kParts + part;
+          if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf, slot);
+          else if constexpr (Epi::kHasPmax) epi.pmax_store(row, M, slot, -INFINITY);
         } else if (row < M) {
 #pragma unroll
           for (int ci = 0; ci < kChunks; ++ci)
@@ -1005,9 +1053,13 @@ gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, 
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_free);   // the tensor core may start the next tile
       const bool last = tile + (int)gridDim.x >= ntile;
+      const int slot = (tile / mt) * kParts + part;
       if (last && Epi::kHasBlock) {
         // the ring is idle from here on: stage and store coalesced
-        if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf);
+        if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf, slot);
+        else if constexpr (Epi::kHasPmax) epi.pmax_store(row0 + lane, M, slot, -INFINITY);
+      } else if constexpr (Epi::kHasPmax) {
+        epi.direct_block(row0 + lane, M, n0 + ch0 * 16, nmine, macc, slot);
       } else if (row0 + lane < M) {
 #pragma unroll
         for (int ci = 0; ci < kChunks; ++ci)

@@ -276,7 +276,7 @@ __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { ret
 // (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
 constexpr int kTopkCap = 1024;
 static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
-                                                                  int normalise) {
+                                                                  int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   __shared__ float s_tmax[256];
@@ -290,9 +290,12 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   const int warp = tid >> 5, lane = tid & 31;
   const float* z = logits + (size_t)r * ld;
   const int V4 = V & ~3;
-  // ---- pass 1: maxima (four independent 16-byte loads in flight per thread) ----
+  // ---- pass 1: maxima (four independent 16-byte loads in flight per thread) -- or, when the GEMM that
+  // produced the logits left the maxima of disjoint column blocks of every row (pmax), just those ----
   float m = -INFINITY;
-  {
+  if (pmax) {
+    for (int s = tid; s < n_slots; s += 256) m = fmaxf(m, pmax[(size_t)r * pmax_ld + s]);
+  } else {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
     int i = tid * 4;
     for (; i + 3 * 1024 < V4; i += 4 * 1024) {
@@ -310,8 +313,8 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
       m0 = fmaxf(fmaxf(m0, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
     }
     m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    for (int i = V4 + tid; i < V; i += 256) m = fmaxf(m, z[i]);
   }
-  for (int i = V4 + tid; i < V; i += 256) m = fmaxf(m, z[i]);
   s_tmax[tid] = m;
   if (tid == 0) s_count = 0;
   __syncthreads();
@@ -427,8 +430,9 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
 }
 
 inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, int normalise,
-                                       cudaStream_t st, bool pdl = false) {
-  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, kk, out, normalise);
+                                       cudaStream_t st, bool pdl = false, const float* pmax = nullptr, int pmax_ld = 0, int n_slots = 0) {
+  if (n_slots <= 0) pmax = nullptr;
+  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, kk, out, normalise, pmax, pmax_ld, n_slots);
 }
 
 // ---------------------------------------------------------------------------------------
