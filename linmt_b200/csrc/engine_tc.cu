@@ -105,7 +105,10 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   // 16-byte partial-tile stores whatever the number of layers sharing it
   const size_t ws_floats = (kSplitKWsFloats / ws_parts_) & ~(size_t)63;
   const int max_tiles = kSplitKMaxTiles / ws_parts_;
-  tc::pick_shape(M, N, K, nt, n_sm_, ws_floats, max_tiles, &bn, &splits, fmt_);
+  // The encoder runs its L layers as a wavefront on L streams: a GEMM sized for the whole machine would only
+  // queue behind its neighbours, so there each one is shaped for its share of the SMs and they run side by side.
+  const int sm_budget = ws_parts_ > 1 ? (n_sm_ / ws_parts_ > 0 ? n_sm_ / ws_parts_ : 1) : n_sm_;
+  tc::pick_shape(M, N, K, nt, sm_budget, ws_floats, max_tiles, &bn, &splits, fmt_);
   // one plane (bf16 precision): 64-deep stages with 128-byte rows halve the per-k-block overheads
   // (measured 1.5x on the gate GEMMs); with split operands only 32-deep stages leave room for a ring
   // the f16 pair: 64-deep stages as well, except for a weight matrix far larger than L2 under
