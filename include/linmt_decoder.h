@@ -61,8 +61,11 @@ enum { LINMT_PREC_FP32 = 0, LINMT_PREC_BF16 = 1 };
  * tensor-core kernels; with fp32 precision every operand is held as an fp16 pair x ~ a0 + 2^-11 a1
  * (22 mantissa bits, three partial products per product, fp32-class accuracy; operands must be
  * below 65504 in magnitude).  TENSOR3 = three bf16 planes (six partial products, same accuracy,
- * no range limit), TENSOR2 = two bf16 planes (error ~2^-17 per product).  AUTO = TENSOR. */
-enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3, LINMT_GEMM_TENSOR3 = 4 };
+ * no range limit), TENSOR2 = two bf16 planes (error ~2^-17 per product).  TENSOR_V16 = TENSOR for the
+ * recurrent and attention products, but the vocabulary projection in plain fp16 (one product instead of three:
+ * logits carry ~2^-12 relative noise, 1e-5 on a log-probability; near-ties in the beam may resolve differently;
+ * ~15 % faster).  AUTO = TENSOR. */
+enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3, LINMT_GEMM_TENSOR3 = 4, LINMT_GEMM_TENSOR_V16 = 5 };
 
 /* Model dimensions: first five of the nine integers on line 1 of a model file
  * (src/decoder.h:1202-1210). */

@@ -231,7 +231,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (nm > 8) return fail(LINMT_ELIMIT, "at most 8 ensemble members");
   if (nm > 1 && o.print_info) return fail(LINMT_EINVAL, "alignment output (print_info) is not available with ensembles");
   if (o.precision != LINMT_PREC_FP32 && o.precision != LINMT_PREC_BF16) return fail(LINMT_EINVAL, "bad precision");
-  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR3) return fail(LINMT_EINVAL, "bad gemm_path");
+  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR_V16) return fail(LINMT_EINVAL, "bad gemm_path");
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
@@ -239,12 +239,13 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
-  fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR)) ? 1 : 0;
+  fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR || o.gemm_path == LINMT_GEMM_TENSOR_V16)) ? 1 : 0;
   nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR3 ? 3 : 2);
   // The vocabulary product feeds only the softmax of its own step (nothing recurrent), so two
   // planes (error ~2^-17 per product, ~3e-7 relative on a log-probability) are enough there:
   // measured parity on the 64-sentence reference configuration is unchanged and the GEMM is 1.3x faster.
   nt_vocab_ = (nt_ == 3) ? 2 : nt_;
+  if (fmt_ == 1 && o.gemm_path == LINMT_GEMM_TENSOR_V16) nt_vocab_ = 1;   // plain fp16 logits: the first plane of each pair
   if (linmt_blob_floats(&d) != blob_floats) return fail(LINMT_EINVAL, "weight blob size does not match the model dimensions");
   if (o.beam <= 0) return fail(LINMT_EINVAL, "--beam-size cannot be <= 0");
   if (o.penalty < 0) return fail(LINMT_EINVAL, "--penalty cannot be < 0");

@@ -115,7 +115,7 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   // the widest tiles, where only two such stages fit and four 32-deep ones hide DRAM latency better
   // (vocabulary GEMM: 143 us against 149 us)
   int bk = (nt == 1) ? 64 : 32;
-  if (fmt_ == 1 && K % 64 == 0) bk = (bn >= 240 && (size_t)N * K * 4 > ((size_t)96 << 20)) ? 32 : 64;
+  if (fmt_ == 1 && nt == 2 && K % 64 == 0) bk = (bn >= 240 && (size_t)N * K * 4 > ((size_t)96 << 20)) ? 32 : 64;
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K, bk);
   const CUtensorMap* bm = b_maps(W, N, K, bn, bk);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");

@@ -565,7 +565,8 @@ __host__ __device__ inline int acc_stride(int bn) { return (bn + 31) & ~31; }
 // Partial products (plane of A, plane of B): the small cross terms first, the leading p0p0 last.
 // The first argument is a product-set code: the plane count for bf16 planes, kF16PairCode for the f16 pair.
 constexpr int kF16PairCode = 4;
-__host__ __device__ constexpr int product_code(int nt, int fmt) { return fmt ? kF16PairCode : nt; }
+// (one plane of an fp16 pair is a plain fp16 operand: one product)
+__host__ __device__ constexpr int product_code(int nt, int fmt) { return (fmt && nt == 2) ? kF16PairCode : nt; }
 __host__ __device__ constexpr int num_products(int nt) { return nt == 1 ? 1 : (nt == 2 ? 4 : (nt == kF16PairCode ? 3 : 6)); }
 __host__ __device__ constexpr int prod_a(int nt, int p) {
   return nt == kF16PairCode ? (p == 0 ? 1 : 0)
@@ -1131,6 +1132,10 @@ template <class Epi>
 inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                   cudaStream_t st, float* ws = nullptr, int* counters = nullptr) {
   if (sh.fmt == 1) {
+    if (sh.nt == 1) {
+      if (sh.bk == 64) return launch_gemm_tc_nt<1, 64, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+      return launch_gemm_tc_nt<1, 32, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
+    }
     if (sh.nt != 2) return cudaErrorInvalidValue;
     if (sh.bk == 64) return launch_gemm_tc_nt<2, 64, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
     return launch_gemm_tc_nt<2, 32, 1, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
@@ -1221,7 +1226,7 @@ inline void pick_shape_f16(int M, int N, int K, int n_sm, size_t ws_floats, int 
 }
 
 inline void pick_shape(int M, int N, int K, int nt, int n_sm, size_t ws_floats, int max_tiles, int* bn_out, int* splits_out, int fmt = 0) {
-  if (fmt == 1 && K % 64 == 0) { pick_shape_f16(M, N, K, n_sm, ws_floats, max_tiles, bn_out, splits_out); return; }
+  if (fmt == 1 && nt == 2 && K % 64 == 0) { pick_shape_f16(M, N, K, n_sm, ws_floats, max_tiles, bn_out, splits_out); return; }
   const int mt = (M + BM - 1) / BM;
   const int nkb = K / BK;
   const int np = num_products(product_code(nt, fmt));
