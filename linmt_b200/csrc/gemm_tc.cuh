@@ -3,30 +3,32 @@
 //
 //   C[M][N] = A[M][K] . Wt[N][K]^T        (both operands K-contiguous, "K-major")
 //
-// Precision.  The tensor cores multiply bf16.  An fp32 operand x is held as NT bf16 planes
-// x ~ p0 + p1 (+ p2), p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1); a product of
-// two split operands is the sum of the partial products whose weight is at least 2^-16
+// Precision.  The tensor cores multiply 16-bit operands.  An fp32 operand x is held as planes.
+// Plane format 0: NT bf16 planes x ~ p0 + p1 (+ p2), p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1);
+// a product of two split operands is the sum of the partial products whose weight is at least 2^-16
 // (NT = 3: p0p0, p0p1, p1p0, p1p1, p0p2, p2p0 -- error ~2^-23 per product, i.e. fp32-class
-// results; NT = 2: p0p0, p0p1, p1p0, p1p1 -- error ~2^-17; NT = 1: plain bf16).  The tensor
-// core truncates a little on every accumulate, in units of the accumulator's magnitude, so the
-// leading product p0p0 has a TMEM accumulator of its own and the small cross terms share a
-// second one (their truncation is 2^-8 smaller in absolute terms); the epilogue adds the two.
+// results; NT = 2: p0p0, p0p1, p1p0, p1p1 -- error ~2^-17; NT = 1: plain bf16).
+// Plane format 1 ("f16 pair", the default for fp32 weights) reaches the same accuracy with half the
+// tensor work: x ~ a0 + 2^-11 a1 with a0 = fp16(x), a1 = fp16((x - a0) * 2^11) -- two 11-bit mantissas,
+// 22 bits in all, the residual scaled back into fp16's normal range -- and three partial products a0b0
+// (own accumulator), a0b1 + a1b0 (second accumulator, weighted 2^-11 when the two are added); the
+// dropped a1b1 weighs 2^-22.  Operands must stay below fp16's largest finite value (65504).
+// The tensor core truncates a little on every accumulate, in units of the accumulator's magnitude, so
+// the leading product has a TMEM accumulator of its own, drained into fp32 registers every few k-blocks
+// (two-level accumulation), and the small cross terms share a second one; the epilogue adds the two.
 // Measured against a float64 product this gives the error of an fp32 FMA loop.
-//
-// Plane format 1 ("f16 pair") reaches the same accuracy with half the tensor work: x ~ a0 + 2^-11 a1
-// with a0 = fp16(x), a1 = fp16((x - a0) * 2^11) -- two 11-bit mantissas, 22 bits in all, the
-// residual scaled back into fp16's normal range -- and three partial products a0b0 (own
-// accumulator), a0b1 + a1b0 (second accumulator, weighted 2^-11 when the two are added); the dropped
-// a1b1 weighs 2^-22.  Operands must stay below fp16's largest finite value (65504).
 //
 // One CTA computes one 128 x BN tile; BN (a multiple of 16 up to 256) is a launch parameter so
 // the host can size the grid to the 148 SMs for every problem shape.  Warp 0 issues the TMA
-// loads, warp 1 owns TMEM and issues the MMAs, warps 2..17 run the epilogue (tcgen05.ld ->
-// registers -> fused math -> global; four warps per TMEM lane quadrant, interleaved column chunks).  The single issuing threads are the critical path of a
-// narrow tile, so their loops carry descriptors forward by constant increments and everything
-// that can be is a compile-time constant; the waiting epilogue warps sleep between polls.
-// A ring of shared-memory stages is handed back and forth with mbarriers; every wait is
-// bounded and reports through an error flag instead of hanging.
+// loads, warp 1 owns TMEM and issues the leading-product MMAs, warps 2..17 run the epilogue
+// (tcgen05.ld -> registers -> fused math -> staging in the idle stage ring -> coalesced stores; four
+// warps per TMEM lane quadrant, each a contiguous block of columns), warp 18 issues the cross-term
+// MMAs.  The issuing threads are the critical path of a narrow tile, so their loops carry descriptors
+// forward by constant increments and everything that can be is a compile-time constant; the waiting
+// epilogue warps sleep between polls.  A ring of shared-memory stages is handed back and forth with
+// mbarriers; every wait is bounded and reports through an error flag instead of hanging.  All kernels
+// take part in programmatic dependent launch (see pdl_wait below).  A persistent variant
+// (gemm_tc_persist_kernel) serves the many-wave vocabulary GEMM.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
