@@ -337,7 +337,7 @@ def run_ours(args):
                             "tensor_pipe_* counts; the bf16 path runs 1"}
 
         r_voc = roof("vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path)", flops_local, gemm_ms, gemm_n,
-                     (4 if args.gemm_path in ("tensor2", "tensor3") else (1 if args.gemm_path == "tensor_v16" else 3)) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
+                     (4 if args.gemm_path in ("tensor2", "tensor3") else (1 if args.gemm_path in ("tensor_v16", "tensor_v16x", "auto") and len(blobs) == 1 else 3)) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
         r_rec = roof("decoder LSTM gate GEMMs [rows,2H|3H]x[.,4H], fused cell update (" + args.gemm_path + " path)",
                      rec["flops"], rec["ms"], rec["n"],
                      {"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1,
@@ -375,7 +375,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor", "tensor2", "tensor3", "tensor_v16"])
+    ap.add_argument("--gemm-path", default="auto", choices=["auto", "simt", "tensor", "tensor2", "tensor3", "tensor_v16", "tensor_v16x"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default=None, choices=["fp32", "bf16"], help="override the workload's precision")

@@ -64,8 +64,11 @@ enum { LINMT_PREC_FP32 = 0, LINMT_PREC_BF16 = 1 };
  * no range limit), TENSOR2 = two bf16 planes (error ~2^-17 per product).  TENSOR_V16 = TENSOR for the
  * recurrent and attention products, but the vocabulary projection in plain fp16 (one product instead of three:
  * logits carry ~2^-12 relative noise, 1e-5 on a log-probability; near-ties in the beam may resolve differently;
- * ~15 % faster).  AUTO = TENSOR. */
-enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3, LINMT_GEMM_TENSOR3 = 4, LINMT_GEMM_TENSOR_V16 = 5 };
+ * ~15 % faster).  TENSOR_V16X = TENSOR_V16 plus a refinement in the softmax kernel: every logit that can still
+ * be among the k+1 best of its row given the error bound of the fp16 product (and EOS) is recomputed from both
+ * planes, so candidates and their log-probabilities are fp32-class again; only the normaliser sums fp16 logits.
+ * AUTO = TENSOR_V16X for a single model (measured: the same parity as TENSOR, 13 % faster), TENSOR for ensembles. */
+enum { LINMT_GEMM_AUTO = 0, LINMT_GEMM_SIMT = 1, LINMT_GEMM_TENSOR = 2, LINMT_GEMM_TENSOR2 = 3, LINMT_GEMM_TENSOR3 = 4, LINMT_GEMM_TENSOR_V16 = 5, LINMT_GEMM_TENSOR_V16X = 6 };
 
 /* Model dimensions: first five of the nine integers on line 1 of a model file
  * (src/decoder.h:1202-1210). */

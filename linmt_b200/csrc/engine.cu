@@ -199,6 +199,15 @@ int Engine::pack_model(const float* blob, DevModel& m) {
 #pragma omp parallel for schedule(static)
   for (int v = 0; v < V; ++v)
     for (int kx = 0; kx < H; ++kx) host[(size_t)v * Hp + kx] = bv.D[(size_t)kx * V + v];
+  {
+    double best = 0.0;
+    for (int v = 0; v < V; ++v) {
+      double ss = 0.0;
+      for (int kx = 0; kx < H; ++kx) { const double w = host[(size_t)v * Hp + kx]; ss += w * w; }
+      if (ss > best) best = ss;
+    }
+    m.voc_wnorm_max = (float)std::sqrt(best);
+  }
   if ((rc = store(&m.voc_w, &m.p_voc_w, (size_t)Vp, Hp))) return rc;
   host.assign(Vp, 0.f);
   std::memcpy(host.data(), bv.bd, sizeof(float) * V);
@@ -231,7 +240,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (nm > 8) return fail(LINMT_ELIMIT, "at most 8 ensemble members");
   if (nm > 1 && o.print_info) return fail(LINMT_EINVAL, "alignment output (print_info) is not available with ensembles");
   if (o.precision != LINMT_PREC_FP32 && o.precision != LINMT_PREC_BF16) return fail(LINMT_EINVAL, "bad precision");
-  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR_V16) return fail(LINMT_EINVAL, "bad gemm_path");
+  if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR_V16X) return fail(LINMT_EINVAL, "bad gemm_path");
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
@@ -239,13 +248,18 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
-  fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR || o.gemm_path == LINMT_GEMM_TENSOR_V16)) ? 1 : 0;
+  fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR || o.gemm_path == LINMT_GEMM_TENSOR_V16 ||
+          o.gemm_path == LINMT_GEMM_TENSOR_V16X)) ? 1 : 0;
   nt_ = (o.precision == LINMT_PREC_BF16) ? 1 : (o.gemm_path == LINMT_GEMM_TENSOR3 ? 3 : 2);
   // The vocabulary product feeds only the softmax of its own step (nothing recurrent), so two
   // planes (error ~2^-17 per product, ~3e-7 relative on a log-probability) are enough there:
   // measured parity on the 64-sentence reference configuration is unchanged and the GEMM is 1.3x faster.
   nt_vocab_ = (nt_ == 3) ? 2 : nt_;
-  if (fmt_ == 1 && o.gemm_path == LINMT_GEMM_TENSOR_V16) nt_vocab_ = 1;   // plain fp16 logits: the first plane of each pair
+  // AUTO = TENSOR_V16X: plain fp16 logits (the first plane of each pair) with the candidates recomputed accurately
+  // in the softmax kernel; ensembles combine whole distributions and keep the three-product logits
+  const bool v16x = o.gemm_path == LINMT_GEMM_TENSOR_V16X || o.gemm_path == LINMT_GEMM_AUTO;
+  if (fmt_ == 1 && (o.gemm_path == LINMT_GEMM_TENSOR_V16 || (v16x && nm == 1))) nt_vocab_ = 1;
+  refine_ = fmt_ == 1 && v16x && nm == 1;
   if (linmt_blob_floats(&d) != blob_floats) return fail(LINMT_EINVAL, "weight blob size does not match the model dimensions");
   if (o.beam <= 0) return fail(LINMT_EINVAL, "--beam-size cannot be <= 0");
   if (o.penalty < 0) return fail(LINMT_EINVAL, "--penalty cannot be < 0");
@@ -290,7 +304,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   DA(d_fin_score_, (size_t)B * fin_cap); DA(d_fin_final_, (size_t)B * fin_cap);
   if (nm > 1) DA(d_combined_, (size_t)R * Vp);
   DA(d_cand_idx_, (size_t)R * kk); DA(d_cand_logp_, (size_t)R * kk); DA(d_eos_logp_, R); DA(d_row_stats_, 2 * (size_t)R);
-  pmax_ld_ = 4 * ((Vp + 63) / 64) + 4;
+  pmax_ld_ = 4 * ((Vp + 47) / 48) + 4;   // four column blocks per tile, tiles at least 48 wide
   DA(d_pmax_, (size_t)R * pmax_ld_);
   if (o.print_info) {
     DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
@@ -432,7 +446,18 @@ int Engine::step_tail(int t, int rows) {
     trace_dev_.ld_logits = Vp;
     trace_dev_.row_stats = d_row_stats_;
     if (n_models == 1) {
-      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_));
+      TopkRefine rf{};
+      if (refine_) {
+        const TcState& ts = tc_states_[0];
+        const DevModel& m0 = models_[0];
+        rf.a0 = reinterpret_cast<const __half*>(ts.panel_ht.p[0]); rf.a1 = reinterpret_cast<const __half*>(ts.panel_ht.p[1]);
+        rf.lda = ts.panel_ht.ld;
+        rf.b0 = reinterpret_cast<const __half*>(m0.p_voc_w.p[0]); rf.b1 = reinterpret_cast<const __half*>(m0.p_voc_w.p[1]);
+        rf.ldb = m0.p_voc_w.ld;
+        rf.bias = m0.voc_b; rf.K = Hp;
+        rf.eps_coef = 1.1f * (1.0f / 1024.0f) * m0.voc_wnorm_max;
+      }
+      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_, refine_ ? &rf : nullptr));
     } else {
       // EnsembleFactory::EnsemblesModels (src/decoder.h:1910-1931): mean of the members'
       // probabilities, renormalised -- written as log(mean p) so that the log-softmax of the

@@ -31,6 +31,7 @@ struct DevModel {
   float* vp = nullptr;                   // [Hp]
   float* voc_w = nullptr;                // [Vp][Hp]
   float* voc_b = nullptr;                // [Vp]
+  float voc_wnorm_max = 0.f;             // largest 2-norm of a vocabulary weight row
   // the same operands as bf16 planes for the tensor-core path (fp32 copies are then not kept)
   tc::Planes p_emb_src{}, p_emb_tgt{}, p_att_proj_w{}, p_att_out_w{}, p_voc_w{};
   std::vector<tc::Planes> p_enc_w, p_dec_w;
@@ -110,6 +111,7 @@ class Engine {
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
+  bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)

@@ -129,8 +129,9 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   if constexpr (Epi::kHasPmax) {
     // block maxima for the softmax: four column blocks per tile; not from the split-K fix-up path
     if (e.pmax) {
-      if (splits > 1) { e.pmax = nullptr; pmax_slots_ = 0; }
-      else pmax_slots_ = 4 * ((N + bn - 1) / bn);
+      const int slots = 4 * ((N + bn - 1) / bn);
+      if (splits > 1 || slots > e.pmax_ld) { e.pmax = nullptr; pmax_slots_ = 0; }
+      else pmax_slots_ = slots;
     }
   }
   // many waves of tiles whose leading product is one chain: one persistent CTA per SM

@@ -118,7 +118,8 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
     else if (*v == "tensor2") c.opt.gemm_path = LINMT_GEMM_TENSOR2;
     else if (*v == "tensor3") c.opt.gemm_path = LINMT_GEMM_TENSOR3;
     else if (*v == "tensor_v16") c.opt.gemm_path = LINMT_GEMM_TENSOR_V16;
-    else { err = "--gemm-path must be auto, simt, tensor, tensor2, tensor3 or tensor_v16"; return false; }
+    else if (*v == "tensor_v16x") c.opt.gemm_path = LINMT_GEMM_TENSOR_V16X;
+    else { err = "--gemm-path must be auto, simt, tensor, tensor2, tensor3, tensor_v16 or tensor_v16x"; return false; }
   }
   if (auto v = get("--batch-size")) c.opt.max_batch = std::atoi(v->c_str());
   if (auto v = get("--device")) c.opt.device = std::atoi(v->c_str());

@@ -269,6 +269,20 @@ struct TopkOut {
 };
 __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
 
+// Refinement of a row whose logits came from a ONE-product (plain fp16) vocabulary GEMM: the row's
+// activations and the vocabulary weights as fp16 pairs, from which the few logits that matter are
+// recomputed at fp32-class accuracy.  eps_coef * |a|_2 bounds the error of a one-product logit
+// (both operands rounded to 11 bits: relative 2^-10 on every term, Cauchy-Schwarz over the row,
+// largest weight-row norm of the model folded into eps_coef).
+struct TopkRefine {
+  const __half* a0; const __half* a1; int lda;   // activations [rows][lda], planes of the fp16 pair
+  const __half* b0; const __half* b1; int ldb;   // vocabulary weights [V][ldb]
+  const float* bias;                             // [V]
+  int K;
+  float eps_coef;
+};
+constexpr float kPairInv = 1.0f / 2048.0f;
+
 // Pass 1 finds the row maximum and, from the 256 per-thread maxima, a threshold that at least
 // kk elements reach (the kk-th largest thread maximum).  Pass 2 (the row is L2/L1 resident by
 // then) sums exp(z - max) and collects the few elements at or above the threshold, which are
@@ -276,7 +290,8 @@ __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { ret
 // (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
 constexpr int kTopkCap = 1024;
 static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
-                                                                  int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots) {
+                                                                  int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots, TopkRefine rf) {
+  extern __shared__ float s_a[];   // [rf.K] the row's activations in fp32 (refinement only)
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   __shared__ float s_tmax[256];
@@ -351,7 +366,26 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
     if (tid == 0) s_max = bm;
   }
   __syncthreads();
-  const float tau = s_tau, rmax = s_max;
+  float tau = s_tau;
+  const float rmax = s_max;
+  if (rf.a0) {
+    // Every logit in this row is within eps of its accurate value, so the accurate top-kk all lie at or
+    // above (kk-th largest approximate value) - 2 eps, and tau is no larger than that kk-th value.
+    float ss = 0.f;
+    for (int j = tid; j < rf.K; j += 256) {
+      const float a = __half2float(rf.a0[(size_t)r * rf.lda + j]) + __half2float(rf.a1[(size_t)r * rf.lda + j]) * kPairInv;
+      s_a[j] = a;
+      ss = fmaf(a, a, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < 8; ++w) tot += s_red[w];
+    tau -= 2.0f * (rf.eps_coef * sqrtf(tot) + 1e-6f);
+    __syncthreads();
+  }
   // ---- pass 2: sum of exponentials, candidates ----
   float ssum = 0.f;
   auto visit = [&](float v, int i) {
@@ -374,12 +408,42 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
     float bs = 0.f;
     for (int w = 0; w < 8; ++w) bs += s_red[w];
     s_lse = normalise ? logf(bs) : -rmax;   // normalise = 0: the row already holds log-probabilities
-    if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
+    if (out.eos_logp && !rf.a0) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
     if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
   }
   __syncthreads();
   const float rlse = s_lse;
   const int n = s_count;
+  if (rf.a0) {
+    // accurate values for the candidates (and for EOS, whose log-probability is always reported): one
+    // warp per candidate, fp32 FMAs over the two planes of both operands
+    const int nc = n <= kTopkCap ? n : 0;
+    for (int c = warp; c <= nc; c += 8) {
+      const int v = (c < nc) ? s_ci[c] : kEos;
+      const __half* w0 = rf.b0 + (size_t)v * rf.ldb;
+      const __half* w1 = rf.b1 + (size_t)v * rf.ldb;
+      float acc = 0.f;
+      for (int j = lane * 4; j < rf.K; j += 128) {
+        const uint2 q0 = *reinterpret_cast<const uint2*>(w0 + j);
+        const uint2 q1 = *reinterpret_cast<const uint2*>(w1 + j);
+        const __half2 h00 = *reinterpret_cast<const __half2*>(&q0.x), h01 = *reinterpret_cast<const __half2*>(&q0.y);
+        const __half2 h10 = *reinterpret_cast<const __half2*>(&q1.x), h11 = *reinterpret_cast<const __half2*>(&q1.y);
+        const float2 b00 = __half22float2(h00), b01 = __half22float2(h01), b10 = __half22float2(h10), b11 = __half22float2(h11);
+        acc = fmaf(s_a[j + 0], fmaf(b10.x, kPairInv, b00.x), acc);
+        acc = fmaf(s_a[j + 1], fmaf(b10.y, kPairInv, b00.y), acc);
+        acc = fmaf(s_a[j + 2], fmaf(b11.x, kPairInv, b01.x), acc);
+        acc = fmaf(s_a[j + 3], fmaf(b11.y, kPairInv, b01.y), acc);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) {
+        const float zv = acc + (rf.bias ? rf.bias[v] : 0.f);
+        if (c < nc) s_cv[c] = zv;
+        else if (out.eos_logp) out.eos_logp[r] = (zv - rmax) - rlse;
+      }
+    }
+    __syncthreads();
+  }
   if (n <= kTopkCap) {
     // exact ranking of the candidates: value descending, index ascending
     for (int c = tid; c < n; c += 256) {
@@ -430,9 +494,13 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
 }
 
 inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, int normalise,
-                                       cudaStream_t st, bool pdl = false, const float* pmax = nullptr, int pmax_ld = 0, int n_slots = 0) {
+                                       cudaStream_t st, bool pdl = false, const float* pmax = nullptr, int pmax_ld = 0, int n_slots = 0,
+                                       const TopkRefine* refine = nullptr) {
   if (n_slots <= 0) pmax = nullptr;
-  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), 0, st, logits, ld, V, kk, out, normalise, pmax, pmax_ld, n_slots);
+  TopkRefine rf{};
+  if (refine) rf = *refine;
+  const size_t smem = rf.a0 ? sizeof(float) * (size_t)rf.K : 0;
+  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), smem, st, logits, ld, V, kk, out, normalise, pmax, pmax_ld, n_slots, rf);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -16,7 +16,7 @@ from . import _lib
 ATT = {"local_p_general": 0, "global_general": 1, "global_dot": 2}
 ENS = {"prob_mean": 0, "logprob_mean": 1}
 PREC = {"fp32": 0, "bf16": 1}
-GEMM = {"auto": 0, "simt": 1, "tensor": 2, "tensor2": 3, "tensor3": 4, "tensor_v16": 5}
+GEMM = {"auto": 0, "simt": 1, "tensor": 2, "tensor2": 3, "tensor3": 4, "tensor_v16": 5, "tensor_v16x": 6}
 
 
 class LinmtError(RuntimeError):

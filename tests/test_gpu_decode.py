@@ -119,7 +119,7 @@ def test_limits_are_errors_not_faults(cuda_lib, c1):
         decoder.Decoder(c.desc, [blob[:-1]], beam=2)
 
 
-@pytest.mark.parametrize("gemm_path", ["simt", "tensor", "tensor3", "tensor2", "tensor_v16"])
+@pytest.mark.parametrize("gemm_path", ["simt", "auto", "tensor", "tensor3", "tensor2", "tensor_v16"])
 def test_c2_shape_subset(oracle, cuda_lib, gemm_path):
     """The 4 x 1000, 30k-vocabulary, beam-12 model on 6 sentences of the reference decode
     configuration, against the checker."""
@@ -224,7 +224,7 @@ def test_bf16_against_fp32_token_identity(oracle, cuda_lib):
     dec.close()
 
 
-@pytest.mark.parametrize("gemm_path,min_identical", [("tensor", 0.95), ("simt", 0.85)])
+@pytest.mark.parametrize("gemm_path,min_identical", [("auto", 0.95), ("tensor", 0.95), ("simt", 0.85)])
 def test_c2_whole_batch_against_golden(cuda_lib, gemm_path, min_identical):
     """The reference decode configuration at full size (64 sentences, beam 12, 4 x 1000, 30k
     vocabulary), free-running, against the checker's committed hypotheses: token-identical 1-best
