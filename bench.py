@@ -336,8 +336,8 @@ def run_ours(args):
                             "this many bf16 partial products (operands split into bf16 planes), which is what "
                             "tensor_pipe_* counts; the bf16 path runs 1"}
 
-        r_voc = roof("vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path)", flops_local, gemm_ms, gemm_n,
-                     (4 if args.gemm_path in ("tensor2", "tensor3") else (1 if args.gemm_path in ("tensor_v16", "tensor_v16x", "auto") and len(blobs) == 1 else 3)) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
+        r_voc = roof("vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path; the default computes it as one fp16 product and recomputes the top candidates in the softmax kernel)", flops_local, gemm_ms, gemm_n,
+                     (4 if args.gemm_path in ("tensor2", "tensor3") else (1 if args.gemm_path in ("tensor_v16", "tensor_v16x", "auto") and len(blobs) == 1 else 3)) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path == "tensor" else None)
         r_rec = roof("decoder LSTM gate GEMMs [rows,2H|3H]x[.,4H], fused cell update (" + args.gemm_path + " path)",
                      rec["flops"], rec["ms"], rec["n"],
                      {"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1,
