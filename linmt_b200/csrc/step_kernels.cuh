@@ -383,7 +383,7 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
     __syncthreads();
     float tot = 0.f;
     for (int w = 0; w < 8; ++w) tot += s_red[w];
-    tau -= 2.0f * (rf.eps_coef * sqrtf(tot) + 1e-6f);
+    tau -= 2.0f * (rf.eps_coef * sqrtf(tot) + 1e-5f);   // + fp16 subnormals and the accumulator's own rounding
     __syncthreads();
   }
   // ---- pass 2: sum of exponentials, candidates ----
