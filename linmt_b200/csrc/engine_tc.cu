@@ -136,7 +136,13 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   }
   // many waves of tiles whose leading product is one chain: one persistent CTA per SM
   const long tiles = (long)((M + tc::BM - 1) / tc::BM) * ((N + bn - 1) / bn);
-  if (persist_ && nt == 2 && splits == 1 && drain >= K / 32 && tiles > n_sm_) {
+  const bool one_plane_logits = nt == 1 && Epi::kHasPmax;   // the fp32-output GEMMs: vocabulary projection
+  if (persist_ && splits == 1 && tiles > n_sm_ && ((nt == 2 && drain >= K / 32) || one_plane_logits)) {
+    if (nt == 1) {
+      const int pdl = sh.pdl;
+      sh = tc::make_shape_persist(bn, nt, bk, fmt_);   // a ring of one stage less, staging areas of its own
+      sh.pdl = pdl;
+    }
     CK(tc::launch_gemm_tc_persist(tm, M, N, K, sh, e, d_tc_err_, stream, n_sm_));
     LAUNCHED();
     return LINMT_OK;

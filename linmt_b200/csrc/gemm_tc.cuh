@@ -525,7 +525,11 @@ struct TcEpiF32 {
     }
     pmax_store(row, M, slot, m);
   }
-  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf, int slot) const {
+  // Stages nch (<= 4) chunks of this warp's 32 rows with `stride` floats per row (>= 16 * nch + 4) and
+  // stores them with consecutive lanes on consecutive addresses; returns this lane's (= row's) maximum
+  // over the valid columns.
+  __device__ __forceinline__ float stage_store(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf,
+                                               int stride) const {
     float m = -INFINITY;
 #pragma unroll
     for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
@@ -539,7 +543,7 @@ struct TcEpiF32 {
             r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
           }
           if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
-          *reinterpret_cast<float4*>(sbuf + lane * kEpiScratchStride + 16 * ci + 4 * q) = r;
+          *reinterpret_cast<float4*>(sbuf + lane * stride + 16 * ci + 4 * q) = r;
           const int c = col0 + 4 * q;
           if (c + 0 < n_valid) m = fmaxf(m, r.x);
           if (c + 1 < n_valid) m = fmaxf(m, r.y);
@@ -548,16 +552,20 @@ struct TcEpiF32 {
         }
       }
     }
-    pmax_store(row0 + lane, M, slot, m);
     __syncwarp();
     const int nq = 4 * nch;   // float4 per row
     for (int s = lane; s < 32 * nq; s += 32) {
       const int r = s / nq, g = s - r * nq;
       if (row0 + r < M)
         *reinterpret_cast<float4*>(out + (size_t)(row0 + r) * ld + col_first + 4 * g) =
-            *reinterpret_cast<const float4*>(sbuf + r * kEpiScratchStride + 4 * g);
+            *reinterpret_cast<const float4*>(sbuf + r * stride + 4 * g);
     }
     __syncwarp();
+    return m;
+  }
+  __device__ __forceinline__ void block(int row0, int lane, int M, int col_first, int nch, float (*v)[16], float* sbuf, int slot) const {
+    const float m = stage_store(row0, lane, M, col_first, nch, v, sbuf, kEpiScratchStride);
+    pmax_store(row0 + lane, M, slot, m);
   }
 };
 
@@ -910,16 +918,17 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
 // across tile boundaries; the epilogue warps copy a finished accumulator pair to registers, hand
 // TMEM back at once, and write their tile to memory while the tensor core is already on the next
 // one -- the ~7 us of prologue and epilogue that every tile of a multi-wave launch used to pay is
-// paid once per CTA.  (Direct row-per-lane stores here: the staging area of the one-tile kernel
-// is the stage ring, which is busy; the last tile of a CTA, with the ring idle, uses it.)
-// Split operands only (NP > 1), no split-K, no intermediate drains.
+// paid once per CTA.  Stores: the staging area of the one-tile kernel is the stage ring, which is busy
+// here, so either the launch sets aside a small staging area of its own (stage_stride > 0: 32 rows x
+// stage_stride floats per epilogue warp, two 16-column chunks at a time -- the one-plane launches, whose
+// ring leaves the room), or tiles go out with row-per-lane stores and only a CTA's last tile, with the
+// ring idle, is staged there.  No split-K, no intermediate drains.
 template <int NT, int BKT, int FMT, class Epi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, Epi epi,
-                       int* __restrict__ err_flag) {
+                       int* __restrict__ err_flag, int stage_stride) {
   constexpr int PC = product_code(NT, FMT);
   constexpr int NP = num_products(PC);
-  static_assert(NP > 1, "split operands only");
   constexpr int A_BYTES = BM * BKT * 2;
   constexpr int BK = BKT;
   extern __shared__ unsigned char smem_raw[];
@@ -928,9 +937,11 @@ gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, 
   unsigned char* base_ptr = smem_raw + (base - raw);
   const int B_BYTES = BN * BK * 2;
   const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
-  const int RING = ring_bytes(STAGES, STAGE_BYTES);
-  const uint32_t bars = base + RING;   // full[STAGES], empty[STAGES], accum_full, tmem_free
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + RING + 8 * (2 * STAGES + 3));
+  const int STG_WARP = 32 * stage_stride * 4;                    // bytes of a warp's own staging area (0: none)
+  const int RING = (stage_stride > 0 ? STAGES * STAGE_BYTES : ring_bytes(STAGES, STAGE_BYTES));
+  const int PRE = RING + kEpiWarps * STG_WARP;                   // ring, then the staging areas, then the barriers
+  const uint32_t bars = base + PRE;   // full[STAGES], empty[STAGES], accum_full, tmem_free
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + PRE + 8 * (2 * STAGES + 3));
   __shared__ int s_abort;
 
   pdl_launch_dependents();
@@ -999,13 +1010,15 @@ gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, 
           tc_fence_after();
           const uint64_t a0 = make_desc<BKT>(st);
           const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);
+          if (NP > 1) {
 #pragma unroll
-          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
 #pragma unroll
-            for (int p = 0; p < NP - 1; ++p) {
-              const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
-              const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
-              umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
+              for (int p = 0; p < NP - 1; ++p) {
+                const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
+                const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
+                umma_bf16(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
+              }
             }
           }
 #pragma unroll
@@ -1045,11 +1058,13 @@ gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, 
 #pragma unroll
       for (int ci = 0; ci < kChunks; ++ci) {
         if (ci < nmine) {
-          float sm[16];
           tmem_ld16(lane_base + (uint32_t)(ci * 16), macc[ci]);
-          tmem_ld16(lane_base + astride + (uint32_t)(ci * 16), sm);
+          if (NP > 1) {
+            float sm[16];
+            tmem_ld16(lane_base + astride + (uint32_t)(ci * 16), sm);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
+            for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
+          }
         }
       }
       tc_fence_before();
@@ -1057,6 +1072,22 @@ gemm_tc_persist_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, 
       if (lane == 0) mbar_arrive(tmem_free);   // the tensor core may start the next tile
       const bool last = tile + (int)gridDim.x >= ntile;
       const int slot = (tile / mt) * kParts + part;
+      if constexpr (Epi::kHasPmax) {
+        if (stage_stride > 0) {
+          // this warp's own staging area: as many chunks at a time as a staged row holds
+          float* own = reinterpret_cast<float*>(base_ptr + RING + (warp - 2) * STG_WARP);
+          float m = -INFINITY;
+#pragma unroll
+          for (int c0 = 0; c0 < kChunks; c0 += 2) {   // two chunks at a time (stage_stride >= 36); static indices keep macc in registers
+            if (c0 < nmine) {
+              const int nc = nmine - c0 < 2 ? nmine - c0 : 2;
+              m = fmaxf(m, epi.stage_store(row0, lane, M, n0 + (ch0 + c0) * 16, nc, macc + c0, own, stage_stride));
+            }
+          }
+          epi.pmax_store(row0 + lane, M, slot, m);
+          continue;
+        }
+      }
       if (last && Epi::kHasBlock) {
         // the ring is idle from here on: stage and store coalesced
         if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf, slot);
@@ -1152,29 +1183,48 @@ inline cudaError_t launch_gemm_tc(const TmapSet& tm, int M, int N, int K, const 
   return launch_gemm_tc_nt<1, 32, 0, Epi>(tm, M, N, K, sh, epi, err_flag, st, ws, counters);
 }
 
-// Persistent launch (see gemm_tc_persist_kernel): fp16 pair or two bf16 planes, no split-K.
+// Persistent launch (see gemm_tc_persist_kernel): one or two planes per operand, no split-K.  One-plane
+// launches get a staging area of their own beside a ring of one stage less.
+constexpr int kPersistStageStride = 36;   // floats per staged row: two 16-column chunks + 4
+inline Shape make_shape_persist(int bn, int nt, int bk, int fmt) {
+  Shape s = make_shape(bn, nt, bk, fmt);
+  if (nt == 1) {
+    const int stg = kEpiWarps * 32 * kPersistStageStride * 4;
+    s.stages = (SMEM_BUDGET - stg) / s.stage_bytes;
+    if (s.stages > kMaxStages) s.stages = kMaxStages;
+    s.smem_bytes = s.stages * s.stage_bytes + stg + 1024 + 256;
+  }
+  return s;
+}
 template <class Epi>
 inline cudaError_t launch_gemm_tc_persist(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                           cudaStream_t st, int n_sm) {
-  if (sh.nt != 2 || K % sh.bk) return cudaErrorInvalidValue;
+  if ((sh.nt != 2 && sh.nt != 1) || K % sh.bk || sh.stages < 2) return cudaErrorInvalidValue;
   const int tiles = ((M + BM - 1) / BM) * ((N + sh.bn - 1) / sh.bn);
   const dim3 grid(tiles < n_sm ? tiles : n_sm);
-#define LINMT_PERSIST_CASE(BKV, FMTV)                                                                                        \
+  const int stride = sh.nt == 1 ? kPersistStageStride : 0;
+#define LINMT_PERSIST_CASE(NTV, BKV, FMTV)                                                                                   \
   {                                                                                                                          \
     static bool done = false;                                                                                                \
     if (!done) {                                                                                                             \
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<2, BKV, FMTV, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<NTV, BKV, FMTV, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            SMEM_BUDGET + 1280);                                                              \
       if (e != cudaSuccess) return e;                                                                                        \
       done = true;                                                                                                           \
     }                                                                                                                        \
-    return launch_k(sh.pdl != 0, gemm_tc_persist_kernel<2, BKV, FMTV, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, \
-                    sh.bn, sh.stages, epi, err_flag);                                                                        \
+    return launch_k(sh.pdl != 0, gemm_tc_persist_kernel<NTV, BKV, FMTV, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, \
+                    sh.bn, sh.stages, epi, err_flag, stride);                                                                \
   }
-  if (sh.fmt == 1 && sh.bk == 64) LINMT_PERSIST_CASE(64, 1)
-  if (sh.fmt == 1) LINMT_PERSIST_CASE(32, 1)
-  if (sh.bk == 64) LINMT_PERSIST_CASE(64, 0)
-  LINMT_PERSIST_CASE(32, 0)
+  if (sh.nt == 1) {
+    if (sh.fmt == 1 && sh.bk == 64) LINMT_PERSIST_CASE(1, 64, 1)
+    if (sh.fmt == 1) LINMT_PERSIST_CASE(1, 32, 1)
+    if (sh.bk == 64) LINMT_PERSIST_CASE(1, 64, 0)
+    LINMT_PERSIST_CASE(1, 32, 0)
+  }
+  if (sh.fmt == 1 && sh.bk == 64) LINMT_PERSIST_CASE(2, 64, 1)
+  if (sh.fmt == 1) LINMT_PERSIST_CASE(2, 32, 1)
+  if (sh.bk == 64) LINMT_PERSIST_CASE(2, 64, 0)
+  LINMT_PERSIST_CASE(2, 32, 0)
 #undef LINMT_PERSIST_CASE
 }
 
