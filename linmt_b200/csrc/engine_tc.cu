@@ -249,7 +249,9 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
         else { src = hcur_planes(l).p[p] + hcur_col0(l); sst = (long long)hcur_planes(l).ld * 2; }
         add(src, sst, hprev_planes(l).p[p] + Hp, (long long)hprev_planes(l).ld * 2, Hp * 2, 0);
       }
-      add(t == 0 ? s.enc_c[fb][l] : s.c_cur[l], (long long)Hp * 4, s.c_prev[l], (long long)Hp * 4, Hp * 4, 0);
+      // the cell state is copied only at the first step (from the encoder); afterwards the LSTM epilogue
+      // reads it through the parent index and the two buffers swap roles every step
+      if (t == 0) add(s.enc_c[fb][l], (long long)Hp * 4, s.c_prev[l], (long long)Hp * 4, Hp * 4, 0);
     }
     if (feed)
       for (int p = 0; p < nt_; ++p)
@@ -265,7 +267,13 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   for (int l = 0; l < L; ++l) {
     tc::TcEpiLstm e{};
-    e.bias = m.dec_b[l]; e.c_prev = s.c_prev[l]; e.ldc = Hp; e.c_out = s.c_cur[l];
+    e.bias = m.dec_b[l]; e.ldc = Hp;
+    if (t == 0) { e.c_prev = s.c_prev[l]; e.c_out = s.c_cur[l]; }
+    else {
+      e.c_prev = (t & 1) ? s.c_cur[l] : s.c_prev[l];
+      e.c_out = (t & 1) ? s.c_prev[l] : s.c_cur[l];
+      e.c_parent = d_parent_; e.c_k = k;
+    }
     e.h_out1 = hcur_planes(l); e.h1_col0 = hcur_col0(l);
     e.h_out2 = no_planes(); e.h2_col0 = 0;
     e.h_prev = no_planes(); e.hp_col0 = 0;

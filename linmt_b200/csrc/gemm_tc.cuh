@@ -318,11 +318,15 @@ struct TcEpiLstm {
   float* h_f32; long long hf_row_stride;  // optional fp32 copy, element (row, j) at h_f32[row*stride + j]
   const int* row_len; int pos;
   int nt;
+  // Optional beam reordering of the cell state: row r continues slot c_parent[r] of its sentence (k slots per
+  // sentence), so c_prev is read from that row -- the state then needs no copy between steps.
+  const int32_t* c_parent = nullptr; int c_k = 1;
+  __device__ __forceinline__ int c_src_row(int row) const { return c_parent ? (row / c_k) * c_k + c_parent[row] : row; }
   __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
     const bool active = (row_len == nullptr) || (pos < row_len[row]);
     const int j0 = col0 >> 2;
     const size_t ic = (size_t)row * ldc + j0;
-    const float4 cp = *reinterpret_cast<const float4*>(c_prev + ic);
+    const float4 cp = *reinterpret_cast<const float4*>(c_prev + (size_t)c_src_row(row) * ldc + j0);
     const size_t i1 = (size_t)row * h_out1.ld + h1_col0 + j0;
     const size_t i2 = (size_t)row * h_out2.ld + h2_col0 + j0;
     if (active) {
@@ -377,7 +381,7 @@ struct TcEpiLstm {
       const int r = s / nq, g = s - r * nq;
       if (row0 + r < M)
         *reinterpret_cast<float4*>(cs + r * 20 + 4 * g) =
-            *reinterpret_cast<const float4*>(c_prev + (size_t)(row0 + r) * ldc + j_first + 4 * g);
+            *reinterpret_cast<const float4*>(c_prev + (size_t)c_src_row(row0 + r) * ldc + j_first + 4 * g);
     }
     __syncwarp();
     if (active) {
