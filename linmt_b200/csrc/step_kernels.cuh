@@ -395,9 +395,31 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
       if (pos < kTopkCap) { s_cv[pos] = v; s_ci[pos] = i; }
     }
   };
-  for (int i = tid * 4; i < V4; i += 256 * 4) {
-    const float4 q = *reinterpret_cast<const float4*>(z + i);
-    visit(q.x, i); visit(q.y, i + 1); visit(q.z, i + 2); visit(q.w, i + 3);
+  {
+    // four independent 16-byte loads in flight per thread; candidates are rare, so a group of four is
+    // first tested as a whole against the threshold
+    auto group = [&](const float4& q, int i) {
+      ssum += __expf(q.x - rmax) + __expf(q.y - rmax);
+      ssum += __expf(q.z - rmax) + __expf(q.w - rmax);
+      if (fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)) >= tau) {
+        const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v[u] >= tau) {
+            const int pos = atomicAdd(&s_count, 1);
+            if (pos < kTopkCap) { s_cv[pos] = v[u]; s_ci[pos] = i + u; }
+          }
+      }
+    };
+    int i = tid * 4;
+    for (; i + 3 * 1024 < V4; i += 4 * 1024) {
+      const float4 q0 = *reinterpret_cast<const float4*>(z + i);
+      const float4 q1 = *reinterpret_cast<const float4*>(z + i + 1024);
+      const float4 q2 = *reinterpret_cast<const float4*>(z + i + 2048);
+      const float4 q3 = *reinterpret_cast<const float4*>(z + i + 3072);
+      group(q0, i); group(q1, i + 1024); group(q2, i + 2048); group(q3, i + 3072);
+    }
+    for (; i < V4; i += 1024) group(*reinterpret_cast<const float4*>(z + i), i);
   }
   for (int i = V4 + tid; i < V; i += 256) visit(z[i], i);
 #pragma unroll
