@@ -244,6 +244,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
     return fail(LINMT_EINVAL, "bf16 precision runs on the tensor-core path only");
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
+  { const char* pe = std::getenv("LINMT_XW"); xw_table_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_XW=0: test knob
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
@@ -309,7 +310,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   if (o.print_info) {
     DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
   }
-  // kernels that may need more than the default dynamic shared memory
+  if (use_tc_ && xw_table_) { const int rc_xw = build_xw_tables(); if (rc_xw) return rc_xw; }
   CK(cudaDeviceSynchronize());  // every weight upload has landed before the first decode
   return LINMT_OK;
 }

@@ -31,6 +31,7 @@ struct DevModel {
   float* vp = nullptr;                   // [Hp]
   float* voc_w = nullptr;                // [Vp][Hp]
   float* voc_b = nullptr;                // [Vp]
+  float* dec_xw = nullptr;               // [V][4Hp] W_x . embedding(v) of the first decoder layer (tensor path, optional)
   float voc_wnorm_max = 0.f;             // largest 2-norm of a vocabulary weight row
   // the same operands as bf16 planes for the tensor-core path (fp32 copies are then not kept)
   tc::Planes p_emb_src{}, p_emb_tgt{}, p_att_proj_w{}, p_att_out_w{}, p_voc_w{};
@@ -97,6 +98,7 @@ class Engine {
   int run_decoder_step_tc(int mi, int t, int rows);
   int step_tail(int t, int rows);
   int alloc_state_tc(TcState& s);
+  int build_xw_tables();   // dec_xw of every model (tensor path, xw_table_)
   int alloc_planes(tc::Planes& p, size_t rows, int ld);
   int to_planes(const std::vector<float>& host, size_t rows, int ld, tc::Planes& dst);
   const CUtensorMap* a_maps(const tc::Planes& p, int col0, int rows_cap, int K, int bk);
@@ -111,6 +113,7 @@ class Engine {
   cudaEvent_t enc_start_ev_ = nullptr;
   int nt_ = 3;
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
+  bool xw_table_ = false;  // first decoder layer: embedding term from a per-vocabulary table instead of the GEMM
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)

@@ -155,6 +155,28 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
 
 static tc::Planes no_planes() { return tc::Planes{}; }
 
+// Input-term table of the first decoder layer: dec_xw[v][:] = W_x . embedding(v) for every target word, computed
+// once with the same tensor GEMM (W_x = the first Hp of the K columns of the layer's weight planes).
+int Engine::build_xw_tables() {
+  for (int mi = 0; mi < n_models; ++mi) {
+    DevModel& m = models_[mi];
+    void* q = nullptr;
+    const size_t bytes = (size_t)desc.vocab_tgt * 4 * Hp * sizeof(float);
+    if (cudaMalloc(&q, bytes) != cudaSuccess) return fail(LINMT_ENOMEM, "cudaMalloc failed (input-term table)");
+    allocs_.push_back(q);
+    m.dec_xw = static_cast<float*>(q);
+    tc::TcEpiF32 e{nullptr, m.dec_xw, 4 * Hp, 0};
+    pdl_gemm_ = false;
+    int rc = tc_gemm(m.p_emb_tgt, 0, desc.vocab_tgt, m.p_dec_w[0], desc.vocab_tgt, 4 * Hp, Hp, e);
+    if (rc) return rc;
+  }
+  CK(cudaStreamSynchronize(stream));
+  int herr = 0;
+  CK(cudaMemcpy(&herr, d_tc_err_, sizeof(int), cudaMemcpyDeviceToHost));
+  if (herr) return fail(LINMT_ECUDA, "a tensor-core GEMM gave up waiting on a barrier while building the input-term table");
+  return LINMT_OK;
+}
+
 // Encoder, tensor-core path (see Engine::run_encoder for the reference procedure).  Panel of
 // layer l at position p: encp[p&1][l] = (input from below | h_prev).  The epilogue writes h to
 // the next position's h_prev slot and to the next layer's input slot of this position.
@@ -256,8 +278,9 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     if (feed)
       for (int p = 0; p < nt_; ++p)
         add(ts.panel_ht.p[p], (long long)ts.panel_ht.ld * 2, ts.panel1.p[p] + 2 * Hp, (long long)ts.panel1.ld * 2, Hp * 2, 0);
-    for (int p = 0; p < nt_; ++p)
-      add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
+    if (!m.dec_xw)   // with the input-term table the embedding never enters the GEMM
+      for (int p = 0; p < nt_; ++p)
+        add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
     jobs.n = nj;
     dim3 grid(rows, nj);
     CK(tc::launch_k(pdl_, row_gather_kernel, grid, dim3(128), 0, stream, jobs, (const int32_t*)d_parent_, (const int32_t*)d_tok_, V, k, t == 0 ? 1 : 0));
@@ -280,8 +303,18 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     e.h_f32 = (l == L - 1 && opt.attention_mode == LINMT_ATT_GLOBAL_DOT) ? s.h_cur[l] : nullptr;
     e.hf_row_stride = Hp;
     e.row_len = nullptr; e.pos = 0; e.nt = nt_;
-    const int K = (l == 0 && feed) ? 3 * Hp : 2 * Hp;
-    int rc = tc_gemm(hprev_planes(l), 0, R, m.p_dec_w[l], rows, 4 * Hp, K, e);
+    int K = (l == 0 && feed) ? 3 * Hp : 2 * Hp;
+    int rc;
+    if (l == 0 && m.dec_xw) {
+      // K columns (h_prev | htilde_prev) only: the x columns of panel and weights are skipped, their term comes from the table
+      tc::Planes wrest = m.p_dec_w[0];
+      for (int p = 0; p < 3; ++p) if (wrest.p[p]) wrest.p[p] += Hp;
+      e.xw = m.dec_xw; e.x_tok = d_tok_; e.x_ld = 4 * Hp; e.x_vocab = V; e.x_unk = kUnk;
+      K -= Hp;
+      rc = tc_gemm(hprev_planes(0), Hp, R, wrest, rows, 4 * Hp, K, e);
+    } else {
+      rc = tc_gemm(hprev_planes(l), 0, R, m.p_dec_w[l], rows, 4 * Hp, K, e);
+    }
     if (rc) return rc;
     if (kernel_timing) rec_flops_ += 2.0 * rows * 4.0 * H * (double)((K / Hp) * H);
   }

@@ -321,8 +321,24 @@ struct TcEpiLstm {
   // Optional beam reordering of the cell state: row r continues slot c_parent[r] of its sentence (k slots per
   // sentence), so c_prev is read from that row -- the state then needs no copy between steps.
   const int32_t* c_parent = nullptr; int c_k = 1;
+  // Optional precomputed input term: xw[tok][col] = (W_x . embedding(tok))[col] for every vocabulary entry, added
+  // to the accumulator of row r with tok = x_tok[r] (out-of-range ids count as x_unk) -- the embedding part of
+  // the first decoder layer's product then costs a row lookup instead of a third of the GEMM.
+  const float* xw = nullptr; const int32_t* x_tok = nullptr; int x_ld = 0; int x_vocab = 0; int x_unk = 0;
+  __device__ __forceinline__ int x_row(int row) const {
+    const int t = x_tok[row];
+    return (t < 0 || t >= x_vocab) ? x_unk : t;
+  }
   __device__ __forceinline__ int c_src_row(int row) const { return c_parent ? (row / c_k) * c_k + c_parent[row] : row; }
-  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+  __device__ __forceinline__ void operator()(int row, int col0, const float* v_in) const {
+    float vx[16];
+    const float* v = v_in;
+    if (xw) {
+      const float* xr = xw + (size_t)x_row(row) * x_ld + col0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) vx[i] = v_in[i] + xr[i];
+      v = vx;
+    }
     const bool active = (row_len == nullptr) || (pos < row_len[row]);
     const int j0 = col0 >> 2;
     const size_t ic = (size_t)row * ldc + j0;
@@ -376,6 +392,30 @@ struct TcEpiLstm {
     float* cs = sbuf;                                            // [32][20] floats: c_prev in, c out
     unsigned short* hs = reinterpret_cast<unsigned short*>(sbuf + 32 * 20);   // [planes][32][24] 16-bit
     float* hf = sbuf + 32 * 20 + 3 * 32 * 12;                    // [32][20] floats: h in fp32 (only if h_f32)
+    if (xw) {
+      // the rows of the input-term table for this block, staged coalesced, then added lane = row
+      const int nq4 = 4 * nch;
+      for (int s = lane; s < 32 * nq4; s += 32) {
+        const int r = s / nq4, g = s - r * nq4;
+        if (row0 + r < M)
+          *reinterpret_cast<float4*>(sbuf + r * kEpiScratchStride + 4 * g) =
+              *reinterpret_cast<const float4*>(xw + (size_t)x_row(row0 + r) * x_ld + col_first + 4 * g);
+      }
+      __syncwarp();
+      if (valid) {
+#pragma unroll
+        for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
+          if (ci < nch) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 t = *reinterpret_cast<const float4*>(sbuf + lane * kEpiScratchStride + 16 * ci + 4 * q);
+              v[ci][4 * q] += t.x; v[ci][4 * q + 1] += t.y; v[ci][4 * q + 2] += t.z; v[ci][4 * q + 3] += t.w;
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
     // c_prev: coalesced load into the staging area
     for (int s = lane; s < 32 * nq; s += 32) {
       const int r = s / nq, g = s - r * nq;
