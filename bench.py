@@ -33,9 +33,10 @@ UNIT = "tokens/s"
 FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
 # DRAM bytes of one launch at 768 rows from ncu captures (see profiles/): read + write
 VOCAB_GEMM_TRAFFIC_BYTES = 185.7e6  # 131.1 MB + 54.6 MB, profiles/vocab_gemm_tensor_path_C2.md (algorithmic 218 MB; logits partly still in L2)
-# gate GEMM: 66.7 MB measured at K = 3072 (profiles/gate_gemm_tensor_path_C2.md, algorithmic 69.1 MB); the three
-# K = 2048 layers scaled by their algorithmic bytes (49.2 MB): average of the four launches of a stack
-GATE_GEMM_TRAFFIC_BYTES = (66.7e6 + 3 * 66.7e6 * 49.2 / 69.1) / 4
+# gate GEMM: 66.7 MB measured at K = 3072 (profiles/gate_gemm_tensor_path_C2.md, algorithmic 69.1 MB); the four
+# launches of a stack now all run K = 2048 (algorithmic 49.2 MB, scaled from that capture), the first of them reading
+# 12.6 MB of input-term table rows besides: average of the four
+GATE_GEMM_TRAFFIC_BYTES = 66.7e6 * 49.2 / 69.1 + 12.6e6 / 4
 
 
 WORKLOADS = {
