@@ -117,6 +117,19 @@ size_t linmt_blob_floats(const linmt_model_desc* desc);
 int linmt_create_from_weights(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models,
                               size_t blob_floats, const linmt_options* opt, linmt_engine** out);
 
+/* The same engine on several GPUs of one box: devices[0..n_devices) each get a replica of the model(s)
+ * (opt->device is then ignored), and linmt_decode_batch / linmt_decode_file deal device batches of
+ * sentences to them, one host thread per device inside the library; nothing crosses between the GPUs
+ * and results come back in the caller's order.  Sentences are independent in the reference too
+ * (EnsembleFactory::DecodeSentence keeps no state between calls, src/decoder.h:1780-1840); its own use
+ * of several GPUs is one DecoderModelWrapper per GPU index (src/decoder.h:1676-1684, config key
+ * --multi-gpu, src/decoder_sentence.cu:183-198), which this replaces.  n_devices = 0 means opt->device. */
+int linmt_create_from_weights_on(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models,
+                                 size_t blob_floats, const linmt_options* opt, const int32_t* devices,
+                                 int32_t n_devices, linmt_engine** out);
+/* Number of devices a handle decodes on. */
+int32_t linmt_device_count(const linmt_engine* e);
+
 /* Creates an engine from a decoding-sentence config file, reading the model file(s) named
  * by --nmt-model in the reference's text format.  Replaces DecoderSentence::Init
  * (src/decoder_sentence.cu:14-37). */
@@ -124,8 +137,14 @@ int linmt_create(const char* config_path, linmt_engine** out);
 
 void linmt_destroy(linmt_engine* e);
 
-/* Text of the last error on this handle (or of the last failed create when e == NULL). */
+/* Text of the last error on this handle (or of the last failed create when e == NULL).
+ * A decode that returns LINMT_ECUDA with "gave up waiting on a barrier" leaves the handle unusable:
+ * every wait inside the GEMM kernels is bounded (about a second) and a wait that ran out means the
+ * device state of this handle can no longer be trusted, so every later decode on it fails the same
+ * way.  Destroy the handle and create a new one. */
 const char* linmt_last_error(const linmt_engine* e);
+/* Text of the last error of linmt_create / linmt_read_model_file (config and model-file problems). */
+const char* linmt_front_error(void);
 
 /* Effective beam after clamping. */
 int32_t linmt_beam(const linmt_engine* e);
@@ -148,6 +167,8 @@ typedef struct linmt_trace {
   const int32_t* force_parent;
   const float* force_score;
   float* gold_logp;   /* [n][Tm][k]: log p of the forced token of each slot (needs force_*), may be NULL */
+  float* pt;          /* [n][Tm+1][k]: attention centre p_t of every forward (local attention; first ensemble
+                         member), may be NULL.  Entries of forwards that did not run hold the bit pattern 0xffffffff. */
 } linmt_trace;
 
 /* Decodes n independent sentences.  Replaces EnsembleFactory<T>::DecodeSentence
@@ -235,12 +256,6 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
  * src/decoder.h:401-410.  idx/logp are [R][kk], eos_logp [R]. */
 int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, int32_t* idx, float* logp,
                          float* eos_logp, int32_t device);
-
-/* Average milliseconds of one tensor-core GEMM launch (R x N x K, operands already on the
- * device) for a given tile width / plane count / stage limit; 0 = the engine's own choice.
- * A tuning and roofline aid; has no counterpart in the reference. */
-int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
-                      float* ms_out, int32_t device);
 
 /* Y[R][N] = X[R][K] . Wt[N][K]^T on the tensor-core kernel (three bf16 planes, fp32-class
  * result) WITHOUT allocating: for hosts that cannot call cudaMalloc once they are running --

@@ -24,7 +24,7 @@ class TraceC(C.Structure):
     _fields_ = [("cand_tok", C.c_void_p), ("cand_logp", C.c_void_p), ("surv_tok", C.c_void_p),
                 ("surv_parent", C.c_void_p), ("surv_score", C.c_void_p), ("final_logp", C.c_void_p),
                 ("force_tok", C.c_void_p), ("force_parent", C.c_void_p), ("force_score", C.c_void_p),
-                ("gold_logp", C.c_void_p)]
+                ("gold_logp", C.c_void_p), ("pt", C.c_void_p)]
 
 
 class StatsC(C.Structure):
@@ -35,9 +35,9 @@ class StatsC(C.Structure):
 
 
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",
-           "linmt_create_from_weights", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
+           "linmt_create_from_weights", "linmt_create_from_weights_on", "linmt_device_count", "linmt_front_error", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
            "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
-           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_k_gemm_time", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch",
+           "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch",
            "linmt_read_model_file", "python_unk_init", "python_unk_do_job", "linmt_unk_create", "linmt_unk_process", "linmt_unk_destroy"]
 
 _lib = None
@@ -62,6 +62,9 @@ def load():
     lib.linmt_blob_floats.restype = C.c_size_t
     lib.linmt_create_from_weights.argtypes = [C.POINTER(ModelDescC), C.POINTER(C.c_void_p), C.c_int32, C.c_size_t,
                                               C.POINTER(OptionsC), C.POINTER(C.c_void_p)]
+    lib.linmt_create_from_weights_on.argtypes = [C.POINTER(ModelDescC), C.POINTER(C.c_void_p), C.c_int32, C.c_size_t,
+                                                 C.POINTER(OptionsC), C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)]
+    lib.linmt_device_count.argtypes = [C.c_void_p]
     lib.linmt_create.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
     lib.linmt_destroy.argtypes = [C.c_void_p]
     lib.linmt_destroy.restype = None
@@ -81,7 +84,6 @@ def load():
                                  C.c_int32, C.c_int32]
     lib.linmt_k_softmax_topk.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                          C.c_void_p, C.c_int32]
-    lib.linmt_k_gemm_time.argtypes = [C.c_int32] * 7 + [C.POINTER(C.c_float), C.c_int32]
     lib.linmt_gemm_f32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     lib.linmt_decode_file.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
     lib.linmt_read_model_file.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32]

@@ -41,17 +41,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
-def build_phase_trace() -> str:
-    """Tuning aid: the tensor-core GEMM with per-CTA phase timestamps (see tuning/tc_phase_trace.cu)."""
-    out = os.path.join(HERE, "tuning", "tc_phase_trace")
-    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           os.path.join(HERE, "tuning", "tc_phase_trace.cu"), "-o", out, "-lcuda"]
-    subprocess.run(cmd, check=True)
-    return out
-
-
 if __name__ == "__main__":
-    if "--phase-trace" in sys.argv:
-        print(build_phase_trace())
-    else:
-        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

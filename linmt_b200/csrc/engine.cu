@@ -11,8 +11,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <numeric>
+#include <thread>
 
 #include "gemm_simt.cuh"
 #include "step_kernels.cuh"
@@ -43,6 +45,17 @@ int Engine::dalloc(T** p, size_t count) {
   *p = static_cast<T*>(q);
   return LINMT_OK;
 }
+// Replaces *p by a fresh allocation of `count` elements and frees the old one.
+template <class T>
+int Engine::regrow(T** p, size_t count) {
+  if (*p) {
+    auto it = std::find(allocs_.begin(), allocs_.end(), static_cast<void*>(*p));
+    if (it != allocs_.end()) allocs_.erase(it);
+    cudaFree(*p);
+    *p = nullptr;
+  }
+  return dalloc(p, count);
+}
 #define DA(p, n)                                  \
   do {                                            \
     int rc_ = dalloc(&(p), (n));                  \
@@ -50,7 +63,7 @@ int Engine::dalloc(T** p, size_t count) {
   } while (0)
 
 Engine::~Engine() {
-  if (stream) cudaStreamSynchronize(stream);
+  if (stream) { cudaSetDevice(opt.device); cudaStreamSynchronize(stream); }
   for (void* p : allocs_) cudaFree(p);
   for (void* p : trace_allocs_) cudaFree(p);
   if (h_meta_) cudaFreeHost(h_meta_);
@@ -171,14 +184,18 @@ int Engine::pack_model(const float* blob, DevModel& m) {
   }
   // attention projections: rows < Hp: W_p (out n, in k) = blob[k*H + n];
   // rows Hp + j: (W_a^T h)[j] = sum_i W_a[i,j] h[i], W_a[i,j] = blob[j*H + i]  (src/layer_attention.h:327)
-  host.assign((size_t)2 * Hp * Hp, 0.f);
+  // rows 2Hp + n (tensor path): W_c2, the h_top half of the attention output product -- it depends on h_top
+  // alone, so it is computed with the projections, ahead of the attention kernel, instead of after it
+  const int proj_rows = use_tc_ ? 3 * Hp : 2 * Hp;
+  host.assign((size_t)proj_rows * Hp, 0.f);
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < H; ++n)
     for (int kx = 0; kx < H; ++kx) {
       host[(size_t)n * Hp + kx] = bv.Wp[(size_t)kx * H + n];
       host[(size_t)(Hp + n) * Hp + kx] = bv.Wa[(size_t)n * H + kx];
+      if (use_tc_) host[(size_t)(2 * Hp + n) * Hp + kx] = bv.Wc2[(size_t)kx * H + n];
     }
-  if ((rc = store(&m.att_proj_w, &m.p_att_proj_w, (size_t)2 * Hp, Hp))) return rc;
+  if ((rc = store(&m.att_proj_w, &m.p_att_proj_w, (size_t)proj_rows, Hp))) return rc;
   // attention output: columns (ctx | h_top) -> W_c1 | W_c2 (src/layer_attention.h:441,448)
   host.assign((size_t)Hp * 2 * Hp, 0.f);
 #pragma omp parallel for schedule(static)
@@ -221,7 +238,7 @@ int Engine::alloc_state(DevState& s) {
   s.h_cur.resize(L); s.c_cur.resize(L); s.h_prev.resize(L); s.c_prev.resize(L);
   for (int l = 0; l < L; ++l) { DA(s.h_cur[l], rh); DA(s.c_cur[l], rh); DA(s.h_prev[l], rh); DA(s.c_prev[l], rh); }
   DA(s.htilde, rh); DA(s.htilde_prev, rh);
-  DA(s.proj, 2 * rh); DA(s.ctx, rh);
+  DA(s.proj, 3 * rh); DA(s.ctx, rh);
   DA(s.logits, (size_t)R * Vp);
   DA(s.hs, (size_t)B * opt.max_src_len * Hp);
   DA(s.enc_x, (size_t)B * Hp);
@@ -238,7 +255,6 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
     return fail(LINMT_EINVAL, "bad model dimensions (layers 1..5)");
   if (nm < 1) return fail(LINMT_EINVAL, "need at least one model");
   if (nm > 8) return fail(LINMT_ELIMIT, "at most 8 ensemble members");
-  if (nm > 1 && o.print_info) return fail(LINMT_EINVAL, "alignment output (print_info) is not available with ensembles");
   if (o.precision != LINMT_PREC_FP32 && o.precision != LINMT_PREC_BF16) return fail(LINMT_EINVAL, "bad precision");
   if (o.gemm_path < LINMT_GEMM_AUTO || o.gemm_path > LINMT_GEMM_TENSOR_V16X) return fail(LINMT_EINVAL, "bad gemm_path");
   if (o.precision == LINMT_PREC_BF16 && o.gemm_path == LINMT_GEMM_SIMT)
@@ -246,6 +262,8 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
   { const char* pe = std::getenv("LINMT_XW"); xw_table_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_XW=0: test knob
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
+  { const char* pe = std::getenv("LINMT_ATT_GROUP"); att_group_ = !(pe && std::atoi(pe) == 0); }
+  { const char* pe = std::getenv("LINMT_ATT_MERGE"); att_merge_ = use_tc_ && !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
@@ -274,6 +292,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   Vp = round_up(V, 128);
   B = o.max_batch; R = B * k;
   win = (o.attention_mode == LINMT_ATT_LOCAL_P_GENERAL) ? 2 * o.attention_d + 1 : o.max_src_len;
+  rec_win = (nm > 1) ? o.max_src_len : win;   // ensembles keep dense alignment records: the members' windows differ
   Tcap = o.max_steps + 1;
   fin_cap = Tcap * k;
   CK(cudaSetDevice(o.device));
@@ -308,7 +327,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   pmax_ld_ = 4 * ((Vp + 47) / 48) + 4;   // four column blocks per tile, tiles at least 48 wide
   DA(d_pmax_, (size_t)R * pmax_ld_);
   if (o.print_info) {
-    DA(d_rec_align_, (size_t)Tcap * R * win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
+    DA(d_rec_align_, (size_t)Tcap * R * rec_win); DA(d_rec_lo_, (size_t)Tcap * R); DA(d_rec_vit_, (size_t)Tcap * R);
   }
   if (use_tc_ && xw_table_) { const int rc_xw = build_xw_tables(); if (rc_xw) return rc_xw; }
   CK(cudaDeviceSynchronize());  // every weight upload has landed before the first decode
@@ -409,14 +428,10 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
   }
   // 4. scores, softmax x Gaussian, context
   {
-    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
+    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * rec_win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
-    const size_t smem = sizeof(float) * (win + 8);
-    attention_kernel<<<rows, 256, smem, stream>>>(s.proj, 2 * Hp, u_alt, Hp, m.vp, s.hs, d_len_, s.ctx, H, Hp, k,
-                                                  opt.max_src_len, opt.attention_mode, opt.attention_d, win, ra, rl, rv,
-                                                  tc::Planes{}, 0);
-    LAUNCHED();
+    if (int rc = launch_attention(mi, t, rows, u_alt, s.ctx, tc::Planes{}, 0, ra, rl, rv)) return rc;
   }
   // 5. attentional state htilde = tanh(W_c1 ctx + W_c2 h + b)
   {
@@ -434,6 +449,39 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     LAUNCHED();
     if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
   }
+  return LINMT_OK;
+}
+
+// Attention of one decoder forward (both GEMM families): a CTA per group of beams of a sentence
+// (attention_group_kernel), or a CTA per row (attention_kernel; LINMT_ATT_GROUP=0, a test knob -- the two
+// return the same bits).
+int Engine::launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
+                             float* ra, int32_t* rl, int32_t* rv) {
+  const AttTrace at{mi == 0 ? trace_dev_.pt : nullptr, d_orig_, trace_dev_.Tm + 1, t};
+  DevModel& m = models_[mi];
+  DevState& s = states_[mi];
+  const int ens = ens_member_code(mi);
+  const int ldp = att_merge_ ? 3 * Hp : 2 * Hp;
+  if (!att_group_) {
+    const size_t smem = sizeof(float) * (win + 8);
+    CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, ldp, u_alt, Hp, (const float*)m.vp,
+                    (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
+                    (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens, at));
+    LAUNCHED();
+    return LINMT_OK;
+  }
+  const int n_act = rows / k;
+  // beams per CTA: as few as fill the SMs, at most kAttBeams, within 48 KB of shared memory
+  const size_t per_beam = sizeof(float) * (size_t)(Hp + win + 16);
+  int bpc_max = (int)std::min<size_t>(kAttBeams, (48 * 1024) / per_beam);
+  if (bpc_max < 1) return fail(LINMT_ELIMIT, "hidden size too large for the attention kernel's shared memory");
+  int groups = std::max((k + bpc_max - 1) / bpc_max, std::min(k, (n_sm_ + n_act - 1) / n_act));
+  const int bpc = (k + groups - 1) / groups;
+  groups = (k + bpc - 1) / bpc;
+  CK(tc::launch_k(pdl_, attention_group_kernel, dim3(n_act, groups), dim3(256), per_beam * bpc, stream, (const float*)s.proj, ldp, u_alt, Hp,
+                  (const float*)m.vp, (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len,
+                  (int)opt.attention_mode, (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens, bpc, at));
+  LAUNCHED();
   return LINMT_OK;
 }
 
@@ -458,6 +506,7 @@ int Engine::step_tail(int t, int rows) {
         rf.bias = m0.voc_b; rf.K = Hp;
         rf.eps_coef = 1.1f * (1.0f / 1024.0f) * m0.voc_wnorm_max;
       }
+      if (refine_) trace_dev_.rf = rf;
       CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_, refine_ ? &rf : nullptr));
     } else {
       // EnsembleFactory::EnsemblesModels (src/decoder.h:1910-1931): mean of the members'
@@ -530,6 +579,7 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     trace_dev_.force_tok = trace_dev->force_tok; trace_dev_.force_parent = trace_dev->force_parent;
     trace_dev_.force_score = trace_dev->force_score; trace_dev_.Tm = trace_Tm;
     trace_dev_.gold_logp = trace_dev->gold_logp;
+    trace_dev_.pt = trace_dev->pt;
   }
   gemm_ev_used_ = 0; rec_ev_used_ = 0; rec_flops_ = 0.0;
   int rc = use_tc_ ? run_encoder_tc(n, Smax) : run_encoder(n, Smax);
@@ -549,7 +599,7 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     a.bs = BeamState{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
     a.steps = d_steps_; a.src_len = d_len_; a.orig = d_orig_;
     a.rec_align = d_rec_align_; a.rec_lo = d_rec_lo_; a.rec_vit = d_rec_vit_;
-    a.fin_final = d_fin_final_; a.win = win; a.k = k; a.nbest = opt.nbest; a.max_len = max_len; a.max_src = opt.max_src_len;
+    a.fin_final = d_fin_final_; a.win = rec_win; a.k = k; a.nbest = opt.nbest; a.max_len = max_len; a.max_src = opt.max_src_len;
     a.lp_alpha = opt.lp_alpha; a.cp_beta = opt.cp_beta; a.min_ratio = opt.min_ratio;
     a.out_tok = d_out_tok; a.out_len = d_out_len; a.out_score = d_out_score; a.out_vit = d_out_vit; a.out_align = d_out_align;
     const size_t smem = 4 * ((size_t)opt.max_src_len * sizeof(float) + (size_t)max_len * sizeof(int));
@@ -610,16 +660,21 @@ int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, c
     const int cn = std::min(B, n - c0);
     const int32_t base = src_off[c0];
     const size_t n_ids = (size_t)(src_off[c0 + cn] - base);
+    // staging buffers grow with the longest input seen; the outgrown buffer is freed (the previous chunk's
+    // work on it ended with the synchronisation in finish_timing)
     if (n_ids > d_ids_cap_) {
-      DA(d_ids_, n_ids + 1024);
+      if (int rc_ = regrow(&d_ids_, n_ids + 1024)) return rc_;
       d_ids_cap_ = n_ids + 1024;
     }
     const size_t need = (size_t)cn * nb;
     if (need > out_cap_len_ || max_len > out_cap_maxlen_) {
       const size_t ml = std::max<size_t>(max_len, out_cap_maxlen_);
       const size_t cap = std::max<size_t>(need, (size_t)B * nb);
-      DA(d_out_tok_, cap * ml); DA(d_out_vit_, cap * ml); DA(d_out_len_, cap); DA(d_out_score_, cap);
-      if (opt.print_info) DA(d_out_align_, cap * ml * opt.max_src_len);
+      int rc_;
+      if ((rc_ = regrow(&d_out_tok_, cap * ml)) || (rc_ = regrow(&d_out_vit_, cap * ml)) || (rc_ = regrow(&d_out_len_, cap)) ||
+          (rc_ = regrow(&d_out_score_, cap)))
+        return rc_;
+      if (opt.print_info && (rc_ = regrow(&d_out_align_, cap * ml * opt.max_src_len))) return rc_;
       out_cap_len_ = cap; out_cap_maxlen_ = ml;
     }
     CK(cudaMemcpyAsync(d_ids_, src_ids + base, n_ids * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
@@ -654,6 +709,7 @@ int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, c
       if ((rc = mk(n_s, 4, trace->surv_score ? trace->surv_score + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_score))) return rc;
       if ((rc = mk(n_f, 4, trace->final_logp ? trace->final_logp + (size_t)c0 * k : nullptr, nullptr, (void**)&td.final_logp))) return rc;
       if ((rc = mk(n_s, 4, trace->gold_logp ? trace->gold_logp + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.gold_logp))) return rc;
+      if ((rc = mk((size_t)cn * (Tm_all + 1) * k, 4, trace->pt ? trace->pt + (size_t)c0 * (Tm_all + 1) * k : nullptr, nullptr, (void**)&td.pt))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_tok ? trace->force_tok + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_tok))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_parent ? trace->force_parent + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_parent))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_score ? trace->force_score + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_score))) return rc;
@@ -674,6 +730,37 @@ int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, c
   }
   stats.last_decode_ms = total_ms; stats.last_gemm_ms = gemm_ms; stats.last_gemm_launches = gemm_launches;
   return LINMT_OK;
+}
+
+int run_on_engines(linmt_engine* h, const std::vector<int>& order, const std::function<int(Engine&, int)>& job) {
+  const int ne = h->n_engines();
+  if (ne == 1 || order.size() <= 1) {
+    for (int item : order)
+      if (int rc = job(h->eng, item)) return rc;
+    return LINMT_OK;
+  }
+  std::atomic<size_t> next{0};
+  std::atomic<int> first_rc{LINMT_OK};
+  std::mutex err_mutex;
+  std::string err_text;
+  auto worker = [&](int ei) {
+    Engine& g = h->engine(ei);
+    while (first_rc.load() == LINMT_OK) {
+      const size_t i = next.fetch_add(1);
+      if (i >= order.size()) break;
+      const int rc = job(g, order[i]);
+      if (rc != LINMT_OK) {
+        std::lock_guard<std::mutex> lock(err_mutex);
+        if (first_rc.load() == LINMT_OK) { first_rc.store(rc); err_text = g.err; }
+      }
+    }
+  };
+  std::vector<std::thread> threads;
+  for (int ei = 1; ei < ne; ++ei) threads.emplace_back(worker, ei);
+  worker(0);
+  for (auto& t : threads) t.join();
+  if (first_rc.load() != LINMT_OK) h->eng.err = err_text;
+  return first_rc.load();
 }
 
 }  // namespace linmt
@@ -708,21 +795,39 @@ size_t linmt_blob_floats(const linmt_model_desc* d) {
   return n;
 }
 
-int linmt_create_from_weights(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models, size_t blob_floats,
-                              const linmt_options* opt, linmt_engine** out) {
-  if (!desc || !blobs || !opt || !out) { g_create_error = "null argument"; return LINMT_EINVAL; }
+int linmt_create_from_weights_on(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models, size_t blob_floats,
+                                 const linmt_options* opt, const int32_t* devices, int32_t n_devices, linmt_engine** out) {
+  if (!desc || !blobs || !opt || !out || (n_devices > 0 && !devices)) { g_create_error = "null argument"; return LINMT_EINVAL; }
+  *out = nullptr;
+  if (n_devices > 64) { g_create_error = "at most 64 devices"; return LINMT_ELIMIT; }
+  for (int i = 0; i < n_devices; ++i)
+    for (int j = 0; j < i; ++j)
+      if (devices[i] == devices[j]) { g_create_error = "a device is listed twice"; return LINMT_EINVAL; }
   linmt_engine* e = new (std::nothrow) linmt_engine();
   if (!e) { g_create_error = "out of host memory"; return LINMT_ENOMEM; }
-  int rc = e->eng.init(*desc, blobs, n_models, blob_floats, *opt);
-  if (rc != LINMT_OK) {
-    g_create_error = e->eng.err;
-    delete e;
-    *out = nullptr;
-    return rc;
+  const int nd = n_devices > 0 ? n_devices : 1;
+  for (int i = 0; i < nd; ++i) {
+    linmt_options o = *opt;
+    if (n_devices > 0) o.device = devices[i];
+    Engine* g = &e->eng;
+    if (i > 0) { e->replicas.emplace_back(new (std::nothrow) Engine()); g = e->replicas.back().get(); }
+    int rc = g ? g->init(*desc, blobs, n_models, blob_floats, o) : LINMT_ENOMEM;
+    if (rc != LINMT_OK) {
+      g_create_error = g ? g->err : "out of host memory";
+      delete e;
+      return rc;
+    }
   }
   *out = e;
   return LINMT_OK;
 }
+
+int linmt_create_from_weights(const linmt_model_desc* desc, const float* const* blobs, int32_t n_models, size_t blob_floats,
+                              const linmt_options* opt, linmt_engine** out) {
+  return linmt_create_from_weights_on(desc, blobs, n_models, blob_floats, opt, nullptr, 0, out);
+}
+
+int32_t linmt_device_count(const linmt_engine* e) { return e ? e->n_engines() : 0; }
 
 void linmt_destroy(linmt_engine* e) { delete e; }
 
@@ -734,7 +839,43 @@ int linmt_decode_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* s
                        int32_t max_len, int32_t* out_tok, int32_t* out_len, float* out_score, int32_t* out_vit,
                        float* out_align, const linmt_trace* trace) {
   if (!e) return LINMT_EINVAL;
-  return e->eng.decode_host(src_ids, src_off, n, steps, max_len, out_tok, out_len, out_score, out_vit, out_align, trace);
+  Engine& g0 = e->eng;
+  const int B = g0.B;
+  if (e->n_engines() == 1 || trace || n <= B || !src_ids || !src_off || !steps || !out_tok || !out_len || !out_score)
+    return g0.decode_host(src_ids, src_off, n, steps, max_len, out_tok, out_len, out_score, out_vit, out_align, trace);
+  // several devices: the job is cut into device batches of consecutive sentences; each device's host thread
+  // takes the next batch when it is free, the batches with the most decoder forwards first
+  const int nchunks = (n + B - 1) / B;
+  std::vector<long long> cost(nchunks, 0);
+  for (int c = 0; c < nchunks; ++c) {
+    int tm = 0;
+    const int cn = std::min(B, n - c * B);
+    for (int i = 0; i < cn; ++i) tm = std::max(tm, steps[c * B + i]);
+    cost[c] = (long long)(tm + 1) * cn;
+  }
+  std::vector<int> order(nchunks);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+  const size_t nb = (size_t)g0.opt.nbest, ml = (size_t)max_len, ms = (size_t)g0.opt.max_src_len;
+  std::vector<float> ms_per_engine(e->n_engines(), 0.f);
+  std::mutex stat_mutex;
+  int rc = linmt::run_on_engines(e, order, [&](Engine& g, int c) -> int {
+    const size_t c0 = (size_t)c * B;
+    const int cn = std::min(B, n - (int)c0);
+    int r = g.decode_host(src_ids, src_off + c0, cn, steps + c0, max_len, out_tok + c0 * nb * ml, out_len + c0 * nb,
+                          out_score + c0 * nb, out_vit ? out_vit + c0 * nb * ml : nullptr,
+                          out_align ? out_align + c0 * nb * ml * ms : nullptr, nullptr);
+    if (r == LINMT_OK) {
+      std::lock_guard<std::mutex> lock(stat_mutex);
+      for (int i = 0; i < e->n_engines(); ++i)
+        if (&e->engine(i) == &g) ms_per_engine[i] += g.stats.last_decode_ms;
+    }
+    return r;
+  });
+  if (rc != LINMT_OK) return rc;
+  // device time of the call = the busiest device's; the counters of the replicas are folded into the handle's
+  g0.stats.last_decode_ms = *std::max_element(ms_per_engine.begin(), ms_per_engine.end());
+  return LINMT_OK;
 }
 
 int linmt_decode_batch_device(linmt_engine* e, const int32_t* d_src_ids, const int32_t* src_off_host, int32_t n,
@@ -800,6 +941,11 @@ int linmt_score_batch(linmt_engine* e, const int32_t* src_ids, const int32_t* sr
 int linmt_get_stats(const linmt_engine* e, linmt_stats* out) {
   if (!e || !out) return LINMT_EINVAL;
   *out = e->eng.stats;
+  for (const auto& r : e->replicas) {   // launches and forwards of every device
+    out->kernel_launches += r->stats.kernel_launches;
+    out->decoder_row_steps += r->stats.decoder_row_steps;
+    out->sentence_steps += r->stats.sentence_steps;
+  }
   return LINMT_OK;
 }
 

@@ -10,7 +10,9 @@
 #include "step_kernels.cuh"
 #include "gemm_tc.cuh"
 #include <array>
+#include <functional>
 #include <map>
+#include <memory>
 #include <tuple>
 
 namespace linmt {
@@ -25,7 +27,7 @@ struct DevModel {
   std::vector<float*> enc_w, enc_b;      // [4Hp][2Hp], [4Hp]   gate-interleaved rows 4j+g
   std::vector<float*> dec_w, dec_b;      // layer 0: [4Hp][3Hp] (x | h' | htilde'), others [4Hp][2Hp]
   std::vector<int> dec_ldw;
-  float* att_proj_w = nullptr;           // [2Hp][Hp]: rows < Hp = W_p, rows >= Hp = W_a^T
+  float* att_proj_w = nullptr;           // [2Hp][Hp]: rows < Hp = W_p, rows >= Hp = W_a^T (tensor path: [3Hp][Hp], rows >= 2Hp = W_c2)
   float* att_out_w = nullptr;            // [Hp][2Hp]: (ctx | h_top)
   float* att_bout = nullptr;             // [Hp]
   float* vp = nullptr;                   // [Hp]
@@ -52,7 +54,7 @@ struct DevState {
   float* x = nullptr;                        // [R][Hp]
   std::vector<float*> h_cur, c_cur, h_prev, c_prev;  // [L] x [R][Hp]
   float *htilde = nullptr, *htilde_prev = nullptr;   // [R][Hp]
-  float *proj = nullptr, *ctx = nullptr;             // [R][2Hp], [R][Hp]
+  float *proj = nullptr, *ctx = nullptr;             // [R][2Hp or 3Hp], [R][Hp]
   float* logits = nullptr;                           // [R][Vp]
   float* hs = nullptr;                               // [B][max_src][Hp]
   float* enc_x = nullptr;                            // [B][Hp]
@@ -75,7 +77,7 @@ class Engine {
   std::string err;
   linmt_model_desc desc{};
   linmt_options opt{};
-  int k = 0, kk = 0, H = 0, Hp = 0, V = 0, Vp = 0, L = 0, B = 0, R = 0, win = 0, Tcap = 0, fin_cap = 0;
+  int k = 0, kk = 0, H = 0, Hp = 0, V = 0, Vp = 0, L = 0, B = 0, R = 0, win = 0, rec_win = 0, Tcap = 0, fin_cap = 0;
   int n_models = 0;
   cudaStream_t stream = nullptr;
   linmt_stats stats{};
@@ -86,10 +88,13 @@ class Engine {
   std::vector<std::pair<std::string, int>> src_words_sorted;
   int longest_sentence = 0;
   int print_align_scores = 0;
+  int src_unk_id = 0;   // id unknown source words read: the source map's "UNK" entry, 0 when it has none
   std::string result_buf;
 
  private:
   int fail(int code, const std::string& msg) { err = msg; return code; }
+  // role of member mi in the alignment record of a step: 0 = single model, 1 / 2 / 3 = first / middle / last member
+  int ens_member_code(int mi) const { return n_models == 1 ? 0 : (mi == 0 ? 1 : (mi == n_models - 1 ? 3 : 2)); }
   int pack_model(const float* blob, DevModel& m);
   int alloc_state(DevState& s);
   int run_encoder(int n, int Smax);
@@ -97,6 +102,8 @@ class Engine {
   int run_encoder_tc(int n, int Smax);
   int run_decoder_step_tc(int mi, int t, int rows);
   int step_tail(int t, int rows);
+  int launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
+                       float* rec_align, int32_t* rec_lo, int32_t* rec_vit);
   int alloc_state_tc(TcState& s);
   int build_xw_tables();   // dec_xw of every model (tensor path, xw_table_)
   int alloc_planes(tc::Planes& p, size_t rows, int ld);
@@ -115,6 +122,8 @@ class Engine {
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
   bool xw_table_ = false;  // first decoder layer: embedding term from a per-vocabulary table instead of the GEMM
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
+  bool att_merge_ = false; // tensor path: W_c2 . h_top computed with the attention projections (LINMT_ATT_MERGE=0: test knob)
+  bool att_group_ = true;  // attention: one CTA per group of beams of a sentence (LINMT_ATT_GROUP=0: one per row, test knob)
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
@@ -138,6 +147,7 @@ class Engine {
   std::vector<DevState> states_;
   std::vector<void*> allocs_;
   template <class T> int dalloc(T** p, size_t count);
+  template <class T> int regrow(T** p, size_t count);
 
   // batch metadata (device) and pinned staging
   int32_t *d_off_ = nullptr, *d_len_ = nullptr, *d_steps_ = nullptr, *d_orig_ = nullptr;
@@ -176,7 +186,18 @@ void pack_gate_weights(const float* const* mats, int nseg, int H, int Hp, float*
 
 }  // namespace linmt
 
-// The opaque handle of the C ABI.
+// The opaque handle of the C ABI: the engine on the first device and, for a handle created on several
+// devices, one replica of the same models per further device.  Sentences are independent, so a job is
+// dealt to the devices in device batches, one host thread per device, with no traffic between them.
 struct linmt_engine {
   linmt::Engine eng;
+  std::vector<std::unique_ptr<linmt::Engine>> replicas;
+  int n_engines() const { return 1 + (int)replicas.size(); }
+  linmt::Engine& engine(int i) { return i == 0 ? eng : *replicas[i - 1]; }
 };
+
+namespace linmt {
+// Runs job(engine, item) for item = order[0], order[1], ... on the engines of a handle, one host thread per
+// engine, each taking the next item when it is free.  Returns the first error; engine 0's `err` names it.
+int run_on_engines(linmt_engine* h, const std::vector<int>& order, const std::function<int(Engine&, int)>& job);
+}  // namespace linmt

@@ -320,29 +320,39 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   }
   if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   // 3. attention projections: tanh(W_p h) | W_a^T h
-  const float* u_alt = nullptr;
-  if (opt.attention_mode != LINMT_ATT_GLOBAL_DOT) {
+  const float* u_alt = (opt.attention_mode == LINMT_ATT_GLOBAL_DOT) ? s.h_cur[L - 1] : nullptr;
+  if (att_merge_) {
+    // ... | W_c2 h: the half of the attention output's pre-activation that needs h_top only (global dot
+    // attention uses no projection, so only those rows run)
+    const int n0 = (opt.attention_mode == LINMT_ATT_GLOBAL_DOT) ? 2 * Hp : 0;
+    tc::Planes w = m.p_att_proj_w;
+    for (int p = 0; p < 3; ++p) if (w.p[p]) w.p[p] += (size_t)n0 * w.ld;
+    tc::TcEpiF32 e{nullptr, s.proj + n0, 3 * Hp, n0 ? 0 : Hp};
+    int rc = tc_gemm(ts.panel_top, Hp, R, w, rows, 3 * Hp - n0, Hp, e);
+    if (rc) return rc;
+  } else if (opt.attention_mode != LINMT_ATT_GLOBAL_DOT) {
     tc::TcEpiF32 e{nullptr, s.proj, 2 * Hp, Hp};
     int rc = tc_gemm(ts.panel_top, Hp, R, m.p_att_proj_w, rows, 2 * Hp, Hp, e);
     if (rc) return rc;
-  } else {
-    u_alt = s.h_cur[L - 1];
   }
   // 4. scores, softmax x Gaussian, context (written into the attention-output panel)
   {
-    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * win : nullptr;
+    float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * rec_win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
-    const size_t smem = sizeof(float) * (win + 8);
-    CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, 2 * Hp, u_alt, Hp, (const float*)m.vp,
-                    (const float*)s.hs, (const int32_t*)d_len_, (float*)nullptr, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
-                    (int)opt.attention_d, win, ra, rl, rv, ts.panel_top, nt_));
-    LAUNCHED();
+    if (int rc = launch_attention(mi, t, rows, u_alt, nullptr, ts.panel_top, nt_, ra, rl, rv)) return rc;
   }
   // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)
   {
     tc::TcEpiBiasTanh e{m.att_bout, ts.panel_ht, 0, nt_};
-    int rc = tc_gemm(ts.panel_top, 0, R, m.p_att_out_w, rows, Hp, 2 * Hp, e);
+    int rc;
+    if (att_merge_) {
+      // W_c1 ctx over the first Hp of the K columns; W_c2 h comes in as a precomputed row
+      e.add = s.proj + 2 * Hp; e.ld_add = 3 * Hp;
+      rc = tc_gemm(ts.panel_top, 0, R, m.p_att_out_w, rows, Hp, Hp, e);
+    } else {
+      rc = tc_gemm(ts.panel_top, 0, R, m.p_att_out_w, rows, Hp, 2 * Hp, e);
+    }
     if (rc) return rc;
   }
   // 6. logits

@@ -58,12 +58,16 @@ struct SentenceConfig {
   int longest_sentence;  // user value + 4 (src/decoder_sentence.cu:126)
   int print_align_scores;
   int model_cache;       // 1 = keep / use a binary copy of the weights next to a text model
+  std::vector<int32_t> devices;   // --devices: GPUs that each hold a replica and share the sentences (empty: opt.device)
 };
 
 // DecoderSentence::GeneralSettings, src/decoder_sentence.cu:110-264.  Like the reference,
 // --decoding-ratio is parsed as two INTEGERS (atoi/stoi, :224-225) and --penalty is not
 // read in sentence mode.  Keys beyond the reference's: --precision, --attention-type,
-// --ensemble-mode, --batch-size, --device, --max-src-len, --gemm-path.
+// --ensemble-mode, --batch-size, --device, --devices, --max-src-len, --gemm-path.  --devices "0 1 ..." puts a
+// replica of the model(s) on every listed GPU and deals the sentences of a file (or of a batch call) to them.
+// The reference's --multi-gpu (one GPU index per ensemble member, src/decoder_sentence.cu:183-198) is read
+// as the same list without repeats: here every member lives on every listed GPU.
 bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceConfig& c, std::string& err) {
   linmt_default_options(&c.opt);
   auto get = [&](const char* key) -> const std::string* {
@@ -123,6 +127,15 @@ bool sentence_settings(const std::map<std::string, std::string>& kv, SentenceCon
   }
   if (auto v = get("--batch-size")) c.opt.max_batch = std::atoi(v->c_str());
   if (auto v = get("--device")) c.opt.device = std::atoi(v->c_str());
+  for (const char* key : {"--devices", "--multi-gpu"})
+    if (auto v = get(key)) {
+      c.devices.clear();
+      for (const std::string& w : split_ws(*v)) {
+        const int32_t d = std::atoi(w.c_str());
+        if (std::find(c.devices.begin(), c.devices.end(), d) == c.devices.end()) c.devices.push_back(d);
+      }
+      break;
+    }
   if (auto v = get("--max-src-len")) c.opt.max_src_len = std::atoi(v->c_str());
   // the sentence API decodes one sentence per call unless told otherwise
   if (!get("--batch-size")) c.opt.max_batch = 1;
@@ -396,11 +409,19 @@ int linmt_create(const char* config_path, linmt_engine** out) {
   std::vector<const float*> blobs;
   for (auto& m : mfs) blobs.push_back(m.blob.data());
   linmt_engine* e = nullptr;
-  int rc = linmt_create_from_weights(&mfs[0].desc, blobs.data(), (int)blobs.size(), mfs[0].blob.size(), &sc.opt, &e);
+  int rc = linmt_create_from_weights_on(&mfs[0].desc, blobs.data(), (int)blobs.size(), mfs[0].blob.size(), &sc.opt,
+                                        sc.devices.data(), (int32_t)sc.devices.size(), &e);
   if (rc != LINMT_OK) { g_front_error = linmt_last_error(nullptr); return rc; }
   e->eng.tgt_words = mfs[0].tgt_words;
   e->eng.src_words_sorted = mfs[0].src_words;
   std::sort(e->eng.src_words_sorted.begin(), e->eng.src_words_sorted.end());
+  // Unknown words read the id of the source map's "UNK" entry; looking that key up in the reference's map
+  // inserts id 0 when the model has no such word (src/decoder_sentence.cu:61-62).
+  e->eng.src_unk_id = 0;
+  {
+    auto it = std::lower_bound(e->eng.src_words_sorted.begin(), e->eng.src_words_sorted.end(), std::make_pair(std::string("UNK"), INT32_MIN));
+    if (it != e->eng.src_words_sorted.end() && it->first == "UNK") e->eng.src_unk_id = it->second;
+  }
   e->eng.longest_sentence = sc.longest_sentence;
   e->eng.print_align_scores = sc.print_align_scores;
   *out = e;
@@ -439,7 +460,7 @@ const char* linmt_translate(linmt_engine* h, const char* sentence) {
     while (iss >> w) {
       auto it = std::lower_bound(e.src_words_sorted.begin(), e.src_words_sorted.end(), std::make_pair(w, INT32_MIN));
       if (it != e.src_words_sorted.end() && it->first == w) ids.push_back(it->second);
-      else ids.push_back(0);  // unknown words read id 0 = <UNK> (src/decoder_sentence.cu:61-62)
+      else ids.push_back(e.src_unk_id);  // src/decoder_sentence.cu:61-62
     }
   }
   if (ids.empty()) return e.result_buf.c_str();
@@ -487,7 +508,7 @@ int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path
     std::string w;
     while (iss >> w) {
       auto it = std::lower_bound(e.src_words_sorted.begin(), e.src_words_sorted.end(), std::make_pair(w, INT32_MIN));
-      ids.push_back((it != e.src_words_sorted.end() && it->first == w) ? it->second : 0);
+      ids.push_back((it != e.src_words_sorted.end() && it->first == w) ? it->second : e.src_unk_id);
     }
     if ((int)ids.size() > e.opt.max_src_len) ids.clear();
     sents.push_back(std::move(ids));
@@ -504,7 +525,12 @@ int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path
   const int nb = e.opt.nbest, B = e.opt.max_batch;
   const bool info = e.opt.print_info != 0;
   const bool want_align = info && e.print_align_scores;
-  for (size_t b0 = 0; b0 < order.size(); b0 += B) {
+  // one job per device batch; with several devices each device's host thread takes the next batch when it is
+  // free (the batches are in descending step count, so the long ones go first)
+  std::vector<int> batch_ids;
+  for (size_t b0 = 0; b0 < order.size(); b0 += B) batch_ids.push_back((int)(b0 / B));
+  const int rc_all = run_on_engines(h, batch_ids, [&](Engine& g, int bi) -> int {
+    const size_t b0 = (size_t)bi * B;
     const int n = (int)std::min<size_t>(B, order.size() - b0);
     std::vector<int32_t> ids, off(1, 0), steps;
     int Tm = 0;
@@ -519,7 +545,7 @@ int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path
     std::vector<int32_t> tok((size_t)n * nb * max_len), len((size_t)n * nb), vit((size_t)n * nb * max_len, -1);
     std::vector<float> score((size_t)n * nb), align;
     if (want_align) align.resize((size_t)n * nb * max_len * e.opt.max_src_len);
-    int rc = e.decode_host(ids.data(), off.data(), n, steps.data(), max_len, tok.data(), len.data(), score.data(), vit.data(),
+    int rc = g.decode_host(ids.data(), off.data(), n, steps.data(), max_len, tok.data(), len.data(), score.data(), vit.data(),
                            want_align ? align.data() : nullptr, nullptr);
     if (rc != LINMT_OK) return rc;
     for (int i = 0; i < n; ++i) {
@@ -537,7 +563,9 @@ int linmt_decode_file(linmt_engine* h, const char* in_path, const char* out_path
       if (nb != 1) out += "================\n";
       results[order[b0 + i]] = out;
     }
-  }
+    return LINMT_OK;
+  });
+  if (rc_all != LINMT_OK) return rc_all;
   std::ofstream outf(out_path);
   if (!outf) { e.err = std::string("can not open ") + out_path; return LINMT_EIO; }
   for (int i = 0; i < n_all; ++i) {

@@ -492,11 +492,13 @@ struct TcEpiLstm {
   }
 };
 
-// out = tanh(acc + bias) as bf16 planes (the attentional state).
+// out = tanh(acc [+ add] + bias) as bf16 planes (the attentional state).  `add` is an optional fp32 term per
+// element, add[row * ld_add + col]: the part of the pre-activation that was computed ahead of this product.
 struct TcEpiBiasTanh {
   const float* bias;
   Planes out; int col_off;
   int nt;
+  const float* add = nullptr; int ld_add = 0;
   static constexpr bool kHasBlock = false;
   static constexpr bool kHasPmax = false;
   __device__ __forceinline__ void block(int, int, int, int, int, float (*)[16], float*, int) const {}
@@ -505,8 +507,12 @@ struct TcEpiBiasTanh {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
-      split_store4(out, nt, idx + 4 * q, tanh_fast(v[4 * q] + b.x), tanh_fast(v[4 * q + 1] + b.y),
-                   tanh_fast(v[4 * q + 2] + b.z), tanh_fast(v[4 * q + 3] + b.w));
+      float4 a = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      if (add) {
+        const float4 g = *reinterpret_cast<const float4*>(add + (size_t)row * ld_add + col0 + 4 * q);
+        a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
+      }
+      split_store4(out, nt, idx + 4 * q, tanh_fast(a.x + b.x), tanh_fast(a.y + b.y), tanh_fast(a.z + b.z), tanh_fast(a.w + b.w));
     }
   }
 };
@@ -651,20 +657,6 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
   return true;
 }
 
-// Phase timestamps for tuning builds only (-DLINMT_TC_PROF): slot s of CTA c at g_tc_prof[c * 8 + s].
-#ifdef LINMT_TC_PROF
-__device__ unsigned long long* g_tc_prof = nullptr;
-__device__ __forceinline__ void tc_prof(int slot) {
-  if (g_tc_prof) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_tc_prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
-  }
-}
-#define TC_PROF(slot) tc_prof(slot)
-#else
-#define TC_PROF(slot) ((void)0)
-#endif
 
 // ---- kernel -------------------------------------------------------------------------------
 template <int NT, int BKT, int FMT, class Epi>
@@ -698,7 +690,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   const int ndrain = (nkb + kDrainEvery - 1) / kDrainEvery;
 
   if (threadIdx.x == 0) {
-    TC_PROF(0);
     s_abort = 0;
     // with split operands two threads issue MMAs: a stage is free, and the tile complete, when both have committed
     for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), NP > 1 ? 2 : 1); }
@@ -713,7 +704,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
-  if (threadIdx.x == 0) TC_PROF(1);
 
   if (warp == 0) {
     // Producer.  A TMA instruction costs its issuing thread ~150 ns whatever the box size
@@ -757,7 +747,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(fb, ph, &s_abort)) break;
         tc_fence_after();
-        if (kb == 0) TC_PROF(2);
         const uint64_t a0 = make_desc<BKT>(st);                        // plane 0 of A, k-step 0
         const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);         // plane 0 of B, k-step 0
         if (NP == 1) {
@@ -784,7 +773,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
         st += STAGE_BYTES; fb += 8u; eb += 8u;
         if (++s == STAGES) { s = 0; ph ^= 1u; st = base; fb = bars; eb = bars + 8u * STAGES; }
       }
-      TC_PROF(3);
       umma_commit(accum_bar);
     }
   } else if (warp == kIssue2Warp) {
@@ -898,7 +886,6 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       }
       if (ok && mbar_wait(accum_bar, 0, &s_abort)) {
         tc_fence_after();
-        if (threadIdx.x == 64) TC_PROF(4);
 #pragma unroll
         for (int ci = 0; ci < kChunks; ++ci) {
           if (ci < nmine) {
@@ -912,12 +899,10 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
       }
     }
   }
-  if (threadIdx.x == 64) TC_PROF(5);
   if (splits > 1) __threadfence();  // partial sums visible before this CTA takes its ticket
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_acc, TMEM_COLS);
-  if (threadIdx.x == 0) TC_PROF(6);
   if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
   if (splits > 1) {
     // The CTA that arrives last at this tile sums the partial tiles in split order (a fixed
@@ -1189,15 +1174,28 @@ inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A kernel's opt-in to more than 48 KB of dynamic shared memory is an attribute of the kernel ON ONE DEVICE:
+// it is set once per (kernel, device), for the device that is current at the launch.
+constexpr int kMaxDevices = 64;
+template <class Kernel>
+inline cudaError_t ensure_smem_optin(Kernel* kernel, bool* done_per_device) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!done_per_device[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    if (e != cudaSuccess) return e;
+    done_per_device[dev] = true;
+  }
+  return cudaSuccess;
+}
+
 template <int NT, int BKT, int FMT, class Epi>
 inline cudaError_t launch_gemm_tc_nt(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
                                      cudaStream_t st, float* ws, int* counters) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, BKT, FMT, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
-    if (e != cudaSuccess) return e;
-    attr_done = true;
-  }
+  static bool optin_done[kMaxDevices] = {};
+  if (cudaError_t e = ensure_smem_optin(gemm_tc_kernel<NT, BKT, FMT, Epi>, optin_done); e != cudaSuccess) return e;
   const int splits = (sh.splits > 1 && ws && counters) ? sh.splits : 1;
   dim3 grid((M + BM - 1) / BM, (N + sh.bn - 1) / sh.bn, splits);
   int drain = (sh.drain > 0 ? sh.drain : kDrainDefault) * 32 / BKT;
@@ -1249,13 +1247,8 @@ inline cudaError_t launch_gemm_tc_persist(const TmapSet& tm, int M, int N, int K
   const int stride = sh.nt == 1 ? kPersistStageStride : 0;
 #define LINMT_PERSIST_CASE(NTV, BKV, FMTV)                                                                                   \
   {                                                                                                                          \
-    static bool done = false;                                                                                                \
-    if (!done) {                                                                                                             \
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_persist_kernel<NTV, BKV, FMTV, Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           SMEM_BUDGET + 1280);                                                              \
-      if (e != cudaSuccess) return e;                                                                                        \
-      done = true;                                                                                                           \
-    }                                                                                                                        \
+    static bool optin_done[kMaxDevices] = {};                                                                                \
+    if (cudaError_t e = ensure_smem_optin(gemm_tc_persist_kernel<NTV, BKV, FMTV, Epi>, optin_done); e != cudaSuccess) return e; \
     return launch_k(sh.pdl != 0, gemm_tc_persist_kernel<NTV, BKV, FMTV, Epi>, grid, dim3(kThreads), (size_t)sh.smem_bytes, st, tm, M, N, K, \
                     sh.bn, sh.stages, epi, err_flag, stride);                                                                \
   }

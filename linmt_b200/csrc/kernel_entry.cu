@@ -108,68 +108,4 @@ int linmt_k_softmax_topk(const float* logits, int32_t R, int32_t V, int32_t kk, 
   return LINMT_OK;
 }
 
-
-// Timing of the tensor-core GEMM alone on device-resident operands (tuning aid): returns the
-// average milliseconds of `iters` launches of an R x N x K problem with tile width bn (0 = the
-// engine's own choice), nt planes and at most max_stages shared-memory stages (0 = all that fit).
-int linmt_k_gemm_time(int32_t R, int32_t K, int32_t N, int32_t bn, int32_t nt, int32_t max_stages, int32_t iters,
-                      float* ms_out, int32_t device) {
-  int drain = 0, force_splits = 0, bk = 32;
-  if (bn >= 1000) { bk = 64; bn -= 1000; }  // tuning: bn + 1000 = 128-byte rows
-  if (max_stages >= 10000) { force_splits = max_stages / 10000; max_stages %= 10000; }  // tuning: splits * 10000
-  if (max_stages >= 100) { drain = max_stages / 100; max_stages %= 100; }                 // + drain * 100 + stages
-  using namespace linmt;
-  int fmt = 0;
-  if (nt == tc::kF16PairCode) { fmt = 1; nt = 2; }   // nt = 4: the f16 pair format
-  if (R < 1 || K < 32 || N < 16 || nt < 1 || nt > 3 || iters < 1 || !ms_out) return LINMT_EINVAL;
-  if (K % 32 || N % 16) return LINMT_EINVAL;
-  KCK(cudaSetDevice(device));
-  int splits = 1;
-  const size_t ws_floats = (size_t)16 << 20;
-  if (bn <= 0) tc::pick_shape(R, N, K, nt, 148, ws_floats, 4096, &bn, &splits, fmt);
-  if (bn % 16 || bn > 256) return LINMT_EINVAL;
-  DevBuf pa[3], pb[3], dy, derr;
-  tc::Planes A{}, B{};
-  A.ld = K; B.ld = K; A.fmt = fmt; B.fmt = fmt;
-  for (int t = 0; t < nt; ++t) {
-    KCK(pa[t].alloc((size_t)R * K * 2)); KCK(pb[t].alloc((size_t)N * K * 2));
-    KCK(cudaMemset(pa[t].p, 0x3c, (size_t)R * K * 2)); KCK(cudaMemset(pb[t].p, 0x3c, (size_t)N * K * 2));
-    A.p[t] = pa[t].as<__nv_bfloat16>(); B.p[t] = pb[t].as<__nv_bfloat16>();
-  }
-  KCK(dy.alloc((size_t)R * N * 4)); KCK(derr.alloc(4)); KCK(cudaMemset(derr.p, 0, 4));
-  DevBuf dws, dcnt;
-  KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
-  tc::TmapSet tm{};
-  for (int t = 0; t < nt; ++t) {
-    if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM, bk)) return LINMT_ECUDA;
-    if (!tc::make_tmap(&tm.b[t], B.p[t], N, K, K, bn, bk)) return LINMT_ECUDA;
-  }
-  tc::Shape sh = tc::make_shape(bn, nt, bk, fmt);
-  if (max_stages > 0 && sh.stages > max_stages) { sh.stages = max_stages; sh.smem_bytes = tc::shape_smem_bytes(sh.stages, sh.stage_bytes); }
-  if (drain > 0) sh.drain = drain;
-  sh.splits = force_splits > 0 ? force_splits : splits;
-  {
-    // a forced split must fit the workspace and the tile counters, as the engine's own choice does
-    const size_t mt = (size_t)((R + tc::BM - 1) / tc::BM), ntile = (size_t)((N + bn - 1) / bn);
-    if (sh.splits > 1 && ((size_t)sh.splits * mt * tc::BM * (size_t)N > ws_floats || mt * ntile > 4096 || (K / bk) / sh.splits < 1))
-      return LINMT_ELIMIT;
-  }
-  tc::TcEpiF32 e{nullptr, dy.as<float>(), N, 0};
-  cudaEvent_t e0, e1;
-  KCK(cudaEventCreate(&e0)); KCK(cudaEventCreate(&e1));
-  for (int i = 0; i < 2; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>()));
-  KCK(cudaEventRecord(e0, 0));
-  for (int i = 0; i < iters; ++i) KCK(tc::launch_gemm_tc(tm, R, N, K, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>()));
-  KCK(cudaEventRecord(e1, 0));
-  KCK(cudaDeviceSynchronize());
-  float ms = 0.f;
-  KCK(cudaEventElapsedTime(&ms, e0, e1));
-  cudaEventDestroy(e0); cudaEventDestroy(e1);
-  int herr = 0;
-  KCK(cudaMemcpy(&herr, derr.p, 4, cudaMemcpyDeviceToHost));
-  if (herr) return LINMT_ECUDA;
-  *ms_out = ms / iters;
-  return LINMT_OK;
-}
-
 }  // extern "C"

@@ -30,20 +30,26 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 constexpr int kMaxDevices = 64;
 unsigned char* g_scratch_addr[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
 std::mutex g_setup_mutex;
 
-// Device address of the scratch array on `device` (which must be current).  The first call on a
-// device asks the runtime for it and checks the answer; later calls reuse it.
-cudaError_t scratch_address(int device, unsigned char** out) {
+// Device address of the scratch array on `device` (which must be current) and the device's SM count.  The
+// first call on a device asks the runtime for both and checks the answers; later calls reuse them.
+cudaError_t scratch_address(int device, unsigned char** out, int* n_sm) {
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_addr[device]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_scratch);
     if (e != cudaSuccess) return e;
     if (!p) return cudaErrorInvalidSymbol;
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return e;
+    g_sm_count[device] = sms > 0 ? sms : 1;
     g_scratch_addr[device] = static_cast<unsigned char*>(p);
   }
   *out = g_scratch_addr[device];
+  *n_sm = g_sm_count[device];
   return cudaSuccess;
 }
 
@@ -58,7 +64,8 @@ extern "C" int linmt_gemm_f32_noalloc(const float* d_x, const float* d_wt, float
   if (K % tc::BK != 0 || N % 16 != 0) return LINMT_EINVAL;        // no room to pad without allocating
   if (cudaSetDevice(device) != cudaSuccess) return LINMT_ECUDA;
   unsigned char* scratch = nullptr;
-  if (scratch_address(device, &scratch) != cudaSuccess) return LINMT_ECUDA;
+  int n_sm = 1;
+  if (scratch_address(device, &scratch, &n_sm) != cudaSuccess) return LINMT_ECUDA;
 
   int* d_err = reinterpret_cast<int*>(scratch + kFlagOffset);
   tc::Planes A{}, B{};
@@ -72,7 +79,7 @@ extern "C" int linmt_gemm_f32_noalloc(const float* d_x, const float* d_wt, float
   tc::split_planes_kernel<<<128, 256>>>(d_x, A, 3, (size_t)R * K);
   tc::split_planes_kernel<<<256, 256>>>(d_wt, B, 3, (size_t)N * K);
   if (cudaGetLastError() != cudaSuccess) return LINMT_ECUDA;
-  const int bn = tc::pick_bn(R, N, 148);
+  const int bn = tc::pick_bn(R, N, n_sm);
   tc::TmapSet tm{};
   for (int t = 0; t < 3; ++t) {
     if (!tc::make_tmap(&tm.a[t], A.p[t], R, K, K, tc::BM)) return LINMT_ECUDA;

@@ -147,16 +147,30 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   proj [rows][2*Hp]: tanh(W_p h) | W_a^T h      (global_dot: `u` = h_top itself)
 //   hs   [B][max_src][Hp]: top encoder state after consuming reversed position p
 //   ctx  [rows][Hp] fp32 and/or ctx_planes (bf16 planes, columns [0,Hp) of the panel)
-//   rec_align [rows][win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
+//   rec_align [rows][rec_win] / rec_lo [rows] / rec_vit [rows]: alignment record of this step
 //   (may be null).  win = 2D+1 for local attention, max_src for the global modes.
+//   ens = 0: one model; the record is the window (rec_win = win) and its first position rec_lo.
+//   ens = 1, 2, 3: first / middle / last member of an ensemble; the record is dense over the source
+//   (rec_win = max_src, rec_lo = 0), the first member writes it, the others add to it in member order,
+//   and the last one takes the vote: the position of the largest summed score, the search starting from
+//   "none, 0" (EnsembleFactory::EnsemblesModels, src/decoder.h:1934-1964).
 // grid = rows, block = 256, dynamic smem = (win + 8) floats.  (Keeping the window's states in shared
 // memory between the score sweep and the context sweep was tried: 86 KB per CTA costs the occupancy that
 // the halved L2 traffic buys, no change in the decode time.)
+// Optional record of the attention centre p_t of every row of a forward (local attention): the parity tests
+// use it to tell a window that was cut on the other side of an integer apart from an error.
+struct AttTrace {
+  float* pt;            // [n][T1][k] by the caller's sentence index, or null
+  const int32_t* orig;  // batch slot -> caller's sentence index
+  int T1;               // forwards per sentence in the record (longest step count + 1)
+  int t;                // this forward
+};
 static __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
-                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt) {
+                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt,
+                                 int rec_win, int ens, AttTrace at) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   extern __shared__ float sm[];
@@ -181,6 +195,7 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
       s_pt = pt;
       s_lo = (0 > (int)pt - D) ? 0 : ((int)pt - D);                       // LowerUpperKernel, :1094-1100
       s_hi = ((S - 1) < (int)pt + D) ? (S - 1) : ((int)pt + D);
+      if (at.pt) at.pt[((size_t)at.orig[sent] * at.T1 + at.t) * k + (r - sent * k)] = pt;
     }
   } else if (threadIdx.x == 0) {
     s_pt = 0.f; s_lo = 0; s_hi = S - 1;
@@ -231,11 +246,35 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
       const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
       if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
     }
-    if (lane == 0 && rec_lo) { rec_lo[r] = lo; rec_vit[r] = (best > 0.f) ? besti : -1; }
+    if (lane == 0 && rec_lo && ens == 0) { rec_lo[r] = lo; rec_vit[r] = (best > 0.f) ? besti : -1; }
   }
   __syncthreads();
-  if (rec_align)
-    for (int w = threadIdx.x; w < win; w += blockDim.x) rec_align[(size_t)r * win + w] = (w < W) ? e[w] : 0.f;
+  if (rec_align && ens == 0)
+    for (int w = threadIdx.x; w < rec_win; w += blockDim.x) rec_align[(size_t)r * rec_win + w] = (w < W) ? e[w] : 0.f;
+  if (rec_align && ens != 0) {
+    float* row = rec_align + (size_t)r * rec_win;
+    for (int sp = threadIdx.x; sp < rec_win; sp += blockDim.x) {
+      const float a = (sp >= lo && sp <= hi) ? e[sp - lo] : 0.f;
+      row[sp] = (ens == 1) ? (0.f + a) : (row[sp] + a);
+    }
+    if (ens == 3) {
+      __syncthreads();
+      if (warp == 0) {
+        float best = 0.f; int besti = 0x7fffffff;
+        for (int sp = lane; sp < rec_win; sp += 32) {
+          const float a = row[sp];
+          if (a > best) { best = a; besti = sp; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+          if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+        }
+        if (lane == 0) { rec_lo[r] = 0; rec_vit[r] = (best > 0.f) ? besti : -1; }
+      }
+    }
+  }
   // context: CreateCTKernel, deep_rnn_kernel.h:1250-1260 (sum over window positions in order)
   float* crow = ctx ? ctx + (size_t)r * Hp : nullptr;
   for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
@@ -249,6 +288,195 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
     if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
       const size_t idx = (size_t)r * ctx_planes.ld + j;
       tc::split_store4(ctx_planes, nt, idx, acc.x, acc.y, acc.z, acc.w);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The same attention for a GROUP of beams of one sentence per CTA.  The k beams of a sentence attend
+// over the same encoder states, so a CTA that serves several of them reads every state row once per
+// pass for all of them (attention_kernel reads the window of every row on its own: k times the L2
+// traffic).  Every sum is formed in the same order as in attention_kernel -- the same lane-strided FMA
+// chains, the same shuffle trees, the same position order in the context -- so the two kernels return
+// the same bits.
+//   grid = (active sentences, groups), block = 256; beams [g * bpc, min(k, (g+1) * bpc)) belong to group g,
+//   bpc <= kAttBeams.  dynamic smem = bpc * (Hp + win + 16) floats.
+constexpr int kAttBeams = 6;
+static __global__ void __launch_bounds__(256) attention_group_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+                                 const float* __restrict__ vp, const float* __restrict__ hs,
+                                 const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
+                                 int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
+                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt,
+                                 int rec_win, int ens, int bpc, AttTrace at) {
+  tc::pdl_launch_dependents();
+  tc::pdl_wait();
+  extern __shared__ float sm[];
+  float* su = sm;                          // [bpc][Hp]   the beams' query vectors
+  float* se = su + (size_t)bpc * Hp;       // [bpc][win]  scores, then alignments
+  float* sred = se + (size_t)bpc * win;    // [bpc][8]    per-warp partial sums
+  __shared__ float s_pt[kAttBeams];
+  __shared__ int s_lo[kAttBeams], s_hi[kAttBeams];
+  const int sent = blockIdx.x;
+  const int b0 = blockIdx.y * bpc;
+  const int nb = (k - b0) < bpc ? (k - b0) : bpc;
+  if (nb <= 0) return;
+  const int S = src_len[sent];
+  const int r0 = sent * k + b0;
+  const float* hsb = hs + (size_t)sent * max_src * Hp;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  for (int i = tid; i < nb * (Hp / 4); i += 256) {
+    const int b = i / (Hp / 4), j = (i - b * (Hp / 4)) * 4;
+    const float* u = u_alt ? (u_alt + (size_t)(r0 + b) * ldu) : (proj + (size_t)(r0 + b) * ldp + Hp);
+    *reinterpret_cast<float4*>(su + (size_t)b * Hp + j) = *reinterpret_cast<const float4*>(u + j);
+  }
+  if (mode == 0) {
+    float part[kAttBeams];
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) part[b] = 0.f;
+    for (int j = tid; j < H; j += 256) {
+      const float v = vp[j];
+#pragma unroll
+      for (int b = 0; b < kAttBeams; ++b)
+        if (b < nb) part[b] = fmaf(v, proj[(size_t)(r0 + b) * ldp + j], part[b]);
+    }
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part[b] += __shfl_xor_sync(0xffffffffu, part[b], o);
+      if (lane == 0 && b < nb) sred[b * 8 + warp] = part[b];
+    }
+    __syncthreads();
+    if (tid < nb) {
+      float dot = 0.f;
+      for (int i = 0; i < 8; ++i) dot += sred[tid * 8 + i];
+      const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)dot)));  // SigmoidKernel, deep_rnn_kernel.h:1075-1080
+      const float pt = (float)S * sg;
+      s_pt[tid] = pt;
+      s_lo[tid] = (0 > (int)pt - D) ? 0 : ((int)pt - D);                  // LowerUpperKernel, :1094-1100
+      s_hi[tid] = ((S - 1) < (int)pt + D) ? (S - 1) : ((int)pt + D);
+      if (at.pt) at.pt[((size_t)at.orig[sent] * at.T1 + at.t) * k + b0 + tid] = pt;
+    }
+  } else if (tid < nb) {
+    s_pt[tid] = 0.f; s_lo[tid] = 0; s_hi[tid] = S - 1;
+  }
+  __syncthreads();
+  int lo_min = 0x7fffffff, hi_max = -1;
+  for (int b = 0; b < nb; ++b) { lo_min = min(lo_min, s_lo[b]); hi_max = max(hi_max, s_hi[b]); }
+  // scores: a warp per source position, the row's dot product with every beam whose window holds it
+  for (int sp = lo_min + warp; sp <= hi_max; sp += 8) {
+    const float* hrow = hsb + (size_t)(S - 1 - sp) * Hp;
+    float acc[kAttBeams];
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) acc[b] = 0.f;
+    for (int j = lane * 4; j < Hp; j += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(hrow + j);
+#pragma unroll
+      for (int b = 0; b < kAttBeams; ++b) {
+        if (b < nb) {
+          const float4 q = *reinterpret_cast<const float4*>(su + (size_t)b * Hp + j);
+          acc[b] = fmaf(a.x, q.x, acc[b]); acc[b] = fmaf(a.y, q.y, acc[b]); acc[b] = fmaf(a.z, q.z, acc[b]); acc[b] = fmaf(a.w, q.w, acc[b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], o);
+      if (lane == 0 && b < nb && sp >= s_lo[b] && sp <= s_hi[b]) se[(size_t)b * win + (sp - s_lo[b])] = acc[b];
+    }
+  }
+  __syncthreads();
+  // AlignmentReductionKernel (deep_rnn_kernel.h:1197-1241) per beam: one warp each
+  for (int b = warp; b < nb; b += 8) {
+    float* e = se + (size_t)b * win;
+    const int lo = s_lo[b], W = s_hi[b] - lo + 1;
+    const int r = r0 + b;
+    float mx = 0.f;
+    for (int w = lane; w < W; w += 32) mx = fmaxf(mx, e[w]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int w = lane; w < W; w += 32) { const float ev = expf(e[w] - mx); e[w] = ev; sum += ev; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float sigma_sq = ((float)D * (float)D) / 4.0f;
+    const float pt = s_pt[b];
+    float best = 0.f; int besti = 0x7fffffff;
+    for (int w = lane; w < W; w += 32) {
+      float a = e[w];
+      if (mode == 0) {
+        const float tmp = expf((-1 * powf(pt - (float)(lo + w), 2.0f)) / (2 * sigma_sq));
+        if (0 != sum) a = (a / sum) * tmp;
+      } else if (0 != sum) a = a / sum;
+      e[w] = a;
+      if (a > best) { best = a; besti = lo + w; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0 && rec_lo && ens == 0) { rec_lo[r] = lo; rec_vit[r] = (best > 0.f) ? besti : -1; }
+  }
+  __syncthreads();
+  if (rec_align) {
+    for (int b = 0; b < nb; ++b) {
+      const float* e = se + (size_t)b * win;
+      const int lo = s_lo[b], hi = s_hi[b], W = hi - lo + 1;
+      float* row = rec_align + (size_t)(r0 + b) * rec_win;
+      if (ens == 0) {
+        for (int w = tid; w < rec_win; w += 256) row[w] = (w < W) ? e[w] : 0.f;
+      } else {
+        for (int sp = tid; sp < rec_win; sp += 256) {
+          const float a = (sp >= lo && sp <= hi) ? e[sp - lo] : 0.f;
+          row[sp] = (ens == 1) ? (0.f + a) : (row[sp] + a);
+        }
+      }
+    }
+    if (ens == 3) {
+      __syncthreads();
+      for (int b = warp; b < nb; b += 8) {
+        const float* row = rec_align + (size_t)(r0 + b) * rec_win;
+        float best = 0.f; int besti = 0x7fffffff;
+        for (int sp = lane; sp < rec_win; sp += 32) {
+          const float a = row[sp];
+          if (a > best) { best = a; besti = sp; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+          if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+        }
+        if (lane == 0) { rec_lo[r0 + b] = 0; rec_vit[r0 + b] = (best > 0.f) ? besti : -1; }
+      }
+    }
+  }
+  // context (CreateCTKernel, deep_rnn_kernel.h:1250-1260): every state row of the union of the windows is
+  // loaded once and added, in position order, into the sums of the beams whose window holds it
+  for (int j = tid * 4; j < Hp; j += 1024) {
+    float4 acc[kAttBeams];
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) acc[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = lo_min; sp <= hi_max; ++sp) {
+      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - sp) * Hp + j);
+#pragma unroll
+      for (int b = 0; b < kAttBeams; ++b) {
+        if (b < nb && sp >= s_lo[b] && sp <= s_hi[b]) {
+          const float a = se[(size_t)b * win + (sp - s_lo[b])];
+          acc[b].x += a * h4.x; acc[b].y += a * h4.y; acc[b].z += a * h4.z; acc[b].w += a * h4.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kAttBeams; ++b) {
+      if (b < nb) {
+        const int r = r0 + b;
+        if (ctx) *reinterpret_cast<float4*>(ctx + (size_t)r * Hp + j) = acc[b];
+        if (ctx_planes.p[0]) tc::split_store4(ctx_planes, nt, (size_t)r * ctx_planes.ld + j, acc[b].x, acc[b].y, acc[b].z, acc[b].w);
+      }
     }
   }
 }
@@ -299,8 +527,10 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   __shared__ int s_ci[kTopkCap];
   __shared__ float s_red[8];
   __shared__ int s_redi[8];
+  __shared__ float s_cd[kTopkCap];   // refinement: change of exp(z - max) per candidate, in buffer order ...
+  __shared__ float s_co[kTopkCap];   // ... and in vocabulary order
   __shared__ int s_count;
-  __shared__ float s_tau, s_max, s_lse;
+  __shared__ float s_tau, s_max, s_lse, s_sum, s_eos, s_eos_delta;
   const int r = blockIdx.x, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const float* z = logits + (size_t)r * ld;
@@ -429,17 +659,57 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
   if (tid == 0) {
     float bs = 0.f;
     for (int w = 0; w < 8; ++w) bs += s_red[w];
+    s_sum = bs;
     s_lse = normalise ? logf(bs) : -rmax;   // normalise = 0: the row already holds log-probabilities
-    if (out.eos_logp && !rf.a0) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
-    if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
+    if (!rf.a0) {
+      if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
+      if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
+    }
   }
   __syncthreads();
-  const float rlse = s_lse;
-  const int n = s_count;
+  int n = s_count;
+  if (rf.a0 && n > kTopkCap) {
+    // More elements than the buffer holds reach the widened threshold (a nearly flat row): pick the kk best
+    // of the one-product logits by exact sweeps and make those the candidates.  Their values are refined
+    // like any others below; an element within the error bound just beyond the kk-th can be missed here,
+    // which on a row this flat is a tie within the tolerance.
+    float last_v = INFINITY;
+    int last_i = -1;
+    for (int round = 0; round < kk; ++round) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int i = tid; i < V; i += 256) {
+        const float v = z[i];
+        const bool after = (v < last_v) || (v == last_v && i > last_i);
+        if (after && better(v, i, bv, bi)) { bv = v; bi = i; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+      }
+      __syncthreads();
+      if (lane == 0) { s_red[warp] = bv; s_redi[warp] = bi; }
+      __syncthreads();
+      bv = s_red[0]; bi = s_redi[0];
+      for (int w = 1; w < 8; ++w) if (better(s_red[w], s_redi[w], bv, bi)) { bv = s_red[w]; bi = s_redi[w]; }
+      if (tid == 0) { s_cv[round] = bv; s_ci[round] = bi; }
+      last_v = bv; last_i = bi;
+    }
+    __syncthreads();
+    n = 0;
+    while (n < kk && s_ci[n] != 0x7fffffff) ++n;   // fewer than kk elements in the row
+    __syncthreads();
+    if (tid == 0) s_count = n;
+  }
   if (rf.a0) {
     // accurate values for the candidates (and for EOS, whose log-probability is always reported): one
-    // warp per candidate, fp32 FMAs over the two planes of both operands
-    const int nc = n <= kTopkCap ? n : 0;
+    // warp per candidate, fp32 FMAs over the two planes of both operands.  Each also yields the term by
+    // which the row's sum of exponentials changes when the accurate value replaces the one-product one:
+    // on a peaked row the few dominant logits ARE the normaliser, and their fp16-product error would
+    // otherwise go straight into every log-probability of the row.
+    const int nc = n;
     for (int c = warp; c <= nc; c += 8) {
       const int v = (c < nc) ? s_ci[c] : kEos;
       const __half* w0 = rf.b0 + (size_t)v * rf.ldb;
@@ -460,12 +730,35 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (lane == 0) {
         const float zv = acc + (rf.bias ? rf.bias[v] : 0.f);
-        if (c < nc) s_cv[c] = zv;
-        else if (out.eos_logp) out.eos_logp[r] = (zv - rmax) - rlse;
+        const float za = (c < nc) ? s_cv[c] : z[kEos];
+        const float delta = __expf(zv - rmax) - __expf(za - rmax);
+        if (c < nc) { s_cv[c] = zv; s_cd[c] = delta; }
+        else { s_eos = zv; s_eos_delta = delta; }
       }
     }
     __syncthreads();
+    // the correction is summed in vocabulary order, so the result does not depend on the order in which
+    // the candidates happened to enter the buffer
+    bool eos_listed = false;
+    for (int c = tid; c < nc; c += 256) {
+      const int i = s_ci[c];
+      int pos = 0;
+      for (int d = 0; d < nc; ++d) pos += (s_ci[d] < i) ? 1 : 0;
+      s_co[pos] = s_cd[c];
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float corr = 0.f;
+      for (int c = 0; c < nc; ++c) { corr += s_co[c]; eos_listed = eos_listed || (s_ci[c] == kEos); }
+      if (!eos_listed) corr += s_eos_delta;
+      const float bs = s_sum + corr;
+      s_lse = normalise ? logf(bs > 0.f ? bs : s_sum) : -rmax;
+      if (out.eos_logp) out.eos_logp[r] = (s_eos - rmax) - s_lse;
+      if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
+    }
+    __syncthreads();
   }
+  const float rlse = s_lse;
   if (n <= kTopkCap) {
     // exact ranking of the candidates: value descending, index ascending
     for (int c = tid; c < n; c += 256) {
@@ -599,8 +892,10 @@ struct TraceDev {
   int32_t* cand_tok; float* cand_logp; int32_t* surv_tok; int32_t* surv_parent; float* surv_score; float* final_logp;
   const int32_t* force_tok; const int32_t* force_parent; const float* force_score;
   int Tm;
+  float* pt;                 // [n][Tm+1][k] attention centre of every forward (member 0), or null
   float* gold_logp;          // [n][Tm][k] log-probability of the forced token of every slot (scoring)
   const float* logits; int ld_logits; const float* row_stats;   // what gold_logp is computed from
+  TopkRefine rf;             // set when the logits are one-product values: the forced token's logit is recomputed accurately
 };
 // grid = active sentences, block = 256, dynamic smem = k*kk*24 + 8 bytes
 static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_logp,
@@ -695,6 +990,38 @@ static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, c
     for (; ns < k; ++ns) { s_ntok[ns] = kUnk; s_npar[ns] = 0; s_nscore[ns] = kDeadScore; }
     bs.fin_n[sent] = nf;
   }
+  // Scoring (force-decoding): log-probability of the forced token of every slot under its parent's row.
+  // With one-product logits the token's logit is recomputed from both planes of both operands, like the
+  // candidates in the softmax kernel; one warp per slot.
+  __shared__ float s_gold[kMaxBeam + 1];
+  if (tr.force_tok && tr.gold_logp && tr.logits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int b = warp; b < k; b += (int)(blockDim.x >> 5)) {
+      const size_t off = ((size_t)osent * tr.Tm + t) * k + b;
+      const int npar = tr.force_parent[off];
+      const int prow = r0 + (npar >= 0 && npar < k ? npar : 0);
+      const int gt = tr.force_tok[off] >= 0 ? tr.force_tok[off] : 0;
+      float zv = 0.f;
+      if (tr.rf.a0) {
+        const __half* a0 = tr.rf.a0 + (size_t)prow * tr.rf.lda;
+        const __half* a1 = tr.rf.a1 + (size_t)prow * tr.rf.lda;
+        const __half* w0 = tr.rf.b0 + (size_t)gt * tr.rf.ldb;
+        const __half* w1 = tr.rf.b1 + (size_t)gt * tr.rf.ldb;
+        float acc = 0.f;
+        for (int j = lane; j < tr.rf.K; j += 32) {
+          const float a = fmaf(__half2float(a1[j]), kPairInv, __half2float(a0[j]));
+          const float w = fmaf(__half2float(w1[j]), kPairInv, __half2float(w0[j]));
+          acc = fmaf(a, w, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        zv = acc + (tr.rf.bias ? tr.rf.bias[gt] : 0.f);
+      } else if (lane == 0) {
+        zv = tr.logits[(size_t)prow * tr.ld_logits + gt];
+      }
+      if (lane == 0) s_gold[b] = (zv - tr.row_stats[2 * prow]) - tr.row_stats[2 * prow + 1];
+    }
+  }
   __syncthreads();
   if (threadIdx.x < k) {
     const int b = threadIdx.x;
@@ -704,11 +1031,7 @@ static __global__ void __launch_bounds__(256) beam_select_kernel(BeamState bs, c
     if (tr.surv_tok) { tr.surv_tok[off] = ntok; tr.surv_parent[off] = npar; tr.surv_score[off] = nscore; }
     if (tr.force_tok) {
       ntok = tr.force_tok[off]; npar = tr.force_parent[off]; nscore = tr.force_score[off];
-      if (tr.gold_logp && tr.logits) {
-        const int prow = r0 + (npar >= 0 && npar < k ? npar : 0);
-        const int gt = ntok >= 0 ? ntok : 0;
-        tr.gold_logp[off] = (tr.logits[(size_t)prow * tr.ld_logits + gt] - tr.row_stats[2 * prow]) - tr.row_stats[2 * prow + 1];
-      }
+      if (tr.gold_logp && tr.logits) tr.gold_logp[off] = s_gold[b];
     }
     bs.tok[r0 + b] = ntok; bs.parent[r0 + b] = npar; bs.score[r0 + b] = nscore;
     bs.hist_tok[(size_t)t * bs.R + r0 + b] = ntok;

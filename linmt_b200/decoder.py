@@ -32,7 +32,10 @@ class Decoder:
 
     def __init__(self, desc, blobs, *, beam=12, nbest=1, attention="local_p_general", attention_d=10, print_info=0,
                  precision="fp32", ensemble="prob_mean", gemm_path="auto", max_batch=64, max_src_len=100,
-                 max_steps=200, device=0, penalty=0.0, diversity=0.0, lp_alpha=0.65, cp_beta=0.2, min_ratio=0.5):
+                 max_steps=200, device=0, devices=None, penalty=0.0, diversity=0.0, lp_alpha=0.65, cp_beta=0.2,
+                 min_ratio=0.5):
+        """``devices``: a list of GPU ordinals that each hold a replica and share the sentences of a
+        ``decode`` call (one host thread per GPU inside the library); default: the single ``device``."""
         lib = _lib.load()
         self._lib = lib
         o = _lib.OptionsC()
@@ -46,7 +49,9 @@ class Decoder:
         blobs = [np.ascontiguousarray(b, np.float32) for b in blobs]
         arr = (C.c_void_p * len(blobs))(*[b.ctypes.data for b in blobs])
         h = C.c_void_p()
-        rc = lib.linmt_create_from_weights(C.byref(d), arr, len(blobs), blobs[0].size, C.byref(o), C.byref(h))
+        devs = np.ascontiguousarray(devices if devices is not None else [], np.int32)
+        rc = lib.linmt_create_from_weights_on(C.byref(d), arr, len(blobs), blobs[0].size, C.byref(o),
+                                              _ptr(devs) if len(devs) else None, len(devs), C.byref(h))
         if rc != 0:
             raise LinmtError(f"linmt_create_from_weights failed ({rc}): {lib.linmt_last_error(None).decode()}")
         self._h = h
@@ -91,8 +96,9 @@ class Decoder:
                 out.update({"cand_tok": np.full((n, Tm, k, k + 1), -1, np.int32),
                             "cand_logp": np.zeros((n, Tm, k, k + 1), np.float32),
                             "surv_tok": np.full((n, Tm, k), -1, np.int32), "surv_parent": np.full((n, Tm, k), -1, np.int32),
-                            "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32)})
-                for f in ("cand_tok", "cand_logp", "surv_tok", "surv_parent", "surv_score", "final_logp"):
+                            "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32),
+                            "pt": np.zeros((n, Tm + 1, k), np.float32)})
+                for f in ("cand_tok", "cand_logp", "surv_tok", "surv_parent", "surv_score", "final_logp", "pt"):
                     setattr(tr, f, out[f].ctypes.data)
             if force is not None:
                 self._force = [np.ascontiguousarray(force["surv_tok"], np.int32),

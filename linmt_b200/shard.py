@@ -18,9 +18,10 @@ def batches_by_length(sents, batch: int) -> List[List[int]]:
 
 def partition(sents, world: int, batch: int) -> List[List[int]]:
     """Deals length-bucketed batches to ranks, heaviest first, always to the least loaded rank
-    (load = sum of decoder forwards T_i + 1)."""
+    (load of a batch = its longest sentence's decoder forwards, max T_i + 1, times its rows: a batch
+    runs as long as its longest member)."""
     bl = batches_by_length(sents, batch)
-    cost = [sum(int(sents.steps[i]) + 1 for i in b) * 0 + (max(int(sents.steps[i]) for i in b) + 1) * len(b) for b in bl]
+    cost = [(max(int(sents.steps[i]) for i in b) + 1) * len(b) for b in bl]
     load = [0] * world
     parts: List[List[int]] = [[] for _ in range(world)]
     for bi in sorted(range(len(bl)), key=lambda j: -cost[j]):

@@ -64,18 +64,38 @@ def blob_floats(d: ModelDesc) -> int:
     return sum(r * c for _, r, c in blob_layout(d))
 
 
-def make_blob(d: ModelDesc, seed: int, lo: float = -0.08, hi: float = 0.08) -> np.ndarray:
-    """Weights uniform[lo, hi]; biases 0 except the forget-gate bias = 1."""
+# Scale factors of the "peaked" model family: the same uniform draws as the named configurations, with
+# the embeddings, the recurrent matrices and the output matrix rescaled so that the model behaves like a
+# trained one in the two respects that decide whether two implementations can be compared token by token:
+#   * the output distribution is peaked (with every weight in [-0.08, 0.08] all 30,000 log-probabilities lie
+#     within ~0.5 of each other, so candidates tie to rounding noise at every step);
+#   * the recurrence is contractive (at hidden size 1000 the unscaled recurrent matrices have spectral radius
+#     ~1.5: rounding noise doubles about every ten decoder steps).
+PEAKED = {"emb": 5.0, "recurrent": 0.5, "output": 30.0}
+
+
+def make_blob(d: ModelDesc, seed: int, lo: float = -0.08, hi: float = 0.08, family: str = "flat") -> np.ndarray:
+    """Weights uniform[lo, hi]; biases 0 except the forget-gate bias = 1.  ``family="peaked"``
+    rescales three groups of matrices of the same draws (see ``PEAKED``)."""
     rng = np.random.default_rng(seed)
     n = blob_floats(d)
     blob = rng.random(n, dtype=np.float32)
     blob *= np.float32(hi - lo)
     blob += np.float32(lo)
+    if family not in ("flat", "peaked"):
+        raise ValueError(f"unknown model family {family!r}")
     off = 0
     for name, r, c in blob_layout(d):
         leaf = name.split(".")[1]
         if leaf.startswith("b_"):
             blob[off:off + r * c] = 1.0 if leaf == "b_f" else 0.0
+        elif family == "peaked":
+            if leaf == "W_emb":
+                blob[off:off + r * c] *= np.float32(PEAKED["emb"])
+            elif leaf.startswith("W_h"):
+                blob[off:off + r * c] *= np.float32(PEAKED["recurrent"])
+            elif name == "sm.D":
+                blob[off:off + r * c] *= np.float32(PEAKED["output"])
         off += r * c
     return blob
 
@@ -153,8 +173,8 @@ class Config:
         return make_sentences(n or self.n_sent, self.len_lo, self.len_hi, self.desc.Vs, self.zipf_s,
                               self.seeds[0], self.step_rule)
 
-    def blobs(self):
-        return [make_blob(self.desc, s) for s in self.seeds]
+    def blobs(self, family: str = "flat"):
+        return [make_blob(self.desc, s, family=family) for s in self.seeds]
 
 
 def configs() -> dict:

@@ -18,6 +18,16 @@ def token_identity(a, b, n):
     return same / max(n, 1)
 
 
+def window_flip(pt_e, pt_o, S, D=10, pt_tol=2e-3):
+    """True where the two implementations cut the local-attention window on different sides of an
+    integer although their centres p_t agree to rounding noise: ``(int)p_t`` differs, the two p_t
+    are within ``pt_tol`` of each other, and the shifted window edge lies inside the sentence."""
+    fe, fo = np.floor(pt_e), np.floor(pt_o)
+    hi = np.maximum(fe, fo)
+    inside = (hi > D) | (hi + D < S)   # an edge that moved: lo = n - D > 0 or hi = n + D < S - 1 (+1 for the larger n)
+    return (fe != fo) & (np.abs(pt_e - pt_o) <= pt_tol) & inside
+
+
 def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_len=None, D=10, t_lo=0, t_hi=None):
     """Engine ran with its beam forced to the checker's survivors: every step's per-beam
     top-(k+1) must then agree.
@@ -28,7 +38,9 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
     state then feeds every descendant of that hypothesis.  When the checker's p_t is within
     ``pt_eps`` of an integer n whose window edge lies inside the sentence (n > D or n + D < S),
     the hypothesis and its descendants are left out of the comparison (and counted); everything
-    else must agree.
+    else must agree.  When the engine's own p_t record is there (``eng["pt"]``) the rule is exact
+    instead: a hypothesis is left out from the forward on where the two ``(int)p_t`` really differ
+    while the two p_t agree to rounding noise (``window_flip``).
 
     Only steps t_lo <= t < t_hi are compared (all by default).  On the seeded random weights the
     recurrence amplifies rounding noise by about 2x every 10 steps (the fp32 checker against the
@@ -41,11 +53,15 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
     pt = ora.get("pt") if isinstance(ora, dict) else None
     if pt is not None and not np.any(pt != 0):
         pt = None  # global attention: no window
+    ept = eng.get("pt") if (isinstance(eng, dict) and pt is not None) else None
     worst, bad, skipped, compared = 0.0, 0, 0, 0
     for i in range(n):
         taint = np.zeros(k, bool)
         for t in range(int(steps[i])):
-            if pt is not None:
+            if ept is not None:
+                S = int(src_len[i]) if src_len is not None else 10 ** 9
+                taint = taint | window_flip(ept[i, t], pt[i, t], S, D)
+            elif pt is not None:
                 nn = np.round(pt[i, t])
                 frac = np.abs(pt[i, t] - nn)
                 S = int(src_len[i]) if src_len is not None else 10 ** 9
@@ -81,3 +97,68 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
             par = ora["surv_parent"][i, t]
             taint = taint[np.clip(par, 0, k - 1)] if t > 0 else np.repeat(taint[0], k)
     return worst, bad, skipped, compared
+
+
+def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10):
+    """Free-running engine output against the checker's trace of the same decode: every sentence
+    whose 1-best differs must part ways with the checker at a choice that is a tie within
+    tolerance in the checker's OWN numbers -- the engine's survivor of some rank is a candidate the
+    checker scored within ``rtol`` (relative to the score) of the checker's survivor of that rank
+    -- or after a local-attention window was cut on the other side of an integer (``window_flip``).
+    Anything else is returned as unexplained.
+
+    ``free`` needs the engine's trace (surv_tok, surv_parent, surv_score, pt), ``ora`` the
+    checker's (cand_tok, cand_logp, surv_*, pt).  Returns (identical, explained, unexplained)
+    lists of sentence indices; explained entries are (i, step, reason)."""
+    identical, explained, unexplained = [], [], []
+    lens = sents.lengths()
+    has_pt = ora.get("pt") is not None and np.any(ora["pt"] != 0) and free.get("pt") is not None
+    for i in range(sents.n):
+        if hyps(free, i) == hyps(ora, i):
+            identical.append(i)
+            continue
+        T, S = int(sents.steps[i]), int(lens[i])
+        reason = None
+        flipped = np.zeros(k, bool)   # engine slot descends from a forward with a window flip
+        for t in range(T):
+            if has_pt:
+                flipped = flipped | window_flip(free["pt"][i, t], ora["pt"][i, t], S, D)
+            et, ep = free["surv_tok"][i, t], free["surv_parent"][i, t]
+            ot, op, osc = ora["surv_tok"][i, t], ora["surv_parent"][i, t], ora["surv_score"][i, t]
+            if (et == ot).all() and (ep == op).all():
+                flipped = flipped[np.clip(ep, 0, k - 1)] if t > 0 else np.repeat(flipped[0], k)
+                continue
+            if flipped.any():
+                reason = (i, t, "window flip")
+                break
+            # first step with another choice: every engine survivor must be a candidate the checker scored
+            # within tolerance of the checker's survivor of the same rank
+            prev = ora["surv_score"][i, t - 1] if t > 0 else np.zeros(k, np.float32)
+            ok = True
+            for r in range(k):
+                if et[r] == ot[r] and ep[r] == op[r]:
+                    continue
+                b = int(ep[r])
+                hit = np.nonzero(ora["cand_tok"][i, t, b] == et[r])[0]
+                if len(hit) == 0:
+                    ok = False
+                    break
+                sc = prev[b] + ora["cand_logp"][i, t, b, hit[0]]
+                if abs(sc - osc[r]) > rtol * abs(osc[r]):
+                    ok = False
+                    break
+            reason = (i, t, "tie within tolerance") if ok else None
+            if not ok:
+                unexplained.append((i, t))
+            break
+        else:
+            # the beams agree at every step: the finished lists can still order two hypotheses of (nearly) the
+            # same final score differently
+            a, b = float(free["score"][i, 0]), float(ora["score"][i, 0])
+            if abs(a - b) <= rtol * abs(b):
+                reason = (i, T, "final scores tie")
+            else:
+                unexplained.append((i, T))
+        if reason:
+            explained.append(reason)
+    return identical, explained, unexplained

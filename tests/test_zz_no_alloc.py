@@ -36,9 +36,10 @@ def test_no_alloc_gemm_matches_allocating_entry_point(cuda_lib):
         X = rng.uniform(-1, 1, (R, K)).astype(np.float32)
         Wt = rng.uniform(-0.08, 0.08, (N, K)).astype(np.float32)
         got = _run(cuda_lib, X, Wt)
-        ref = decoder.k_gemm(X, np.ascontiguousarray(Wt.T), "tensor", "fp32")
+        # the ordinary entry point on the same operand format (three bf16 planes)
+        ref = decoder.k_gemm(X, np.ascontiguousarray(Wt.T), "tensor3", "fp32")
         scale = np.abs(X).astype(np.float64) @ np.abs(Wt.T).astype(np.float64)
-        # same kernel, same planes: the tolerance of the tensor-GEMM parity test
+        # the tolerance of the tensor-GEMM parity test
         assert (np.abs(got - ref) <= 1e-6 * scale + 1e-7).all()
         exact = X.astype(np.float64) @ Wt.T.astype(np.float64)
         assert (np.abs(got - exact) <= 1e-6 * scale + 1e-7).all()
