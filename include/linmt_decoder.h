@@ -206,13 +206,18 @@ typedef struct linmt_stats {
   int32_t last_gemm_launches;
   int32_t last_rec_gemm_launches; /* decoder LSTM-stack GEMM launches of the last call, if timing is on */
   float last_rec_gemm_ms;         /* time inside them */
-  float reserved;
+  float last_host_issue_ms;       /* host time spent issuing the decoder steps of the last device batch */
   double last_rec_gemm_flops;     /* their algorithmic flops: 2 * rows * 4H * K per launch */
 } linmt_stats;
 int linmt_get_stats(const linmt_engine* e, linmt_stats* out);
-/* 1 = bracket every vocabulary-GEMM launch and every decoder LSTM stack with CUDA events
- * (for roofline measurements). */
+/* 1 = put a CUDA event before every kernel of the decoder steps (for roofline measurements).  The events
+ * end the overlap of consecutive kernels, so a timed decode is a measurement pass: slower than an untimed one. */
 int linmt_set_kernel_timing(linmt_engine* e, int32_t on);
+/* Device time and launch count per kernel class of the last timed device batch (first device of the handle).
+ * Classes in launch order: 0 state gather, 1 LSTM gate GEMMs, 2 attention projections GEMM, 3 attention,
+ * 4 attention output GEMM, 5 vocabulary GEMM, 6 ensemble combine, 7 softmax / top-k, 8 beam selection.
+ * `ms` and `launches` hold n >= 9 entries. */
+int linmt_kernel_times(const linmt_engine* e, float* ms, int32_t* launches, int32_t n);
 
 /* Sentence API on a handle: DecoderSentence::Process (src/decoder_sentence.cu:40-49).
  * Needs an engine created from a config file (vocabularies).  Returns a library-owned

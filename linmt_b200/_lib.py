@@ -30,13 +30,13 @@ class TraceC(C.Structure):
 class StatsC(C.Structure):
     _fields_ = [("kernel_launches", C.c_int64), ("decoder_row_steps", C.c_int64), ("sentence_steps", C.c_int64),
                 ("last_decode_ms", C.c_float), ("last_gemm_ms", C.c_float), ("last_gemm_launches", C.c_int32),
-                ("last_rec_gemm_launches", C.c_int32), ("last_rec_gemm_ms", C.c_float), ("reserved", C.c_float),
+                ("last_rec_gemm_launches", C.c_int32), ("last_rec_gemm_ms", C.c_float), ("last_host_issue_ms", C.c_float),
                 ("last_rec_gemm_flops", C.c_double)]
 
 
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",
            "linmt_create_from_weights", "linmt_create_from_weights_on", "linmt_device_count", "linmt_front_error", "linmt_create", "linmt_destroy", "linmt_last_error", "linmt_beam",
-           "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing",
+           "linmt_decode_batch", "linmt_decode_batch_device", "linmt_get_stats", "linmt_set_kernel_timing", "linmt_kernel_times",
            "linmt_translate", "linmt_k_gemm", "linmt_k_softmax_topk", "linmt_gemm_f32_noalloc", "linmt_decode_file", "linmt_score_batch",
            "linmt_read_model_file", "python_unk_init", "python_unk_do_job", "linmt_unk_create", "linmt_unk_process", "linmt_unk_destroy"]
 
@@ -78,6 +78,7 @@ def load():
                                               C.c_void_p, C.c_void_p, C.c_void_p]
     lib.linmt_get_stats.argtypes = [C.c_void_p, C.POINTER(StatsC)]
     lib.linmt_set_kernel_timing.argtypes = [C.c_void_p, C.c_int32]
+    lib.linmt_kernel_times.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
     lib.linmt_translate.argtypes = [C.c_void_p, C.c_char_p]
     lib.linmt_translate.restype = C.c_char_p
     lib.linmt_k_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

@@ -12,6 +12,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <atomic>
+#include <chrono>
 #include <mutex>
 #include <numeric>
 #include <thread>
@@ -69,8 +70,7 @@ Engine::~Engine() {
   if (h_meta_) cudaFreeHost(h_meta_);
   if (ev0_) cudaEventDestroy(ev0_);
   if (ev1_) cudaEventDestroy(ev1_);
-  for (auto e : gemm_ev_) cudaEventDestroy(e);
-  for (auto e : rec_ev_) cudaEventDestroy(e);
+  for (auto e : kt_ev_) cudaEventDestroy(e);
   for (auto& v : enc_events_) for (auto e : v) cudaEventDestroy(e);
   if (enc_start_ev_) cudaEventDestroy(enc_start_ev_);
   for (auto st : enc_streams_) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
@@ -262,7 +262,6 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   use_tc_ = o.gemm_path != LINMT_GEMM_SIMT;
   { const char* pe = std::getenv("LINMT_XW"); xw_table_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_XW=0: test knob
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
-  { const char* pe = std::getenv("LINMT_ATT_GROUP"); att_group_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_ATT_MERGE"); att_merge_ = use_tc_ && !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
@@ -389,12 +388,13 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     if (t > 0 && desc.feed_input) { pa.src[na] = s.htilde; pa.dst[na++] = s.htilde_prev; }
     pa.n_arr = na;
     dim3 grid(rows, na + 1);
+    if (int rc = kt(KC_GATHER)) return rc;
     dec_prep_kernel<<<grid, 256, 0, stream>>>(pa, d_parent_, d_tok_, m.emb_tgt, V, s.x, Hp, k, t == 0 ? 1 : 0);
     LAUNCHED();
   }
   // 2. LSTM stack
-  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   for (int l = 0; l < L; ++l) {
+    if (int rc = kt(KC_LSTM)) return rc;
     ASegs a{};
     a.seg_k = Hp;
     a.ptr[0] = (l == 0) ? s.x : s.h_cur[l - 1]; a.ld[0] = Hp;
@@ -409,10 +409,10 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     LAUNCHED();
     if (kernel_timing) rec_flops_ += 2.0 * rows * 4.0 * H * (double)(a.nseg * H);
   }
-  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   float* htop = s.h_cur[L - 1];
   // 3. attention projections
   const float* u_alt = nullptr;
+  if (int rc = kt(KC_PROJ)) return rc;
   if (opt.attention_mode == LINMT_ATT_LOCAL_P_GENERAL) {
     ASegs a{}; a.ptr[0] = htop; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
     EpiAttnProj e{s.proj, 2 * Hp, Hp};
@@ -431,10 +431,12 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
     float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * rec_win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
+    if (int rc = kt(KC_ATTENTION)) return rc;
     if (int rc = launch_attention(mi, t, rows, u_alt, s.ctx, tc::Planes{}, 0, ra, rl, rv)) return rc;
   }
   // 5. attentional state htilde = tanh(W_c1 ctx + W_c2 h + b)
   {
+    if (int rc = kt(KC_ATTOUT)) return rc;
     ASegs a{}; a.ptr[0] = s.ctx; a.ld[0] = Hp; a.ptr[1] = htop; a.ld[1] = Hp; a.nseg = 2; a.seg_k = Hp;
     EpiBiasTanh e{m.att_bout, s.htilde, Hp};
     CK(gemm_simt(a, m.att_out_w, 2 * Hp, rows, Hp, 2 * Hp, e, stream));
@@ -444,43 +446,24 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
   {
     ASegs a{}; a.ptr[0] = s.htilde; a.ld[0] = Hp; a.nseg = 1; a.seg_k = Hp;
     EpiBias e{m.voc_b, s.logits, Vp};
-    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
+    if (int rc = kt(KC_VOCAB)) return rc;
     CK(gemm_simt(a, m.voc_w, Hp, rows, Vp, Hp, e, stream));
     LAUNCHED();
-    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
   }
   return LINMT_OK;
 }
 
-// Attention of one decoder forward (both GEMM families): a CTA per group of beams of a sentence
-// (attention_group_kernel), or a CTA per row (attention_kernel; LINMT_ATT_GROUP=0, a test knob -- the two
-// return the same bits).
+// Attention of one decoder forward (both GEMM families).
 int Engine::launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
                              float* ra, int32_t* rl, int32_t* rv) {
   const AttTrace at{mi == 0 ? trace_dev_.pt : nullptr, d_orig_, trace_dev_.Tm + 1, t};
   DevModel& m = models_[mi];
   DevState& s = states_[mi];
-  const int ens = ens_member_code(mi);
   const int ldp = att_merge_ ? 3 * Hp : 2 * Hp;
-  if (!att_group_) {
-    const size_t smem = sizeof(float) * (win + 8);
-    CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, ldp, u_alt, Hp, (const float*)m.vp,
-                    (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
-                    (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens, at));
-    LAUNCHED();
-    return LINMT_OK;
-  }
-  const int n_act = rows / k;
-  // beams per CTA: as few as fill the SMs, at most kAttBeams, within 48 KB of shared memory
-  const size_t per_beam = sizeof(float) * (size_t)(Hp + win + 16);
-  int bpc_max = (int)std::min<size_t>(kAttBeams, (48 * 1024) / per_beam);
-  if (bpc_max < 1) return fail(LINMT_ELIMIT, "hidden size too large for the attention kernel's shared memory");
-  int groups = std::max((k + bpc_max - 1) / bpc_max, std::min(k, (n_sm_ + n_act - 1) / n_act));
-  const int bpc = (k + groups - 1) / groups;
-  groups = (k + bpc - 1) / bpc;
-  CK(tc::launch_k(pdl_, attention_group_kernel, dim3(n_act, groups), dim3(256), per_beam * bpc, stream, (const float*)s.proj, ldp, u_alt, Hp,
-                  (const float*)m.vp, (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len,
-                  (int)opt.attention_mode, (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens, bpc, at));
+  const size_t smem = sizeof(float) * (win + 8);
+  CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, ldp, u_alt, Hp, (const float*)m.vp,
+                  (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
+                  (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens_member_code(mi), at));
   LAUNCHED();
   return LINMT_OK;
 }
@@ -495,6 +478,7 @@ int Engine::step_tail(int t, int rows) {
     trace_dev_.ld_logits = Vp;
     trace_dev_.row_stats = d_row_stats_;
     if (n_models == 1) {
+      if (int rc = kt(KC_SOFTMAX)) return rc;
       TopkRefine rf{};
       if (refine_) {
         const TcState& ts = tc_states_[0];
@@ -515,8 +499,10 @@ int Engine::step_tail(int t, int rows) {
       EnsembleRows er{};
       for (int mi = 0; mi < n_models; ++mi) er.logits[mi] = states_[mi].logits;
       er.n = n_models;
+      if (int rc = kt(KC_COMBINE)) return rc;
       CK(tc::launch_k(pdl_, ensemble_combine_kernel, dim3(rows), dim3(256), 0, stream, er, Vp, V, (int)opt.ensemble_mode, d_combined_));
       LAUNCHED();
+      if (int rc = kt(KC_SOFTMAX)) return rc;
       CK(launch_softmax_topk(d_combined_, Vp, V, kk, rows, o, opt.ensemble_mode == LINMT_ENS_PROB_MEAN ? 1 : 0, stream, pdl_));
     }
     LAUNCHED();
@@ -524,9 +510,11 @@ int Engine::step_tail(int t, int rows) {
   {
     BeamState bs{d_tok_, d_score_, d_parent_, d_hist_tok_, d_hist_parent_, d_fin_t_, d_fin_b_, d_fin_score_, d_fin_n_, fin_cap, R};
     const size_t smem = (size_t)k * kk * 24 + 16;
+    if (int rc = kt(KC_SELECT)) return rc;
     CK(tc::launch_k(pdl_, beam_select_kernel, dim3(n_act), dim3(256), smem, stream, bs, (const int32_t*)d_cand_idx_, (const float*)d_cand_logp_,
                     (const float*)d_eos_logp_, (const int32_t*)d_steps_, (const int32_t*)d_orig_, t, k, opt.penalty, opt.diversity, trace_dev_));
     LAUNCHED();
+    if (int rc = kt(KC_END)) return rc;
   }
   CK(cudaGetLastError());
   stats.decoder_row_steps += rows;
@@ -581,11 +569,12 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     trace_dev_.gold_logp = trace_dev->gold_logp;
     trace_dev_.pt = trace_dev->pt;
   }
-  gemm_ev_used_ = 0; rec_ev_used_ = 0; rec_flops_ = 0.0;
+  kt_used_ = 0; rec_flops_ = 0.0;
   int rc = use_tc_ ? run_encoder_tc(n, Smax) : run_encoder(n, Smax);
   if (rc) return rc;
   // the encoder's final states sit in buffer (Smax & 1)
   enc_final_buf_ = Smax & 1;
+  const auto host_t0 = std::chrono::steady_clock::now();
   for (int t = 0; t <= Tm; ++t) {
     int n_act = 0;
     while (n_act < n && m_steps[n_act] >= t) ++n_act;
@@ -608,6 +597,7 @@ int Engine::decode_core(const int32_t* d_ids, const int32_t* off_host, int n, co
     CK(cudaGetLastError());
   }
   CK(cudaEventRecord(ev1_, stream));
+  stats.last_host_issue_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
   return LINMT_OK;
 }
 
@@ -619,28 +609,27 @@ int Engine::finish_timing() {
     if (herr) return fail(LINMT_ECUDA, "a tensor-core GEMM gave up waiting on a barrier (results of this call are invalid)");
   }
   CK(cudaEventElapsedTime(&stats.last_decode_ms, ev0_, ev1_));
-  stats.last_gemm_ms = 0.f;
-  stats.last_gemm_launches = (int)(gemm_ev_used_ / 2);
-  for (size_t i = 0; i + 1 < gemm_ev_used_; i += 2) {
+  for (int c = 0; c < KC_COUNT; ++c) { class_ms[c] = 0.f; class_launches[c] = 0; }
+  for (size_t i = 0; i + 1 < kt_used_; ++i) {
+    if (kt_cls_[i] == KC_END) continue;
     float ms = 0.f;
-    CK(cudaEventElapsedTime(&ms, gemm_ev_[i], gemm_ev_[i + 1]));
-    stats.last_gemm_ms += ms;
+    CK(cudaEventElapsedTime(&ms, kt_ev_[i], kt_ev_[i + 1]));
+    class_ms[kt_cls_[i]] += ms;
+    ++class_launches[kt_cls_[i]];
   }
-  stats.last_rec_gemm_ms = 0.f;
-  stats.last_rec_gemm_launches = (int)(rec_ev_used_ / 2) * L;
+  stats.last_gemm_ms = class_ms[KC_VOCAB];
+  stats.last_gemm_launches = class_launches[KC_VOCAB];
+  stats.last_rec_gemm_ms = class_ms[KC_LSTM];
+  stats.last_rec_gemm_launches = class_launches[KC_LSTM];
   stats.last_rec_gemm_flops = rec_flops_;
-  for (size_t i = 0; i + 1 < rec_ev_used_; i += 2) {
-    float ms = 0.f;
-    CK(cudaEventElapsedTime(&ms, rec_ev_[i], rec_ev_[i + 1]));
-    stats.last_rec_gemm_ms += ms;
-  }
   return LINMT_OK;
 }
 
-int Engine::mark(std::vector<cudaEvent_t>& v, size_t& used) {
+int Engine::kt(int cls) {
   if (!kernel_timing) return LINMT_OK;
-  if (used == v.size()) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); v.push_back(ev); }
-  CK(cudaEventRecord(v[used++], stream));
+  if (kt_used_ == kt_ev_.size()) { cudaEvent_t ev; CK(cudaEventCreate(&ev)); kt_ev_.push_back(ev); kt_cls_.push_back(0); }
+  kt_cls_[kt_used_] = cls;
+  CK(cudaEventRecord(kt_ev_[kt_used_++], stream));
   return LINMT_OK;
 }
 
@@ -946,6 +935,12 @@ int linmt_get_stats(const linmt_engine* e, linmt_stats* out) {
     out->decoder_row_steps += r->stats.decoder_row_steps;
     out->sentence_steps += r->stats.sentence_steps;
   }
+  return LINMT_OK;
+}
+
+int linmt_kernel_times(const linmt_engine* e, float* ms, int32_t* launches, int32_t n) {
+  if (!e || !ms || !launches || n < linmt::KC_COUNT) return LINMT_EINVAL;
+  for (int c = 0; c < linmt::KC_COUNT; ++c) { ms[c] = e->eng.class_ms[c]; launches[c] = e->eng.class_launches[c]; }
   return LINMT_OK;
 }
 

@@ -61,8 +61,13 @@ struct DevState {
   std::vector<float*> enc_h[2], enc_c[2];            // [L] x [B][Hp], double buffered
 };
 
+// Kernel classes of a decoder step, in launch order (linmt_kernel_times reports one entry per class).
+enum KernelClass { KC_GATHER = 0, KC_LSTM, KC_PROJ, KC_ATTENTION, KC_ATTOUT, KC_VOCAB, KC_COMBINE, KC_SOFTMAX, KC_SELECT, KC_COUNT, KC_END = KC_COUNT };
+
 class Engine {
  public:
+  float class_ms[KC_COUNT] = {};      // device time per kernel class in the last timed decode
+  int class_launches[KC_COUNT] = {};
   Engine() = default;
   ~Engine();
   int init(const linmt_model_desc& d, const float* const* blobs, int n_models, size_t blob_floats, const linmt_options& o);
@@ -123,7 +128,6 @@ class Engine {
   bool xw_table_ = false;  // first decoder layer: embedding term from a per-vocabulary table instead of the GEMM
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
   bool att_merge_ = false; // tensor path: W_c2 . h_top computed with the attention projections (LINMT_ATT_MERGE=0: test knob)
-  bool att_group_ = true;  // attention: one CTA per group of beams of a sentence (LINMT_ATT_GROUP=0: one per row, test knob)
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
@@ -175,10 +179,14 @@ class Engine {
   // trace buffers (device), sized on demand
   std::vector<void*> trace_allocs_;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
-  std::vector<cudaEvent_t> gemm_ev_, rec_ev_;   // begin/end pairs: vocabulary GEMM, decoder LSTM stack
-  size_t gemm_ev_used_ = 0, rec_ev_used_ = 0;
+  // kernel timing (off by default): an event before every kernel of the decoder steps, tagged with the kernel's
+  // class; the time to the next event is booked to that class.  The events end the overlap of consecutive
+  // kernels, so a timed decode is a measurement pass, not the number to report as throughput.
+  std::vector<cudaEvent_t> kt_ev_;
+  std::vector<int> kt_cls_;
+  size_t kt_used_ = 0;
   double rec_flops_ = 0.0;
-  int mark(std::vector<cudaEvent_t>& v, size_t& used);   // records the next event when kernel timing is on
+  int kt(int cls);
 };
 
 // host-side weight packing

@@ -283,12 +283,13 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
         add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
     jobs.n = nj;
     dim3 grid(rows, nj);
+    if (int rc = kt(KC_GATHER)) return rc;
     CK(tc::launch_k(pdl_, row_gather_kernel, grid, dim3(128), 0, stream, jobs, (const int32_t*)d_parent_, (const int32_t*)d_tok_, V, k, t == 0 ? 1 : 0));
     LAUNCHED();
   }
   // 2. LSTM stack
-  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   for (int l = 0; l < L; ++l) {
+    if (int rc = kt(KC_LSTM)) return rc;
     tc::TcEpiLstm e{};
     e.bias = m.dec_b[l]; e.ldc = Hp;
     if (t == 0) { e.c_prev = s.c_prev[l]; e.c_out = s.c_cur[l]; }
@@ -318,8 +319,8 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     if (rc) return rc;
     if (kernel_timing) rec_flops_ += 2.0 * rows * 4.0 * H * (double)((K / Hp) * H);
   }
-  if (int rc = mark(rec_ev_, rec_ev_used_)) return rc;
   // 3. attention projections: tanh(W_p h) | W_a^T h
+  if (int rc = kt(KC_PROJ)) return rc;
   const float* u_alt = (opt.attention_mode == LINMT_ATT_GLOBAL_DOT) ? s.h_cur[L - 1] : nullptr;
   if (att_merge_) {
     // ... | W_c2 h: the half of the attention output's pre-activation that needs h_top only (global dot
@@ -340,11 +341,13 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     float* ra = d_rec_align_ ? d_rec_align_ + (size_t)t * R * rec_win : nullptr;
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
+    if (int rc = kt(KC_ATTENTION)) return rc;
     if (int rc = launch_attention(mi, t, rows, u_alt, nullptr, ts.panel_top, nt_, ra, rl, rv)) return rc;
   }
   // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)
   {
     tc::TcEpiBiasTanh e{m.att_bout, ts.panel_ht, 0, nt_};
+    if (int rc0 = kt(KC_ATTOUT)) return rc0;
     int rc;
     if (att_merge_) {
       // W_c1 ctx over the first Hp of the K columns; W_c2 h comes in as a precomputed row
@@ -360,14 +363,13 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
     pmax_slots_ = 0;
     if (n_models == 1 && pmax_on_) { e.pmax = d_pmax_; e.pmax_ld = pmax_ld_; e.n_valid = V; }
-    if (int rc = mark(gemm_ev_, gemm_ev_used_)) return rc;
+    if (int rc = kt(KC_VOCAB)) return rc;
     // Logits feed only the softmax of their own step: the tensor core's truncation bias over one
     // K = Hp chain (~32 ulp of the accumulator, 2e-7 relative on a log-probability) does not
     // accumulate over steps as it does through the recurrent products, so this GEMM runs its
     // leading product as one chain (no intermediate drains: 5 % faster).
     int rc = tc_gemm(ts.panel_ht, 0, R, m.p_voc_w, rows, Vp, Hp, e, nt_vocab_, Hp / 32);
     if (rc) return rc;
-    if ((rc = mark(gemm_ev_, gemm_ev_used_))) return rc;
   }
   return LINMT_OK;
 }

@@ -1178,13 +1178,13 @@ inline bool make_tmap(CUtensorMap* map, const __nv_bfloat16* ptr, uint64_t rows,
 // it is set once per (kernel, device), for the device that is current at the launch.
 constexpr int kMaxDevices = 64;
 template <class Kernel>
-inline cudaError_t ensure_smem_optin(Kernel* kernel, bool* done_per_device) {
+inline cudaError_t ensure_smem_optin(Kernel* kernel, bool* done_per_device, int bytes = SMEM_BUDGET + 1280) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
   if (!done_per_device[dev]) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET + 1280);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return e;
     done_per_device[dev] = true;
   }

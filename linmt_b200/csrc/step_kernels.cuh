@@ -154,9 +154,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   (rec_win = max_src, rec_lo = 0), the first member writes it, the others add to it in member order,
 //   and the last one takes the vote: the position of the largest summed score, the search starting from
 //   "none, 0" (EnsembleFactory::EnsemblesModels, src/decoder.h:1934-1964).
-// grid = rows, block = 256, dynamic smem = (win + 8) floats.  (Keeping the window's states in shared
-// memory between the score sweep and the context sweep was tried: 86 KB per CTA costs the occupancy that
-// the halved L2 traffic buys, no change in the decode time.)
+// grid = rows, block = 256, dynamic smem = (win + 8) floats.  The kernel is a chain of L2 round trips, not
+// of bytes: loads are issued in batches ahead of the arithmetic.  (Two forms that cut its L2 traffic were
+// tried and measured no faster: the window's states kept in shared memory between the score sweep and the
+// context sweep -- 86 KB per CTA costs the occupancy the halved traffic buys -- and one CTA per group of
+// beams of a sentence reading every state row once for all of them -- a quarter of the CTAs, the same
+// chain of round trips in each.)
 // Optional record of the attention centre p_t of every row of a forward (local attention): the parity tests
 // use it to tell a window that was cut on the other side of an integer apart from an error.
 struct AttTrace {
@@ -165,7 +168,7 @@ struct AttTrace {
   int T1;               // forwards per sentence in the record (longest step count + 1)
   int t;                // this forward
 };
-static __global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+static __global__ void __launch_bounds__(256, 4) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
@@ -207,10 +210,19 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
   for (int w = warp; w < W; w += nw) {
     const float* hrow = hsb + (size_t)(S - 1 - (lo + w)) * Hp;
     float acc = 0.f;
-    for (int j = lane * 4; j < Hp; j += 128) {
-      const float4 a = *reinterpret_cast<const float4*>(hrow + j);
-      const float4 b = *reinterpret_cast<const float4*>(u + j);
-      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    // loads first, four row segments at a time: the kernel is a chain of L2 round trips otherwise
+    for (int j0 = lane * 4; j0 < Hp; j0 += 4 * 128) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int j = j0 + q * 128;
+        if (j < Hp) { a[q] = *reinterpret_cast<const float4*>(hrow + j); b[q] = *reinterpret_cast<const float4*>(u + j); }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (j0 + q * 128 < Hp) {
+          acc = fmaf(a[q].x, b[q].x, acc); acc = fmaf(a[q].y, b[q].y, acc); acc = fmaf(a[q].z, b[q].z, acc); acc = fmaf(a[q].w, b[q].w, acc);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -279,204 +291,22 @@ static __global__ void __launch_bounds__(256) attention_kernel(const float* __re
   float* crow = ctx ? ctx + (size_t)r * Hp : nullptr;
   for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w = 0; w < W; ++w) {
-      const float a = e[w];
-      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
-      acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
+    for (int w0 = 0; w0 < W; w0 += 8) {   // eight state rows in flight, added in position order
+      float4 h4[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (w0 + q < W) h4[q] = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w0 + q)) * Hp + j);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (w0 + q < W) {
+          const float a = e[w0 + q];
+          acc.x += a * h4[q].x; acc.y += a * h4[q].y; acc.z += a * h4[q].z; acc.w += a * h4[q].w;
+        }
     }
     if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
     if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
       const size_t idx = (size_t)r * ctx_planes.ld + j;
       tc::split_store4(ctx_planes, nt, idx, acc.x, acc.y, acc.z, acc.w);
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------
-// The same attention for a GROUP of beams of one sentence per CTA.  The k beams of a sentence attend
-// over the same encoder states, so a CTA that serves several of them reads every state row once per
-// pass for all of them (attention_kernel reads the window of every row on its own: k times the L2
-// traffic).  Every sum is formed in the same order as in attention_kernel -- the same lane-strided FMA
-// chains, the same shuffle trees, the same position order in the context -- so the two kernels return
-// the same bits.
-//   grid = (active sentences, groups), block = 256; beams [g * bpc, min(k, (g+1) * bpc)) belong to group g,
-//   bpc <= kAttBeams.  dynamic smem = bpc * (Hp + win + 16) floats.
-constexpr int kAttBeams = 6;
-static __global__ void __launch_bounds__(256) attention_group_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
-                                 const float* __restrict__ vp, const float* __restrict__ hs,
-                                 const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
-                                 int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
-                                 int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt,
-                                 int rec_win, int ens, int bpc, AttTrace at) {
-  tc::pdl_launch_dependents();
-  tc::pdl_wait();
-  extern __shared__ float sm[];
-  float* su = sm;                          // [bpc][Hp]   the beams' query vectors
-  float* se = su + (size_t)bpc * Hp;       // [bpc][win]  scores, then alignments
-  float* sred = se + (size_t)bpc * win;    // [bpc][8]    per-warp partial sums
-  __shared__ float s_pt[kAttBeams];
-  __shared__ int s_lo[kAttBeams], s_hi[kAttBeams];
-  const int sent = blockIdx.x;
-  const int b0 = blockIdx.y * bpc;
-  const int nb = (k - b0) < bpc ? (k - b0) : bpc;
-  if (nb <= 0) return;
-  const int S = src_len[sent];
-  const int r0 = sent * k + b0;
-  const float* hsb = hs + (size_t)sent * max_src * Hp;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-  for (int i = tid; i < nb * (Hp / 4); i += 256) {
-    const int b = i / (Hp / 4), j = (i - b * (Hp / 4)) * 4;
-    const float* u = u_alt ? (u_alt + (size_t)(r0 + b) * ldu) : (proj + (size_t)(r0 + b) * ldp + Hp);
-    *reinterpret_cast<float4*>(su + (size_t)b * Hp + j) = *reinterpret_cast<const float4*>(u + j);
-  }
-  if (mode == 0) {
-    float part[kAttBeams];
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) part[b] = 0.f;
-    for (int j = tid; j < H; j += 256) {
-      const float v = vp[j];
-#pragma unroll
-      for (int b = 0; b < kAttBeams; ++b)
-        if (b < nb) part[b] = fmaf(v, proj[(size_t)(r0 + b) * ldp + j], part[b]);
-    }
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) part[b] += __shfl_xor_sync(0xffffffffu, part[b], o);
-      if (lane == 0 && b < nb) sred[b * 8 + warp] = part[b];
-    }
-    __syncthreads();
-    if (tid < nb) {
-      float dot = 0.f;
-      for (int i = 0; i < 8; ++i) dot += sred[tid * 8 + i];
-      const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)dot)));  // SigmoidKernel, deep_rnn_kernel.h:1075-1080
-      const float pt = (float)S * sg;
-      s_pt[tid] = pt;
-      s_lo[tid] = (0 > (int)pt - D) ? 0 : ((int)pt - D);                  // LowerUpperKernel, :1094-1100
-      s_hi[tid] = ((S - 1) < (int)pt + D) ? (S - 1) : ((int)pt + D);
-      if (at.pt) at.pt[((size_t)at.orig[sent] * at.T1 + at.t) * k + b0 + tid] = pt;
-    }
-  } else if (tid < nb) {
-    s_pt[tid] = 0.f; s_lo[tid] = 0; s_hi[tid] = S - 1;
-  }
-  __syncthreads();
-  int lo_min = 0x7fffffff, hi_max = -1;
-  for (int b = 0; b < nb; ++b) { lo_min = min(lo_min, s_lo[b]); hi_max = max(hi_max, s_hi[b]); }
-  // scores: a warp per source position, the row's dot product with every beam whose window holds it
-  for (int sp = lo_min + warp; sp <= hi_max; sp += 8) {
-    const float* hrow = hsb + (size_t)(S - 1 - sp) * Hp;
-    float acc[kAttBeams];
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) acc[b] = 0.f;
-    for (int j = lane * 4; j < Hp; j += 128) {
-      const float4 a = *reinterpret_cast<const float4*>(hrow + j);
-#pragma unroll
-      for (int b = 0; b < kAttBeams; ++b) {
-        if (b < nb) {
-          const float4 q = *reinterpret_cast<const float4*>(su + (size_t)b * Hp + j);
-          acc[b] = fmaf(a.x, q.x, acc[b]); acc[b] = fmaf(a.y, q.y, acc[b]); acc[b] = fmaf(a.z, q.z, acc[b]); acc[b] = fmaf(a.w, q.w, acc[b]);
-        }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], o);
-      if (lane == 0 && b < nb && sp >= s_lo[b] && sp <= s_hi[b]) se[(size_t)b * win + (sp - s_lo[b])] = acc[b];
-    }
-  }
-  __syncthreads();
-  // AlignmentReductionKernel (deep_rnn_kernel.h:1197-1241) per beam: one warp each
-  for (int b = warp; b < nb; b += 8) {
-    float* e = se + (size_t)b * win;
-    const int lo = s_lo[b], W = s_hi[b] - lo + 1;
-    const int r = r0 + b;
-    float mx = 0.f;
-    for (int w = lane; w < W; w += 32) mx = fmaxf(mx, e[w]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-    for (int w = lane; w < W; w += 32) { const float ev = expf(e[w] - mx); e[w] = ev; sum += ev; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float sigma_sq = ((float)D * (float)D) / 4.0f;
-    const float pt = s_pt[b];
-    float best = 0.f; int besti = 0x7fffffff;
-    for (int w = lane; w < W; w += 32) {
-      float a = e[w];
-      if (mode == 0) {
-        const float tmp = expf((-1 * powf(pt - (float)(lo + w), 2.0f)) / (2 * sigma_sq));
-        if (0 != sum) a = (a / sum) * tmp;
-      } else if (0 != sum) a = a / sum;
-      e[w] = a;
-      if (a > best) { best = a; besti = lo + w; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
-    }
-    if (lane == 0 && rec_lo && ens == 0) { rec_lo[r] = lo; rec_vit[r] = (best > 0.f) ? besti : -1; }
-  }
-  __syncthreads();
-  if (rec_align) {
-    for (int b = 0; b < nb; ++b) {
-      const float* e = se + (size_t)b * win;
-      const int lo = s_lo[b], hi = s_hi[b], W = hi - lo + 1;
-      float* row = rec_align + (size_t)(r0 + b) * rec_win;
-      if (ens == 0) {
-        for (int w = tid; w < rec_win; w += 256) row[w] = (w < W) ? e[w] : 0.f;
-      } else {
-        for (int sp = tid; sp < rec_win; sp += 256) {
-          const float a = (sp >= lo && sp <= hi) ? e[sp - lo] : 0.f;
-          row[sp] = (ens == 1) ? (0.f + a) : (row[sp] + a);
-        }
-      }
-    }
-    if (ens == 3) {
-      __syncthreads();
-      for (int b = warp; b < nb; b += 8) {
-        const float* row = rec_align + (size_t)(r0 + b) * rec_win;
-        float best = 0.f; int besti = 0x7fffffff;
-        for (int sp = lane; sp < rec_win; sp += 32) {
-          const float a = row[sp];
-          if (a > best) { best = a; besti = sp; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-          const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-          if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
-        }
-        if (lane == 0) { rec_lo[r0 + b] = 0; rec_vit[r0 + b] = (best > 0.f) ? besti : -1; }
-      }
-    }
-  }
-  // context (CreateCTKernel, deep_rnn_kernel.h:1250-1260): every state row of the union of the windows is
-  // loaded once and added, in position order, into the sums of the beams whose window holds it
-  for (int j = tid * 4; j < Hp; j += 1024) {
-    float4 acc[kAttBeams];
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) acc[b] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int sp = lo_min; sp <= hi_max; ++sp) {
-      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - sp) * Hp + j);
-#pragma unroll
-      for (int b = 0; b < kAttBeams; ++b) {
-        if (b < nb && sp >= s_lo[b] && sp <= s_hi[b]) {
-          const float a = se[(size_t)b * win + (sp - s_lo[b])];
-          acc[b].x += a * h4.x; acc[b].y += a * h4.y; acc[b].z += a * h4.z; acc[b].w += a * h4.w;
-        }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kAttBeams; ++b) {
-      if (b < nb) {
-        const int r = r0 + b;
-        if (ctx) *reinterpret_cast<float4*>(ctx + (size_t)r * Hp + j) = acc[b];
-        if (ctx_planes.p[0]) tc::split_store4(ctx_planes, nt, (size_t)r * ctx_planes.ld + j, acc[b].x, acc[b].y, acc[b].z, acc[b].w);
-      }
     }
   }
 }
@@ -517,7 +347,7 @@ constexpr float kPairInv = 1.0f / 2048.0f;
 // then ranked exactly.  If more elements than the candidate buffer holds reach the threshold
 // (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
 constexpr int kTopkCap = 1024;
-static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
+static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
                                                                   int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots, TopkRefine rf) {
   extern __shared__ float s_a[];   // [rf.K] the row's activations in fp32 (refinement only)
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
@@ -596,6 +426,31 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
     if (tid == 0) s_max = bm;
   }
   __syncthreads();
+  if (pmax) {
+    // The threshold from 32 group maxima admits a few dozen elements.  A tighter one costs little here: the
+    // block maxima that reach it are few, each is an element of the row, the blocks are disjoint, and the
+    // kk-th largest of them is still reached by at least kk elements.
+    const float tau0 = s_tau;
+    for (int sl = tid; sl < n_slots; sl += 256) {
+      const float v = pmax[(size_t)r * pmax_ld + sl];
+      if (v >= tau0) {
+        const int pos = atomicAdd(&s_count, 1);
+        if (pos < kTopkCap) s_cv[pos] = v;
+      }
+    }
+    __syncthreads();
+    const int m2 = s_count;
+    if (m2 <= kTopkCap)
+      for (int c = tid; c < m2; c += 256) {
+        const float v = s_cv[c];
+        int rank = 0;
+        for (int d = 0; d < m2; ++d) rank += (s_cv[d] > v || (s_cv[d] == v && d < c)) ? 1 : 0;
+        if (rank == kk - 1) s_tau = v;
+      }
+    __syncthreads();
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+  }
   float tau = s_tau;
   const float rmax = s_max;
   if (rf.a0) {
@@ -715,16 +570,27 @@ static __global__ void __launch_bounds__(256) softmax_topk_kernel(const float* _
       const __half* w0 = rf.b0 + (size_t)v * rf.ldb;
       const __half* w1 = rf.b1 + (size_t)v * rf.ldb;
       float acc = 0.f;
-      for (int j = lane * 4; j < rf.K; j += 128) {
-        const uint2 q0 = *reinterpret_cast<const uint2*>(w0 + j);
-        const uint2 q1 = *reinterpret_cast<const uint2*>(w1 + j);
-        const __half2 h00 = *reinterpret_cast<const __half2*>(&q0.x), h01 = *reinterpret_cast<const __half2*>(&q0.y);
-        const __half2 h10 = *reinterpret_cast<const __half2*>(&q1.x), h11 = *reinterpret_cast<const __half2*>(&q1.y);
-        const float2 b00 = __half22float2(h00), b01 = __half22float2(h01), b10 = __half22float2(h10), b11 = __half22float2(h11);
-        acc = fmaf(s_a[j + 0], fmaf(b10.x, kPairInv, b00.x), acc);
-        acc = fmaf(s_a[j + 1], fmaf(b10.y, kPairInv, b00.y), acc);
-        acc = fmaf(s_a[j + 2], fmaf(b11.x, kPairInv, b01.x), acc);
-        acc = fmaf(s_a[j + 3], fmaf(b11.y, kPairInv, b01.y), acc);
+      // eight loads in flight per lane: the weight rows come from L2 or HBM and a lane has nothing else to do
+      for (int j0 = lane * 4; j0 < rf.K; j0 += 4 * 128) {
+        uint2 q0[4], q1[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * 128;
+          if (j < rf.K) { q0[u] = *reinterpret_cast<const uint2*>(w0 + j); q1[u] = *reinterpret_cast<const uint2*>(w1 + j); }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * 128;
+          if (j < rf.K) {
+            const __half2 h00 = *reinterpret_cast<const __half2*>(&q0[u].x), h01 = *reinterpret_cast<const __half2*>(&q0[u].y);
+            const __half2 h10 = *reinterpret_cast<const __half2*>(&q1[u].x), h11 = *reinterpret_cast<const __half2*>(&q1[u].y);
+            const float2 b00 = __half22float2(h00), b01 = __half22float2(h01), b10 = __half22float2(h10), b11 = __half22float2(h11);
+            acc = fmaf(s_a[j + 0], fmaf(b10.x, kPairInv, b00.x), acc);
+            acc = fmaf(s_a[j + 1], fmaf(b10.y, kPairInv, b00.y), acc);
+            acc = fmaf(s_a[j + 2], fmaf(b11.x, kPairInv, b01.x), acc);
+            acc = fmaf(s_a[j + 3], fmaf(b11.y, kPairInv, b01.y), acc);
+          }
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

@@ -145,6 +145,16 @@ class Decoder:
     def set_kernel_timing(self, on: bool):
         self._lib.linmt_set_kernel_timing(self._h, int(on))
 
+    KERNEL_CLASSES = ("gather", "lstm_gemm", "attn_proj_gemm", "attention", "attn_out_gemm", "vocab_gemm",
+                      "ensemble_combine", "softmax_topk", "beam_select")
+
+    def kernel_times(self):
+        """{class: (ms, launches)} of the last decode with kernel timing on."""
+        ms = np.zeros(9, np.float32)
+        n = np.zeros(9, np.int32)
+        self._lib.linmt_kernel_times(self._h, _ptr(ms), _ptr(n), 9)
+        return {c: (float(ms[i]), int(n[i])) for i, c in enumerate(self.KERNEL_CLASSES)}
+
 
 class DecoderSentence:
     """Mirror of the reference's ``DecoderSentence`` (src/decoder_sentence.h:28-60)."""

@@ -396,15 +396,21 @@ def test_force_decoding_scores(oracle, cuda_lib, c1):
 
 def test_launch_variants_give_identical_bits(cuda_lib):
     """The overlapped launch forms change scheduling, never arithmetic: with programmatic dependent
-    launch off, with the persistent vocabulary GEMM off, and with the softmax finding its own row
-    maxima instead of taking the GEMM's block maxima, a decode of 24 sentences of the reference
-    configuration returns the same tokens and the same score bits."""
+    launch off and with the persistent vocabulary GEMM off, a decode of 24 sentences of the reference
+    configuration returns the same tokens and the same score bits.  Three more knobs compute the same sums in another
+    order (the softmax finding its own row maxima and threshold instead of taking the GEMM's block
+    maxima, so that another set of candidates is recomputed accurately; the first decoder layer's
+    embedding term inside the GEMM instead of from its table; the attention output product as one GEMM
+    instead of two halves): scores equal to fp32 rounding, and a near-tie may resolve differently in a
+    sentence or two."""
     from linmt_b200 import decoder
     c = synth.configs()["C2"]
     blob = c.blobs()[0]
     sents = c.sentences().subset(range(24))   # 288 rows: several waves of vocabulary tiles -> persistent kernel
+    same_bits = ({"LINMT_PDL": "0"}, {"LINMT_TC_PERSIST": "0"})
+    same_sums = ({"LINMT_PMAX": "0"}, {"LINMT_XW": "0"}, {"LINMT_ATT_MERGE": "0"})
     outs = []
-    for env in ({}, {"LINMT_PDL": "0"}, {"LINMT_TC_PERSIST": "0"}, {"LINMT_PMAX": "0"}, {"LINMT_XW": "0"}):
+    for env in ({},) + same_bits + same_sums:
         old = {k: os.environ.get(k) for k in env}
         os.environ.update(env)
         try:
@@ -418,17 +424,15 @@ def test_launch_variants_give_identical_bits(cuda_lib):
                     os.environ.pop(k, None)
                 else:
                     os.environ[k] = v
-    for o in outs[1:4]:
+    for o in outs[1:1 + len(same_bits)]:
         assert (o["tok"] == outs[0]["tok"]).all() and (o["len"] == outs[0]["len"]).all()
         assert (o["score"] == outs[0]["score"]).all()
-    # the first decoder layer's embedding term from its table or inside the GEMM: the same sum in another order
-    # (scores equal to fp32 rounding; a near-tie may resolve differently in a sentence or two)
-    o = outs[4]
-    same = sum(1 for i in range(sents.n) if hyps(o, i) == hyps(outs[0], i))
-    assert same >= sents.n - 2
-    for i in range(sents.n):
-        if hyps(o, i) == hyps(outs[0], i):
-            assert abs(o["score"][i, 0] - outs[0]["score"][i, 0]) <= 1e-4 * abs(outs[0]["score"][i, 0])
+    for o in outs[1 + len(same_bits):]:
+        same = sum(1 for i in range(sents.n) if hyps(o, i) == hyps(outs[0], i))
+        assert same >= sents.n - 2
+        for i in range(sents.n):
+            if hyps(o, i) == hyps(outs[0], i):
+                assert abs(o["score"][i, 0] - outs[0]["score"][i, 0]) <= 1e-4 * abs(outs[0]["score"][i, 0])
 
 
 @pytest.mark.parametrize("L,H,V,Vs,beam,att", [
