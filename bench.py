@@ -8,7 +8,9 @@ sentences of the reference decode configuration: 4-layer 1000-unit LSTM encoder/
 30k/30k vocabularies, local-p 'general' attention with feed-input, beam 12, 64 sentences of
 10..50 words, T = floor(1.5 S) + 10 expansions, fp32 weights uniform[-0.08, 0.08] (seed 1).
 With N > 1 every rank decodes its own batch of the same distribution on its own replica
-(weak scaling, no collective in the data path).  Prints ONE JSON line on rank 0.
+(weak scaling, no collective in the data path).  Beside that headline the line carries `strong_c3`: the
+fixed 4096-sentence bf16 job of the throughput configuration, length-bucketed, dealt to the N ranks and
+gathered once (strong scaling), with per-rank work and times.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -31,12 +33,14 @@ from linmt_b200 import synth  # noqa: E402
 METRIC = "decoded target tokens/sec, beam 12, 4x1000 LSTM"
 UNIT = "tokens/s"
 FALLBACK_TFLOPS = 1590.0  # used only if MEASURED_PEAKS.json is absent
-# DRAM bytes of one launch at 768 rows from ncu captures (see profiles/): read + write
-VOCAB_GEMM_TRAFFIC_BYTES = 185.7e6  # 131.1 MB + 54.6 MB, profiles/vocab_gemm_tensor_path_C2.md (algorithmic 218 MB; logits partly still in L2)
-# gate GEMM: 66.7 MB measured at K = 3072 (profiles/gate_gemm_tensor_path_C2.md, algorithmic 69.1 MB); the four
-# launches of a stack now all run K = 2048 (algorithmic 49.2 MB, scaled from that capture), the first of them reading
-# 12.6 MB of input-term table rows besides: average of the four
-GATE_GEMM_TRAFFIC_BYTES = 66.7e6 * 49.2 / 69.1 + 12.6e6 / 4
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes (read + write) of ONE launch of each kernel class at the full width of the C2 batch (768 rows), from
+# ncu captures of this benchmark's own C2 decode (dram__bytes_read.sum + dram__bytes_write.sum of one launch; the
+# summaries with the capture commands are committed with the profiles).  None = no capture for that class.
+C2_TRAFFIC_BYTES = {
+    "lstm_gemm": None, "vocab_gemm": None, "attn_proj_gemm": None, "attn_out_gemm": None,
+    "softmax_topk": None, "gather": None, "attention": None, "beam_select": None,
+}
 
 
 WORKLOADS = {
@@ -114,11 +118,12 @@ def clocks_stop(p, path, device_index: int):
 
 
 def peaks():
+    """(sustained bf16 TFLOP/s, HBM GB/s, where the numbers come from)."""
     try:
         p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        return float(p["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+        return float(p["bf16_tflops_sustained"]), float(p["hbm_gbs"]), "measured (cuBLAS bf16 sustained; copy bandwidth)"
     except Exception:
-        return FALLBACK_TFLOPS, "fallback"
+        return FALLBACK_TFLOPS, FALLBACK_HBM_GBS, "fallback"
 
 
 def host_threads() -> int:
@@ -134,60 +139,72 @@ def emitted_tokens(out_len: np.ndarray) -> int:
     return int(np.maximum(out_len[:, 0] - 2, 0).sum())
 
 
-def cpu_leg(c, blobs, sents, n_sample: int, threads: int = 0, repeat: int = 1, ensemble="prob_mean"):
-    """Times the CPU checker (a port of the reference's math; the reference has no CPU path
-    of its own) on the first n_sample sentences of the batch."""
+def cpu_leg(c, blobs, sents, n_sample: int, group: int, ensemble="prob_mean", repeat: int = 1):
+    """Times the CPU restatement of the reference's math (the reference has no CPU forward path of its own
+    and cannot be built without Boost and a GPU) on the first n_sample sentences of the batch, with all host
+    threads.  group = 1 is the reference's own shape: one sentence at a time, rows = beam
+    (src/decoder.h:1780-1840); group = 0 decodes the sample as one batch.  The dense products go through the
+    Eigen headers the reference ships where that build is there, else through the restatement's own FMA loops."""
     from oracle import oracle_py
+    gemm = "eigen" if oracle_py.eigen_lib() is not None else "canonical"
     sub = sents.subset(range(min(n_sample, sents.n)))
     best = None
     for _ in range(repeat):
         t0 = time.perf_counter()
         o = oracle_py.decode(c.desc, blobs, sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
-                             attention=c.attention, precision=c.precision, ensemble=ensemble,
-                             threads=threads or host_threads())
+                             attention=c.attention, precision=c.precision, ensemble=ensemble, group=group,
+                             threads=host_threads(), gemm=gemm)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     toks = emitted_tokens(o["len"])
-    return toks / best, best, sub.n, threads or host_threads()
+    return {"value": toks / best, "seconds": best, "sentences": sub.n, "cores": host_threads(),
+            "gemm": "Eigen 3.2.92 (the reference's vendored headers), OpenMP" if gemm == "eigen" else "the restatement's own blocked FMA loops, OpenMP"}
+
+
+def cpu_baseline_block(c, blobs, sents, ensemble="prob_mean"):
+    """cpu_baseline of the JSON line: the reference-shaped timing is the value; the batched one stands beside it."""
+    ref = cpu_leg(c, blobs, sents, 4, 1, ensemble)
+    bat = cpu_leg(c, blobs, sents, 16, 0, ensemble)
+    return {"value": ref["value"], "unit": UNIT, "cores": ref["cores"], "kind": "port",
+            "sample": f"first {ref['sentences']} sentences of the batch, one sentence at a time (rows = {c.beam}, the reference's own "
+                      f"loop shape), {ref['seconds']:.1f} s of CPU work; dense products: {ref['gemm']}",
+            "batched": {"value": bat["value"], "unit": UNIT,
+                        "sample": f"first {bat['sentences']} sentences as one batch (rows = {bat['sentences']}*{c.beam}), {bat['seconds']:.1f} s of CPU work"}}
 
 
 def run_reference(args):
+    """The reference arm: the CPU restatement of the reference's math, in the reference's own loop shape (one
+    sentence at a time), all host threads, a bounded sample of the same workload per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     c, batches = workload(args.workload, 0, 1)
     sents = batches[0]
-    blob = c.blobs()[0]
-    n_sample = 8
-    times = []
-    toks = 0
-    from oracle import oracle_py
-    sub = sents.subset(range(n_sample))
+    blobs = c.blobs()
+    n_sample = 4
+    times, toks, leg = [], 0, None
     for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        o = oracle_py.decode(c.desc, [blob], sub, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
-                             threads=host_threads())
-        dt = time.perf_counter() - t0
+        leg = cpu_leg(c, blobs, sents, n_sample, 1)
         if i >= args.warmup:
-            times.append(dt)
-            toks = emitted_tokens(o["len"])
+            times.append(leg["seconds"])
+            toks = leg["value"] * leg["seconds"]
         if sum(times) > 150:
             break
     steps_done = len(times)
     ms = 1e3 * sum(times) / steps_done
     value = toks / (ms / 1e3)
-    cores = host_threads()
-    sample = f"first {n_sample} of the 64 sentences of the batch per step, rows = {n_sample}*12, all host threads"
+    sample = (f"first {n_sample} of the {sents.n} sentences of the batch per step, one sentence at a time (rows = {c.beam}), "
+              f"all host threads; dense products: {leg['gemm']}")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps_done,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": config_block(c, sents, args.gpus, args.workload),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": leg["cores"], "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "the reference has no CPU forward path and cannot be built here (Boost, GPU-only math); this arm "
-                "times the CPU port of its math (oracle/) on the host cores",
+                "times the CPU restatement of its math (oracle/) in the reference's loop shape on the host cores",
     }
     print(json.dumps(line))
 
@@ -238,20 +255,23 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    rec = {"ms": 0.0, "n": 0, "flops": 0.0}   # decoder LSTM-stack GEMMs while kernel timing is on
+    cls = {}   # kernel class -> [ms, launches] while kernel timing is on
+    rec = {"flops": 0.0}
 
     def step_device():
         """One pass over this rank's batches, ids and outputs resident in HBM."""
-        ms = gms = 0.0
-        gn = 0
+        ms = 0.0
         for b, (d_ids, d_tok, d_len, d_score) in zip(batches, dbuf):
             dec.decode_device(d_ids.data_ptr(), b.off, b.steps, max_len, d_tok.data_ptr(), d_len.data_ptr(), d_score.data_ptr())
             st = dec.stats()
-            ms += st["last_decode_ms"]; gms += st["last_gemm_ms"]; gn += st["last_gemm_launches"]
-            rec["ms"] += st["last_rec_gemm_ms"]; rec["n"] += st["last_rec_gemm_launches"]; rec["flops"] += st["last_rec_gemm_flops"]
-        return ms, gms, gn
+            ms += st["last_decode_ms"]
+            rec["flops"] += st["last_rec_gemm_flops"]
+            for k_, (m_, n_) in dec.kernel_times().items():
+                e = cls.setdefault(k_, [0.0, 0])
+                e[0] += m_; e[1] += n_
+        return ms
 
-    # ---- device-resident leg: `value` (no per-kernel events inside: they cost ~4 % and end the
+    # ---- device-resident leg: `value` (no per-kernel events inside: they cost a few percent and end the
     # overlap of consecutive kernels at every event) ----
     for _ in range(args.warmup):
         step_device()
@@ -261,23 +281,22 @@ def run_ours(args):
     dev_ms = 0.0
     w0 = time.perf_counter()
     for _ in range(args.steps):
-        a, _, _ = step_device()
-        dev_ms += a
+        dev_ms += step_device()
     barrier()
     wall_ms = 1e3 * (time.perf_counter() - w0)
     s1 = dec.stats()
     launches = s1["kernel_launches"] - s0["kernel_launches"]
     toks = sum(emitted_tokens(d[2].cpu().numpy()) for d in dbuf)
     row_steps = s1["decoder_row_steps"] - s0["decoder_row_steps"]
+    sent_steps = s1["sentence_steps"] - s0["sentence_steps"]
 
-    # ---- the same steps once more with CUDA events around every vocabulary GEMM and every
-    # decoder LSTM stack: the roofline figures (clock sampling runs on over this pass) ----
+    # ---- the same steps once more with a CUDA event before every kernel of the decoder steps: the roofline
+    # figures of every kernel class (clock sampling runs on over this pass) ----
     dec.set_kernel_timing(True)
-    rec.update(ms=0.0, n=0, flops=0.0)
-    gemm_ms, gemm_n, timed_ms = 0.0, 0, 0.0
+    cls.clear(); rec["flops"] = 0.0
+    timed_ms = 0.0
     for _ in range(args.steps):
-        a, g, n = step_device()
-        timed_ms += a; gemm_ms += g; gemm_n += n
+        timed_ms += step_device()
     barrier()
     dec.set_kernel_timing(False)
     clocks = clocks_stop(clk_p, clk_path, local) if rank == 0 else None
@@ -300,55 +319,80 @@ def run_ours(args):
     e_toks = sum(emitted_tokens(o["len"]) for o in outs)
     h2d = int(sum(b.ids.nbytes + 4 * 4 * b.n for b in batches))
     d2h = int(sum(o["tok"].nbytes + o["len"].nbytes + o["score"].nbytes + o["vit"].nbytes for o in outs))
+    dec.close()
+
+    strong = None if args.no_strong_c3 else strong_c3(args, rank, world, local)
 
     # ---- reduce over ranks: max time, summed tokens ----
-    vals = torch.tensor([dev_ms, wall_ms, e2e_wall_ms, gemm_ms], dtype=torch.float64, device=dev)
+    vals = torch.tensor([dev_ms, wall_ms, e2e_wall_ms], dtype=torch.float64, device=dev)
     n_sent_local = sum(b.n for b in batches)
     positions_local = int(sum(int((b.steps + 1).sum()) for b in batches))
-    sums = torch.tensor([toks, e_toks, launches, row_steps, gemm_n, n_sent_local], dtype=torch.float64, device=dev)
+    sums = torch.tensor([toks, e_toks, launches, row_steps, n_sent_local], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    dev_ms_local = dev_ms
-    dev_ms, wall_ms, e2e_wall_ms, gemm_ms_max = vals.tolist()
-    toks_all, e_toks_all, launches_all, row_steps_all, gemm_n_all, n_sent_all = sums.tolist()
+    dev_ms, wall_ms, e2e_wall_ms = vals.tolist()
+    toks_all, e_toks_all, launches_all, row_steps_all, n_sent_all = sums.tolist()
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
         value = toks_all * args.steps / (dev_ms / 1e3)
         e2e_value = e_toks_all * args.steps / (e2e_wall_ms / 1e3)
-        # roofline of the dominant kernel (the vocabulary GEMM): algorithmic FLOPs = 2 * rows * H * V per member
-        H, V = c.desc.H, c.desc.V
-        flops_local = 2.0 * (s1["decoder_row_steps"] - s0["decoder_row_steps"]) * H * V * len(blobs)
-        peak, peak_src = peaks()
+        H, V, L = c.desc.H, c.desc.V, c.desc.L
+        Hp = (H + 63) // 64 * 64
+        M = len(blobs)
+        tf_peak, hbm_peak, peak_src = peaks()
         tensor = args.gemm_path != "simt"
         fp32 = c.precision != "bf16"
+        nt = 2 if fp32 else 1                                     # 16-bit planes per operand on the tensor path
+        gate_products = ({"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1) if tensor else 0
+        voc_products = ((4 if args.gemm_path in ("tensor2", "tensor3") else
+                         (1 if args.gemm_path in ("tensor_v16", "tensor_v16x", "auto") and M == 1 else 3)) if fp32 else 1) if tensor else 0
+        note = ("launch durations from a second pass over the same steps with a CUDA event before every kernel (the pass "
+                "timed for `value` carries none); an event costs a few microseconds per launch and ends the overlap of "
+                "consecutive kernels, so these durations are upper bounds. achieved = ALGORITHMIC flops or bytes; on the "
+                "fp32 tensor path every product is computed as `products_per_product` 16-bit partial products, which is "
+                "what tensor_pipe_* counts")
+        total_cls_ms = sum(v[0] for v in cls.values()) or 1.0
 
-        def roof(kernel, flops, ms, n, products, traffic):
-            """Roofline block of one GEMM class: algorithmic flops over the CUDA-event time of its launches."""
-            ach = flops / (ms / 1e3) / 1e12 if ms > 0 else None
-            return {"bound": "tensor", "kernel": kernel, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                    "frac": (ach / peak) if ach else None, "traffic": traffic, "peak_source": peak_src,
-                    "launches": int(n), "avg_launch_ms": ms / max(n, 1), "share_of_step": ms / timed_ms if timed_ms else None,
-                    "bf16_products_per_product": products if tensor else 0,
-                    "tensor_pipe_tflops": ach * products if (ach and tensor) else None,
-                    "tensor_pipe_frac": ach * products / peak if (ach and tensor) else None,
-                    "note": "launch durations by CUDA events in a second pass over the same steps (the timed pass for `value` carries no per-kernel events); achieved = algorithmic fp32 flops; on the fp32 tensor path every product is computed as "
-                            "this many bf16 partial products (operands split into bf16 planes), which is what "
-                            "tensor_pipe_* counts; the bf16 path runs 1"}
+        def roof(key, kernel, bound, work, products=0):
+            """Roofline block of one kernel class: algorithmic flops (tensor) or bytes (hbm) of the timed pass over
+            the CUDA-event time of the class's launches."""
+            ms, n = cls.get(key, [0.0, 0])
+            if not n:
+                return None
+            peak = tf_peak if bound == "tensor" else hbm_peak
+            ach = work / (ms / 1e3) / (1e12 if bound == "tensor" else 1e9)
+            blk = {"bound": bound, "kernel": kernel, "achieved": ach, "peak": peak, "unit": "TFLOP/s" if bound == "tensor" else "GB/s",
+                   "frac": ach / peak, "traffic": C2_TRAFFIC_BYTES.get(key) if name == "C2" and args.gemm_path == "auto" and fp32 else None,
+                   "peak_source": peak_src, "launches": int(n), "avg_launch_ms": ms / n, "share_of_step": ms / total_cls_ms}
+            if bound == "tensor":
+                blk.update({"products_per_product": products, "tensor_pipe_tflops": ach * products if tensor else None,
+                            "tensor_pipe_frac": ach * products / peak if tensor else None})
+            return blk
 
-        r_voc = roof("vocabulary GEMM [rows,H]x[H,V] (" + args.gemm_path + " path; the default computes it as one fp16 product and recomputes the top candidates in the softmax kernel)", flops_local, gemm_ms, gemm_n,
-                     (4 if args.gemm_path in ("tensor2", "tensor3") else (1 if args.gemm_path in ("tensor_v16", "tensor_v16x", "auto") and len(blobs) == 1 else 3)) if fp32 else 1, VOCAB_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path == "tensor" else None)
-        r_rec = roof("decoder LSTM gate GEMMs [rows,2H|3H]x[.,4H], fused cell update (" + args.gemm_path + " path)",
-                     rec["flops"], rec["ms"], rec["n"],
-                     {"tensor2": 4, "tensor3": 6}.get(args.gemm_path, 3) if fp32 else 1,
-                     GATE_GEMM_TRAFFIC_BYTES if name == "C2" and fp32 and args.gemm_path in ("auto", "tensor") else None)
-        dominant, other = (r_rec, r_voc) if rec["ms"] >= gemm_ms else (r_voc, r_rec)
+        rs, ss = float(row_steps) , float(sent_steps)   # decoder forwards of a row / of a sentence in the timed pass
+        blocks = [
+            roof("lstm_gemm", f"decoder LSTM gate GEMMs [rows,2H]x[2H,4H] with the cell update in the epilogue ({args.gemm_path} path)",
+                 "tensor", rec["flops"], gate_products),
+            roof("vocab_gemm", f"vocabulary GEMM [rows,H]x[H,V] ({args.gemm_path} path)", "tensor", 2.0 * rs * H * V * M, voc_products),
+            roof("attn_proj_gemm", "attention projections GEMM [rows,H]x[H,3H] (W_p | W_a^T | W_c2)", "tensor", 2.0 * rs * H * 3 * H * M, gate_products),
+            roof("attn_out_gemm", "attention output GEMM [rows,H]x[H,H] (W_c1) + tanh", "tensor", 2.0 * rs * H * H * M, gate_products),
+            roof("softmax_topk", "log-softmax statistics + per-row top-(k+1), one pass over the logits", "hbm", rs * V * 4.0),
+            roof("ensemble_combine", "ensemble combination of the members' distributions", "hbm", rs * V * 4.0 * (M + 1)),
+            roof("gather", "beam reordering of the recurrent state (h planes of every layer, attentional state)", "hbm",
+                 rs * (L + 1) * nt * Hp * 2.0 * 2 * M),
+            roof("attention", "attention: p_t, window scores, softmax x Gaussian, context", "hbm",
+                 (ss * 21 * Hp * 4.0 + rs * (3 * Hp * 4.0 + nt * Hp * 2.0)) * M),
+            roof("beam_select", "beam selection (k(k+1) candidates per sentence)", "hbm", rs * (c.beam + 1) * 8.0),
+        ]
+        blocks = [b_ for b_ in blocks if b_]
+        blocks.sort(key=lambda b_: -b_["share_of_step"])
+        dominant, others = blocks[0], blocks[1:]
+        dominant["note"] = note
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            v, secs, ns, cores = cpu_leg(c, blobs, batches[0], 16, ensemble=ensemble)
-            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"first {ns} sentences of the first batch, batched (rows = {ns}*{c.beam}), {secs:.1f} s of CPU work"}
+            cpu = cpu_baseline_block(c, blobs, batches[0], ensemble)
         scaling = WORKLOADS[name][1]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -361,13 +405,90 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_wall_ms / args.steps},
             "gpu_launches": int(launches_all),
-            "roofline": dominant, "roofline_other": [other],
+            "roofline": dominant, "roofline_other": others,
             "cpu_baseline": cpu, "clocks": clocks, "gemm_path": args.gemm_path,
+            "strong_c3": strong,
         }
         print(json.dumps(line))
-    dec.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def strong_c3(args, rank, world, local):
+    """The fixed job of the throughput configuration, strong-scaled: 4096 sentences of 10 to 80 words, bf16 weights,
+    beam 12, length-bucketed batches of 128 dealt to the ranks by decoder forwards (shard.partition), every rank
+    decoding its share on its own replica, and ONE gather of the hypotheses to rank 0 at the end -- all inside the
+    timed region.  Rank 0 then decodes the whole job alone, so the speed-up is measured within this run."""
+    import torch
+    import torch.distributed as dist
+    from linmt_b200 import decoder, shard
+    c = synth.configs()["C3"]
+    allsents = c.sentences(args.c3_sentences)
+    batch = WORKLOADS["C3"][0]
+    blobs = c.blobs()
+    Tm = int(allsents.steps.max())
+    dec = decoder.Decoder(c.desc, blobs, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta, attention=c.attention,
+                          precision="bf16", max_batch=batch, max_src_len=int(allsents.lengths().max()), max_steps=Tm, device=local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def run(parts_of_rank):
+        mine = parts_of_rank
+        sub = allsents.subset(mine)
+        results, dev_ms = {}, 0.0
+        for b in shard.batches_by_length(sub, batch):
+            hb = sub.subset(b)
+            o = dec.decode(hb)
+            dev_ms += dec.stats()["last_decode_ms"]
+            for j, i in enumerate(b):
+                n = int(o["len"][j, 0])
+                results[int(mine[i])] = (o["tok"][j, 0, :n].tolist(), float(o["score"][j, 0]))
+        return results, dev_ms
+
+    parts = shard.partition(allsents, world, batch)
+    run(parts[rank][:batch])   # warm-up: one batch
+    barrier()
+    t0 = time.perf_counter()
+    local_res, local_ms = run(parts[rank])
+    merged = shard.gather_results(local_res, dst=0)
+    barrier()
+    wall = time.perf_counter() - t0
+    fwd = float(sum(int(allsents.steps[i]) + 1 for i in parts[rank]))
+    per = torch.tensor([[fwd, local_ms, float(len(parts[rank]))]], dtype=torch.float64, device=torch.device("cuda", local))
+    if world > 1:
+        allper = [torch.zeros_like(per) for _ in range(world)]
+        dist.all_gather(allper, per)
+        per = torch.cat(allper)
+        wmax = torch.tensor([wall], dtype=torch.float64, device=per.device)
+        dist.all_reduce(wmax, op=dist.ReduceOp.MAX)
+        wall = float(wmax.item())
+    out = None
+    if rank == 0:
+        assert merged is not None and len(merged) == allsents.n
+        toks = sum(max(len(t) - 2, 0) for t, _ in merged.values())
+        out = {"workload": WORKLOADS["C3"][2], "sentences": allsents.n, "tokens": toks, "n_gpus": world,
+               "seconds": wall, "value": toks / wall, "unit": UNIT, "scaling": "strong",
+               "timed_region": "host ids in, every rank's batches, one gather_object of all hypotheses to rank 0",
+               "per_rank": [{"rank": r, "sentences": int(per[r, 2].item()), "decoder_forwards": int(per[r, 0].item()),
+                             "device_ms": float(per[r, 1].item())} for r in range(per.shape[0])]}
+    if world > 1:
+        # the same job on one GPU, within this run: rank 0 alone
+        barrier()
+        if rank == 0:
+            t0 = time.perf_counter()
+            alone, _ = run(list(range(allsents.n)))
+            torch.cuda.synchronize()
+            w1 = time.perf_counter() - t0
+            out["one_gpu_seconds"] = w1
+            out["speedup_over_one_gpu"] = w1 / wall
+            same = sum(1 for i in range(allsents.n) if alone[i][0] == merged[i][0])
+            out["sentences_identical_to_one_gpu"] = same
+        barrier()
+    dec.close()
+    return out
 
 
 def main():
@@ -380,6 +501,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
     ap.add_argument("--precision", default=None, choices=["fp32", "bf16"], help="override the workload's precision")
+    ap.add_argument("--no-strong-c3", action="store_true", help="skip the strong-scaled C3 job reported beside the headline")
+    ap.add_argument("--c3-sentences", type=int, default=4096)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -167,8 +167,8 @@ typedef struct linmt_trace {
   const int32_t* force_parent;
   const float* force_score;
   float* gold_logp;   /* [n][Tm][k]: log p of the forced token of each slot (needs force_*), may be NULL */
-  float* pt;          /* [n][Tm+1][k]: attention centre p_t of every forward (local attention; first ensemble
-                         member), may be NULL.  Entries of forwards that did not run hold the bit pattern 0xffffffff. */
+  float* pt;          /* [n_models][n][Tm+1][k]: attention centre p_t of every forward of every ensemble member (local
+                         attention), may be NULL.  Entries of forwards that did not run hold the bit pattern 0xffffffff. */
 } linmt_trace;
 
 /* Decodes n independent sentences.  Replaces EnsembleFactory<T>::DecodeSentence

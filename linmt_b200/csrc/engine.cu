@@ -456,7 +456,8 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
 // Attention of one decoder forward (both GEMM families).
 int Engine::launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
                              float* ra, int32_t* rl, int32_t* rv) {
-  const AttTrace at{mi == 0 ? trace_dev_.pt : nullptr, d_orig_, trace_dev_.Tm + 1, t};
+  // the record of member mi: [n][Tm+1][k] at pt + mi * (sentences of this device batch's record) * (Tm+1) * k
+  const AttTrace at{trace_dev_.pt ? trace_dev_.pt + (size_t)mi * trace_pt_member_stride_ : nullptr, d_orig_, trace_dev_.Tm + 1, t};
   DevModel& m = models_[mi];
   DevState& s = states_[mi];
   const int ldp = att_merge_ ? 3 * Hp : 2 * Hp;
@@ -698,7 +699,20 @@ int Engine::decode_host(const int32_t* src_ids, const int32_t* src_off, int n, c
       if ((rc = mk(n_s, 4, trace->surv_score ? trace->surv_score + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.surv_score))) return rc;
       if ((rc = mk(n_f, 4, trace->final_logp ? trace->final_logp + (size_t)c0 * k : nullptr, nullptr, (void**)&td.final_logp))) return rc;
       if ((rc = mk(n_s, 4, trace->gold_logp ? trace->gold_logp + (size_t)c0 * Tm_all * k : nullptr, nullptr, (void**)&td.gold_logp))) return rc;
-      if ((rc = mk((size_t)cn * (Tm_all + 1) * k, 4, trace->pt ? trace->pt + (size_t)c0 * (Tm_all + 1) * k : nullptr, nullptr, (void**)&td.pt))) return rc;
+      // p_t: one [cn][Tm+1][k] block per member on the device, copied back member by member into [n_models][n][Tm+1][k]
+      const size_t n_pt = (size_t)cn * (Tm_all + 1) * k;
+      td.pt = nullptr;
+      if (trace->pt) {
+        void* q = nullptr;
+        if (cudaMalloc(&q, std::max<size_t>(n_pt * n_models, 1) * 4) != cudaSuccess) return fail(LINMT_ENOMEM, "trace buffer allocation failed");
+        trace_allocs_.push_back(q);
+        if (cudaMemsetAsync(q, 0xff, n_pt * n_models * 4, stream) != cudaSuccess) return fail(LINMT_ECUDA, "trace clear failed");
+        td.pt = static_cast<float*>(q);
+        trace_pt_member_stride_ = n_pt;
+        for (int mi = 0; mi < n_models; ++mi)
+          copy_back.push_back({td.pt + (size_t)mi * n_pt,
+                               {trace->pt + ((size_t)mi * n + c0) * (Tm_all + 1) * k, n_pt * 4}});
+      }
       if ((rc = mk(n_s, 4, nullptr, trace->force_tok ? trace->force_tok + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_tok))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_parent ? trace->force_parent + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_parent))) return rc;
       if ((rc = mk(n_s, 4, nullptr, trace->force_score ? trace->force_score + (size_t)c0 * Tm_all * k : nullptr, (void**)&td.force_score))) return rc;

@@ -145,6 +145,7 @@ class Engine {
 
   const int32_t* cur_ids_ = nullptr;
   TraceDev trace_dev_{};
+  size_t trace_pt_member_stride_ = 0;   // floats between two members' p_t records in the device trace buffer
   int enc_final_buf_ = 0;
   size_t out_cap_maxlen_ = 0;
   std::vector<DevModel> models_;

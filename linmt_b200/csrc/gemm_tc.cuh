@@ -361,9 +361,9 @@ struct TcEpiLstm {
       *reinterpret_cast<float4*>(c_out + ic) = make_float4(c[0], c[1], c[2], c[3]);
       split_store4(h_out1, nt, i1, h[0], h[1], h[2], h[3]);
       if (h_out2.p[0]) split_store4(h_out2, nt, i2, h[0], h[1], h[2], h[3]);
-      if (h_f32)
+      if (h_f32)   // the value every other consumer of h sees: rounded to bf16 in bf16 precision, as it is with fp32 weights
         *reinterpret_cast<float4*>(h_f32 + (size_t)row * hf_row_stride + j0) =
-            make_float4(h[0], h[1], h[2], h[3]);  // unrounded: attention reads it outside any GEMM
+            make_float4(planes_value(h[0], nt), planes_value(h[1], nt), planes_value(h[2], nt), planes_value(h[3], nt));
     } else {
       *reinterpret_cast<float4*>(c_out + ic) = cp;
       const size_t ip = (size_t)row * h_prev.ld + hp_col0 + j0;
@@ -442,7 +442,9 @@ struct TcEpiLstm {
             h[u] = go * tanh_fast(c[u]);
           }
           *reinterpret_cast<float4*>(cs + lane * 20 + 4 * ci) = make_float4(c[0], c[1], c[2], c[3]);
-          if (h_f32) *reinterpret_cast<float4*>(hf + lane * 20 + 4 * ci) = make_float4(h[0], h[1], h[2], h[3]);
+          if (h_f32)
+            *reinterpret_cast<float4*>(hf + lane * 20 + 4 * ci) =
+                make_float4(planes_value(h[0], nt), planes_value(h[1], nt), planes_value(h[2], nt), planes_value(h[3], nt));
           // planes of h: 4 units = 8 bytes per plane
           unsigned short q0[4], q1[4], q2[4];
 #pragma unroll

@@ -55,6 +55,7 @@ class Decoder:
         if rc != 0:
             raise LinmtError(f"linmt_create_from_weights failed ({rc}): {lib.linmt_last_error(None).decode()}")
         self._h = h
+        self.n_models = len(blobs)
         self.k = lib.linmt_beam(h)
         self.nbest = nbest
         self.max_src_len = max_src_len
@@ -97,7 +98,7 @@ class Decoder:
                             "cand_logp": np.zeros((n, Tm, k, k + 1), np.float32),
                             "surv_tok": np.full((n, Tm, k), -1, np.int32), "surv_parent": np.full((n, Tm, k), -1, np.int32),
                             "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32),
-                            "pt": np.zeros((n, Tm + 1, k), np.float32)})
+                            "pt": np.zeros((self.n_models, n, Tm + 1, k), np.float32)})
                 for f in ("cand_tok", "cand_logp", "surv_tok", "surv_parent", "surv_score", "final_logp", "pt"):
                     setattr(tr, f, out[f].ctypes.data)
             if force is not None:
@@ -109,6 +110,8 @@ class Decoder:
                                           _ptr(out["len"]), _ptr(out["score"]), _ptr(out["vit"]), _ptr(out["align"]),
                                           C.byref(tr) if tr is not None else None)
         self._check(rc, "linmt_decode_batch")
+        if trace and self.n_models == 1:
+            out["pt"] = out["pt"][0]   # one model: [n][Tm+1][k]; ensembles keep the member axis in front
         return out
 
     def decode_device(self, d_ids_ptr, off, steps, max_len, d_tok_ptr, d_len_ptr, d_score_ptr):

@@ -87,6 +87,22 @@ static void gemm_block(float* Y, const float* X, const float* W, int K, int N, i
     for (int v = 0; v < NVEC; ++v) vstore(Y + (size_t)(r0 + r) * ldy + n0 + v * VW, acc[r][v]);
 }
 
+#ifdef LINMT_ORACLE_EIGEN
+}  // namespace
+// Baseline-timing build only: the dense products go through the Eigen headers the reference project ships
+// (package/eigen.tar.gz, Eigen 3.2.92), the library its host code is written with (src/decoder.h:128-199),
+// with Eigen's own OpenMP threading.  Eigen blocks and reorders the sums, so this build's numbers agree with
+// the canonical build only to fp32 rounding: it is timed beside the GPU, never used as the checker.
+#include <Eigen/Dense>
+namespace {
+static void gemm(float* Y, const float* X, const float* W, int R, int K, int N, int ldx, int ldy) {
+  typedef Eigen::Matrix<float, Eigen::Dynamic, Eigen::Dynamic, Eigen::RowMajor> Mat;
+  Eigen::Map<const Mat, 0, Eigen::OuterStride<> > x(X, R, K, Eigen::OuterStride<>(ldx));
+  Eigen::Map<const Mat> w(W, K, N);
+  Eigen::Map<Mat, 0, Eigen::OuterStride<> > y(Y, R, N, Eigen::OuterStride<>(ldy));
+  y.noalias() = x * w;
+}
+#else
 static void gemm(float* Y, const float* X, const float* W, int R, int K, int N, int ldx, int ldy) {
   const int CB = VW * NVEC;
   const int ncb = N / CB;
@@ -110,6 +126,7 @@ static void gemm(float* Y, const float* X, const float* W, int R, int K, int N, 
     }
   }
 }
+#endif
 
 // ---------------------------------------------------------------------------------------
 // Model view over a weight blob.
@@ -512,7 +529,7 @@ void linmt_oracle_softmax_topk(const float* logits, int R, int V, int kk, int32_
 //   tr_surv_tok/tr_surv_parent/tr_surv_score [n_sent][Tm][k]
 //   tr_final_logp [n_sent][k]  logf(p[EOS]) at the extra forward
 //   tr_logp_full  [n_sent][Tm+1][k][V] logf(p) of every forward (small models only)
-//   tr_pt         [n_sent][Tm+1][k] attention centre p_t of member 0 at every forward
+//   tr_pt         [n_models][n_sent][Tm+1][k] attention centre p_t of every member at every forward
 int linmt_oracle_decode(int n_models, const int32_t* desc, const float* const* blobs, size_t blob_n,
                         const void* opts_raw, int n_sent, const int32_t* src_ids, const int32_t* src_off,
                         const int32_t* steps, int32_t* out_tok, int32_t* out_len, float* out_score,
@@ -636,8 +653,10 @@ int linmt_oracle_decode(int n_models, const int32_t* desc, const float* const* b
         }
       }
       if (tr_pt)
-        for (int i = 0; i < n_act; ++i)
-          for (int b = 0; b < k; ++b) tr_pt[((size_t)order[i] * (Tm + 1) + t) * k + b] = runs[0].pt[i * k + b];
+        for (int mi = 0; mi < n_models; ++mi)
+          for (int i = 0; i < n_act; ++i)
+            for (int b = 0; b < k; ++b)
+              tr_pt[(((size_t)mi * n_sent + order[i]) * (Tm + 1) + t) * k + b] = runs[mi].pt[i * k + b];
       if (tr_logp_full) {
         for (int i = 0; i < n_act; ++i)
           for (int b = 0; b < k; ++b) {

@@ -38,6 +38,16 @@ def _has_avx512() -> bool:
     return False
 
 
+_eigen_lib = None
+
+
+def _declare(L):
+    L.linmt_oracle_blob_floats.restype = C.c_size_t
+    L.linmt_oracle_threads.restype = C.c_int
+    L.linmt_oracle_decode.restype = C.c_int
+    return L
+
+
 def lib():
     global _lib
     if _lib is None:
@@ -45,11 +55,19 @@ def lib():
         path = build_oracle.lib_path(variant)
         if not os.path.exists(path):
             build_oracle.build()
-        _lib = C.CDLL(path)
-        _lib.linmt_oracle_blob_floats.restype = C.c_size_t
-        _lib.linmt_oracle_threads.restype = C.c_int
-        _lib.linmt_oracle_decode.restype = C.c_int
+        _lib = _declare(C.CDLL(path))
     return _lib
+
+
+def eigen_lib():
+    """The Eigen-GEMM build (oracle/_ref/, baseline timing only), or None where it was never built."""
+    global _eigen_lib
+    if _eigen_lib is None:
+        path = build_oracle.ref_lib_path("v4" if _has_avx512() else "v3")
+        if not os.path.exists(path):
+            return None
+        _eigen_lib = _declare(C.CDLL(path))
+    return _eigen_lib
 
 
 def _p(a, t):
@@ -77,9 +95,13 @@ def softmax_topk(logits: np.ndarray, kk: int):
 
 def decode(desc, blobs, sents, *, beam, nbest=1, attention="local_p_general", attention_d=10, print_info=0,
            precision="fp32", ensemble="prob_mean", penalty=0.0, diversity=0.0, lp_alpha=0.65, cp_beta=0.0,
-           min_ratio=0.5, group=0, threads=0, trace=False, full_logp=False):
-    """Decode ``sents`` (a ``Sentences``) and return a dict of numpy arrays."""
-    L = lib()
+           min_ratio=0.5, group=0, threads=0, trace=False, full_logp=False, gemm="canonical"):
+    """Decode ``sents`` (a ``Sentences``) and return a dict of numpy arrays.  ``group`` = sentences
+    that advance together (0: all; 1: one sentence at a time, rows = beam, the way the reference's own
+    loop runs, src/decoder.h:1780-1840).  ``gemm="eigen"`` uses the Eigen-GEMM build (timing only)."""
+    L = lib() if gemm == "canonical" else eigen_lib()
+    if L is None:
+        raise RuntimeError("the Eigen-GEMM build of the checker is not there (oracle/_ref/)")
     d = desc.as_array()
     V = int(d[2])
     k = min(beam, int(np.floor(np.sqrt(V))))
@@ -104,7 +126,7 @@ def decode(desc, blobs, sents, *, beam, nbest=1, attention="local_p_general", at
         tr = {"cand_tok": np.full((n, Tm, k, k + 1), -1, np.int32), "cand_logp": np.zeros((n, Tm, k, k + 1), np.float32),
               "surv_tok": np.full((n, Tm, k), -1, np.int32), "surv_parent": np.full((n, Tm, k), -1, np.int32),
               "surv_score": np.zeros((n, Tm, k), np.float32), "final_logp": np.zeros((n, k), np.float32),
-              "pt": np.zeros((n, Tm + 1, k), np.float32)}
+              "pt": np.zeros((len(blobs), n, Tm + 1, k), np.float32)}
     if full_logp:
         tr["logp_full"] = np.zeros((n, Tm + 1, k, V), np.float32)
     rc = L.linmt_oracle_decode(
@@ -118,5 +140,7 @@ def decode(desc, blobs, sents, *, beam, nbest=1, attention="local_p_general", at
         _p(tr.get("logp_full"), C.c_float), _p(tr.get("pt"), C.c_float))
     if rc != 0:
         raise RuntimeError(f"linmt_oracle_decode failed with status {rc}")
+    if "pt" in tr and len(blobs) == 1:
+        tr["pt"] = tr["pt"][0]     # one model: [n][Tm+1][k]; ensembles keep the member axis in front
     out.update(tr)
     return out

@@ -24,3 +24,16 @@ def cuda_lib():
     from linmt_b200 import build, _lib
     build.build()
     return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def cpp_caller(cuda_lib, tmp_path_factory):
+    """tests/cpp/decoder_sentence_main.cpp (the reference's sentence-decoding loop written against
+    include/linmt_decoder_sentence.hpp), compiled and linked against the CUDA library."""
+    import subprocess
+    out = str(tmp_path_factory.mktemp("cpp") / "decoder_sentence_main")
+    libdir = os.path.join(ROOT, "linmt_b200")
+    subprocess.run(["g++", "-std=c++17", "-I" + os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "cpp", "decoder_sentence_main.cpp"), "-o", out,
+                    "-L" + libdir, "-llinmt_decoder", "-Wl,-rpath," + libdir], check=True)
+    return out

@@ -6,7 +6,11 @@ built or run, and ships neither a model nor expected outputs).  Run from the rep
 Writes tests/golden/c1_greedy.npz, c1_beam4.npz and tiny_global.npz, and (about a minute of
 CPU) c2_batch64.npz, the final hypotheses of the whole 64-sentence reference decode
 configuration: inputs are regenerated from seeds by linmt_b200.synth, the files hold the
-expected outputs."""
+expected outputs.  With ``--peaked`` it writes instead the final hypotheses of the "peaked" model
+family (linmt_b200.synth.PEAKED) in fp32 and in the checker's bf16 mode: c2_peaked_{fp32,bf16}.npz
+(the 64 sentences of the reference decode configuration) and c3shape_peaked_{fp32,bf16}.npz (128
+sentences of 10 to 80 words, the batch shape of the throughput configuration); about half an hour of
+CPU on eight cores."""
 import os
 import sys
 
@@ -44,5 +48,20 @@ def main():
     print("c2_batch64", o["len"][:, 0].tolist())
 
 
+def peaked():
+    for name, cfg, n in (("c2_peaked", "C2", 64), ("c3shape_peaked", "C3", 128)):
+        c = synth.configs()[cfg]
+        blob = c.blobs(family="peaked")[0]
+        sents = c.sentences(n)
+        for prec in ("fp32", "bf16"):
+            o = oracle_py.decode(c.desc, [blob], sents, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                                 precision=prec)
+            np.savez_compressed(os.path.join(HERE, f"{name}_{prec}.npz"), tok=o["tok"], len=o["len"], score=o["score"])
+            print(name, prec, o["len"][:, 0].tolist())
+
+
 if __name__ == "__main__":
-    main()
+    if "--peaked" in sys.argv:
+        peaked()
+    else:
+        main()

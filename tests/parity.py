@@ -12,10 +12,9 @@ def hyps(out, i, q=0):
     return list(out["tok"][i, q, :n])
 
 
-def token_identity(a, b, n):
-    """Fraction of sentences whose 1-best token sequences are identical."""
-    same = sum(1 for i in range(n) if hyps(a, i) == hyps(b, i))
-    return same / max(n, 1)
+def _members(pt):
+    """p_t records with the member axis in front: [M][n][T+1][k] (one model: [n][T+1][k] -> [1][n][T+1][k])."""
+    return pt if pt.ndim == 4 else pt[None]
 
 
 def window_flip(pt_e, pt_o, S, D=10, pt_tol=2e-3):
@@ -47,6 +46,14 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
     float64 restatement: 1e-6 at step 0, 1e-4 near step 70, 1e-2 near step 150), so the fp32
     tolerance can only be asked of the first ~60 steps of a long sentence.
 
+    The tolerance of a row's entries is relative to the LARGEST magnitude among the row's k+1 checker
+    log-probabilities: every entry is a difference of logits of the same scale, so its error is
+    commensurate with that scale, not with its own value -- on a peaked row the best candidate's
+    log-probability is close to zero and no fp32 computation holds 1e-4 of THAT.  (On the flat rows of
+    the named configurations all k+1 values are within a few percent of each other and the two readings
+    coincide.)  Where both sides carry ``final_logp`` (log p(EOS) of every beam at the closing forward)
+    it is compared the same way, for the beams still in the comparison, at the row scale of the last step.
+
     Returns (max relative log-prob error, mismatches that are not near-ties, row-steps left out,
     row-steps compared)."""
     n, Tm, k, kk = ora["cand_tok"].shape
@@ -60,12 +67,14 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
         for t in range(int(steps[i])):
             if ept is not None:
                 S = int(src_len[i]) if src_len is not None else 10 ** 9
-                taint = taint | window_flip(ept[i, t], pt[i, t], S, D)
+                for pe_, po_ in zip(_members(ept), _members(pt)):   # any member of an ensemble
+                    taint = taint | window_flip(pe_[i, t], po_[i, t], S, D)
             elif pt is not None:
-                nn = np.round(pt[i, t])
-                frac = np.abs(pt[i, t] - nn)
                 S = int(src_len[i]) if src_len is not None else 10 ** 9
-                taint = taint | ((frac < pt_eps) & ((nn > D) | (nn + D < S)))
+                for po_ in _members(pt):
+                    nn = np.round(po_[i, t])
+                    frac = np.abs(po_[i, t] - nn)
+                    taint = taint | ((frac < pt_eps) & ((nn > D) | (nn + D < S)))
             cols = 1 if t == 0 else k
             if t < t_lo or (t_hi is not None and t >= t_hi):
                 cols = 0
@@ -76,7 +85,8 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
                 compared += 1
                 lo, le = ora["cand_logp"][i, t, b], eng["cand_logp"][i, t, b]
                 to, te = ora["cand_tok"][i, t, b], eng["cand_tok"][i, t, b]
-                err = np.abs(lo - le) / np.maximum(np.abs(lo), 1e-6)
+                scale = max(float(np.abs(lo[np.isfinite(lo)]).max()), 1e-6)
+                err = np.abs(lo - le) / scale
                 tol_hit = (err <= rtol) | (np.abs(lo - le) <= atol)
                 worst = max(worst, float(err.max()))
                 bad += int((~tol_hit).sum())
@@ -85,27 +95,47 @@ def compare_forced(eng, ora, steps, rtol=RTOL_FP32, atol=0.0, pt_eps=5e-4, src_l
                     for q in np.nonzero(to != te)[0]:
                         gap_ok = False
                         for q2 in range(kk):
-                            if te[q] == to[q2] and abs(lo[q2] - lo[q]) <= max(rtol * abs(lo[q]), atol) * 2:
+                            if te[q] == to[q2] and abs(lo[q2] - lo[q]) <= max(rtol * scale, atol) * 2:
                                 gap_ok = True
                         if not gap_ok:
                             # another token of the same value at the same rank: a tie, or (last slots) a
                             # token from just beyond the other side's list on a nearly flat distribution
-                            gap_ok = abs(le[q] - lo[q]) <= max(rtol * abs(lo[q]), atol) * 2
+                            gap_ok = abs(le[q] - lo[q]) <= max(rtol * scale, atol) * 2
                         if not gap_ok:
                             bad += 1
             # survivors inherit the taint of their parent (all k slots start identical at step 0)
             par = ora["surv_parent"][i, t]
             taint = taint[np.clip(par, 0, k - 1)] if t > 0 else np.repeat(taint[0], k)
+        T = int(steps[i])
+        if "final_logp" in ora and "final_logp" in eng and ora["final_logp"] is not None and T > 0 and (t_hi is None or T < t_hi) and T >= t_lo:
+            if ept is not None:
+                S = int(src_len[i]) if src_len is not None else 10 ** 9
+                for pe_, po_ in zip(_members(ept), _members(pt)):
+                    taint = taint | window_flip(pe_[i, T], po_[i, T], S, D)
+            fo, fe = ora["final_logp"][i], eng["final_logp"][i]
+            # the scale of the closing forward's rows: the largest candidate magnitude of the last expansion
+            scale = max(float(np.abs(ora["cand_logp"][i, T - 1][np.isfinite(ora["cand_logp"][i, T - 1])]).max()), float(np.abs(fo).max()), 1e-6)
+            for b in range(k):
+                if taint[b]:
+                    skipped += 1
+                    continue
+                compared += 1
+                e_ = abs(float(fo[b]) - float(fe[b]))
+                worst = max(worst, e_ / scale)
+                if e_ > rtol * scale and e_ > atol:
+                    bad += 1
     return worst, bad, skipped, compared
 
 
-def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10):
+def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10, atol_step=0.0):
     """Free-running engine output against the checker's trace of the same decode: every sentence
     whose 1-best differs must part ways with the checker at a choice that is a tie within
     tolerance in the checker's OWN numbers -- the engine's survivor of some rank is a candidate the
     checker scored within ``rtol`` (relative to the score) of the checker's survivor of that rank
     -- or after a local-attention window was cut on the other side of an integer (``window_flip``).
-    Anything else is returned as unexplained.
+    Anything else is returned as unexplained.  ``atol_step`` widens the tie criterion by that much per
+    decoder step taken (the bf16 bar is an absolute tolerance per step's log-probabilities, and a
+    score is their sum).
 
     ``free`` needs the engine's trace (surv_tok, surv_parent, surv_score, pt), ``ora`` the
     checker's (cand_tok, cand_logp, surv_*, pt).  Returns (identical, explained, unexplained)
@@ -122,7 +152,8 @@ def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10):
         flipped = np.zeros(k, bool)   # engine slot descends from a forward with a window flip
         for t in range(T):
             if has_pt:
-                flipped = flipped | window_flip(free["pt"][i, t], ora["pt"][i, t], S, D)
+                for pe_, po_ in zip(_members(free["pt"]), _members(ora["pt"])):
+                    flipped = flipped | window_flip(pe_[i, t], po_[i, t], S, D)
             et, ep = free["surv_tok"][i, t], free["surv_parent"][i, t]
             ot, op, osc = ora["surv_tok"][i, t], ora["surv_parent"][i, t], ora["surv_score"][i, t]
             if (et == ot).all() and (ep == op).all():
@@ -144,7 +175,7 @@ def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10):
                     ok = False
                     break
                 sc = prev[b] + ora["cand_logp"][i, t, b, hit[0]]
-                if abs(sc - osc[r]) > rtol * abs(osc[r]):
+                if abs(sc - osc[r]) > rtol * abs(osc[r]) + atol_step * (t + 1):
                     ok = False
                     break
             reason = (i, t, "tie within tolerance") if ok else None
@@ -155,7 +186,7 @@ def explain_divergences(free, ora, sents, k, rtol=RTOL_FP32, D=10):
             # the beams agree at every step: the finished lists can still order two hypotheses of (nearly) the
             # same final score differently
             a, b = float(free["score"][i, 0]), float(ora["score"][i, 0])
-            if abs(a - b) <= rtol * abs(b):
+            if abs(a - b) <= rtol * abs(b) + atol_step * (T + 1):
                 reason = (i, T, "final scores tie")
             else:
                 unexplained.append((i, T))

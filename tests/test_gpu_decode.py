@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from linmt_b200 import synth
-from parity import RTOL_FP32, compare_forced, hyps, token_identity
+from parity import RTOL_FP32, compare_forced, explain_divergences, hyps
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -43,8 +43,10 @@ def test_c1_against_golden_and_checker(oracle, cuda_lib, c1, case, kw):
     assert worst <= RTOL_FP32 and bad == 0, (worst, bad)
     np.testing.assert_allclose(forced["final_logp"], g["final_logp"], rtol=RTOL_FP32)
     free = dec.decode(sents, trace=True)
-    same = token_identity(free, {"tok": g["tok"], "len": g["len"]}, sents.n)
-    assert same >= 0.75, same
+    # free-running: token-identical, or parting from the fixture at a tie within tolerance in the fixture's own scores
+    gd = {k: g[k] for k in g.files}
+    _, explained, unexplained = explain_divergences(free, gd, sents, int(forced["k"]))
+    assert not unexplained, (unexplained, explained)
     for i in range(sents.n):
         if hyps(free, i) == list(g["tok"][i, 0, :g["len"][i, 0]]):
             np.testing.assert_allclose(free["score"][i, 0], g["score"][i, 0], rtol=RTOL_FP32)
@@ -98,8 +100,9 @@ def test_ragged_batches_and_chunking(oracle, cuda_lib):
     forced = dec.decode(sents, trace=True, force=o)
     worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
     assert worst <= RTOL_FP32 and bad == 0 and skipped <= 0.1 * (skipped + compared), (worst, bad, skipped, compared)
-    free = dec.decode(sents)
-    assert token_identity(free, o, sents.n) >= 0.7
+    free = dec.decode(sents, trace=True)
+    _, explained, unexplained = explain_divergences(free, o, sents, 3)
+    assert not unexplained, (unexplained, explained)
     assert (free["len"][:, 0] == o["len"][:, 0]).all()
     dec.close()
 
@@ -136,8 +139,9 @@ def test_c2_shape_subset(oracle, cuda_lib, gemm_path):
     rtol = 1e-3 if gemm_path == "tensor2" else (3e-4 if gemm_path == "tensor_v16" else RTOL_FP32)
     worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, rtol=rtol, src_len=sents.lengths())
     assert worst <= rtol and bad == 0 and skipped <= 0.1 * (skipped + compared), (worst, bad, skipped, compared)
-    free = dec.decode(sents)
-    assert token_identity(free, o, sents.n) >= (0.5 if gemm_path == "tensor_v16" else 0.66)
+    free = dec.decode(sents, trace=True)
+    _, explained, unexplained = explain_divergences(free, o, sents, 12, rtol=rtol)
+    assert not unexplained, (unexplained, explained)
     dec.close()
 
 
@@ -209,28 +213,13 @@ def test_bf16_precision_c2_subset(oracle, cuda_lib, attention):
     dec.close()
 
 
-def test_bf16_against_fp32_token_identity(oracle, cuda_lib):
-    """The bf16 engine against the fp32 checker on a small model: nearly all sentences decode to
-    the same tokens (the bar for bf16 is 98% on the large configurations; 24 sentences here)."""
-    c = synth.configs()["C1"]
-    blob = c.blobs()[0]
-    sents = c.sentences(24)
-    kw = dict(beam=4, nbest=1, cp_beta=0.0)
-    o = oracle.decode(c.desc, [blob], sents, precision="bf16", **kw)
-    from linmt_b200 import decoder
-    dec = decoder.Decoder(c.desc, [blob], max_batch=24, max_src_len=32, max_steps=64, precision="bf16", **kw)
-    e = dec.decode(sents)
-    assert (e["len"][:, 0] == o["len"][:, 0]).all()
-    dec.close()
-
-
-@pytest.mark.parametrize("gemm_path,min_identical", [("auto", 0.95), ("tensor", 0.95), ("simt", 0.85)])
-def test_c2_whole_batch_against_golden(cuda_lib, gemm_path, min_identical):
+@pytest.mark.parametrize("gemm_path", ["auto", "simt"])
+def test_c2_whole_batch_against_golden(cuda_lib, gemm_path):
     """The reference decode configuration at full size (64 sentences, beam 12, 4 x 1000, 30k
-    vocabulary), free-running, against the checker's committed hypotheses: token-identical 1-best
-    for nearly every sentence (measured: 63-64 of 64 on the tensor-core path depending on the
-    rounding of the epilogue's activation functions, 60/64 on the CUDA-core path, whose longer fp32
-    FMA chains are slightly noisier), scores within 1e-4 where identical."""
+    vocabulary), free-running, pinned to the checker's committed hypotheses: same lengths, scores within
+    1e-4 wherever the tokens are identical, and the same bits on a second decode.  (Which sentences are
+    identical, and why the others are not, is test_gpu_parity_bars.py's business: it has the checker's
+    trace.)"""
     from linmt_b200 import decoder
     c = synth.configs()["C2"]
     g = np.load(os.path.join(GOLD, "c2_batch64.npz"))
@@ -239,7 +228,6 @@ def test_c2_whole_batch_against_golden(cuda_lib, gemm_path, min_identical):
                           max_batch=64, max_src_len=64, max_steps=100, gemm_path=gemm_path)
     out = dec.decode(sents)
     gold = {"tok": g["tok"], "len": g["len"]}
-    assert token_identity(out, gold, sents.n) >= min_identical
     assert (out["len"][:, 0] == g["len"][:, 0]).all()
     for i in range(sents.n):
         if hyps(out, i) == hyps(gold, i):
@@ -265,8 +253,9 @@ def test_ensemble_of_three(oracle, cuda_lib, c1, mode, gemm_path):
     worst, bad, skipped, compared = compare_forced(forced, o, sents.steps, src_len=sents.lengths())
     assert worst <= RTOL_FP32 and bad == 0, (worst, bad, skipped, compared)
     np.testing.assert_allclose(forced["final_logp"], o["final_logp"], rtol=RTOL_FP32)
-    free = dec.decode(sents)
-    assert token_identity(free, o, sents.n) >= 0.75
+    free = dec.decode(sents, trace=True)
+    _, explained, unexplained = explain_divergences(free, o, sents, 4)
+    assert not unexplained, (unexplained, explained)
     dec.close()
     # a one-member "ensemble" of the reference's rule equals the plain decode
     if mode == "prob_mean":
@@ -458,3 +447,51 @@ def test_odd_shapes_against_checker(oracle, cuda_lib, L, H, V, Vs, beam, att, ge
     free = dec.decode(sents)
     assert (free["len"][:, 0] > 0).all() and np.isfinite(free["score"][:, 0]).all()
     dec.close()
+
+
+def test_cpp_decoder_sentence_class(oracle, cuda_lib, cpp_caller, tmp_path):
+    """The reference's C++ sentence-decoding loop (Dispatcher::DecodingSentence, src/dispatcher.cu:439-476)
+    compiled against include/linmt_decoder_sentence.hpp: "[n] translation" lines equal to what the Python
+    mirror of the same class returns."""
+    import subprocess
+    from linmt_b200 import decoder, modelfile
+    d = synth.ModelDesc(2, 32, 60, 50, 1)
+    blob = synth.make_blob(d, 4)
+    mp, cp = tmp_path / "model.nmt", tmp_path / "dec.config"
+    modelfile.write_model(str(mp), d, blob, binary=True)
+    modelfile.write_config(str(cp), [str(mp)], beam_size=3, nbest=1, longest_sent=30, lp_alpha=0.65, cp_beta=0.2,
+                           print_decoding_info=1)
+    src = modelfile.default_vocab(d.Vs, "src")
+    lines = [" ".join(src[i] for i in ids) for ids in ((5, 9, 1, 33, 7), (2, 2, 40, 11, 3, 8, 19), (14,))]
+    (tmp_path / "in.txt").write_text("\n".join(lines) + "\n")
+    r = subprocess.run([cpp_caller, str(cp), str(tmp_path / "in.txt"), str(tmp_path / "out.txt")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    got = (tmp_path / "out.txt").read_text().split("\n")
+    ds = decoder.DecoderSentence()
+    ds.Init(str(cp))
+    for n, line in enumerate(lines):
+        assert got[n] == f"[{n + 1}] " + ds.Process(line)
+    ds.close()
+
+
+@pytest.mark.skipif("__import__('torch').cuda.device_count() < 2")
+def test_two_devices_in_one_process(oracle, cuda_lib):
+    """One handle on devices 0 and 1 (a replica each, one host thread per device inside the library): a
+    job of five device batches comes back in the caller's order with the tokens and the score bits of the
+    one-device decode; and a second handle on device 1 alone works beside one on device 0."""
+    from linmt_b200 import decoder
+    c = synth.configs()["C1"]
+    blob = c.blobs()[0]
+    sents = c.sentences(37)
+    kw = dict(beam=4, nbest=2, cp_beta=0.2, print_info=1, max_batch=8, max_src_len=32, max_steps=64)
+    one = decoder.Decoder(c.desc, [blob], **kw)
+    ref = one.decode(sents)
+    two = decoder.Decoder(c.desc, [blob], devices=[0, 1], **kw)
+    assert two._lib.linmt_device_count(two._h) == 2
+    out = two.decode(sents)
+    for key in ("tok", "len", "score", "vit"):
+        assert (out[key] == ref[key]).all(), key
+    other = decoder.Decoder(c.desc, [blob], device=1, **kw)
+    out1 = other.decode(sents)
+    assert (out1["tok"] == ref["tok"]).all() and (out1["score"] == ref["score"]).all()
+    one.close(); two.close(); other.close()

@@ -165,3 +165,31 @@ def test_text_model_reader_and_cache(tmp_path):
     assert (gotb == blob).all()
     with pytest.raises(RuntimeError):
         modelfile.read_model(str(tmp_path / "missing.nmt"))
+
+
+def test_cpp_decoder_sentence_class_reports_init_errors(cpp_caller, tmp_path):
+    """A C++ caller of DecoderSentence::Init / Process (src/decoder_sentence.h:40-41) compiles against
+    include/linmt_decoder_sentence.hpp; a bad config is an error return with the reference's message, not
+    an exit from inside the library."""
+    import subprocess
+    r = subprocess.run([cpp_caller, str(tmp_path / "none.config"), "in", "out"], capture_output=True, text=True)
+    assert r.returncode == 2 and "does not exist" in r.stderr
+    cfg = tmp_path / "a.config"
+    cfg.write_text('param="--beam-size" value="4"\n')
+    r = subprocess.run([cpp_caller, str(cfg), "in", "out"], capture_output=True, text=True)
+    assert r.returncode == 2 and "--nmt-model" in r.stderr
+
+
+def test_multi_device_job_order_and_errors(cuda_lib):
+    """Handles on several devices: argument checks that need no GPU."""
+    from linmt_b200 import _lib
+    d = _lib.ModelDescC(1, 8, 20, 10, 1)
+    o = _lib.OptionsC()
+    cuda_lib.linmt_default_options(C.byref(o))
+    blob = synth.make_blob(synth.ModelDesc(1, 8, 20, 10, 1), 0)
+    arr = (C.c_void_p * 1)(blob.ctypes.data)
+    h = C.c_void_p()
+    devs = np.array([0, 1, 0], np.int32)
+    rc = cuda_lib.linmt_create_from_weights_on(C.byref(d), arr, 1, blob.size, C.byref(o), devs.ctypes.data_as(C.c_void_p), 3, C.byref(h))
+    assert rc == 1 and b"twice" in cuda_lib.linmt_last_error(None)
+    assert cuda_lib.linmt_device_count(None) == 0
