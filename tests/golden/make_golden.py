@@ -10,7 +10,12 @@ expected outputs.  With ``--peaked`` it writes instead the final hypotheses of t
 family (linmt_b200.synth.PEAKED) in fp32 and in the checker's bf16 mode: c2_peaked_{fp32,bf16}.npz
 (the 64 sentences of the reference decode configuration) and c3shape_peaked_{fp32,bf16}.npz (128
 sentences of 10 to 80 words, the batch shape of the throughput configuration); about half an hour of
-CPU on eight cores."""
+CPU on eight cores.  With ``--eigen`` (only where the Eigen-GEMM build of the checker exists, i.e. next to
+the reference tree) it writes what a SECOND CPU build of the same math decodes: the checker with its dense
+products handed to the reference's vendored Eigen, which sums in another order --
+c2_{peaked,flat}_{fp32,bf16}_eigen.npz, and c2_flat_bf16.npz, the canonical checker's bf16 decode of the
+unscaled model.  The tests take from these how often two CPU builds of the reference's math agree with each
+other token by token, which is the level the CUDA engine is held to."""
 import os
 import sys
 
@@ -60,8 +65,24 @@ def peaked():
             print(name, prec, o["len"][:, 0].tolist())
 
 
+def eigen():
+    c = synth.configs()["C2"]
+    sents = c.sentences()
+    kw = dict(beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta)
+    for fam in ("peaked", "flat"):
+        blob = c.blobs(family=fam)[0]
+        for prec in ("fp32", "bf16"):
+            o = oracle_py.decode(c.desc, [blob], sents, precision=prec, gemm="eigen", **kw)
+            np.savez_compressed(os.path.join(HERE, f"c2_{fam}_{prec}_eigen.npz"), tok=o["tok"], len=o["len"], score=o["score"])
+            print("c2", fam, prec, "eigen", o["len"][:, 0].tolist())
+    o = oracle_py.decode(c.desc, [c.blobs()[0]], sents, precision="bf16", **kw)
+    np.savez_compressed(os.path.join(HERE, "c2_flat_bf16.npz"), tok=o["tok"], len=o["len"], score=o["score"])
+
+
 if __name__ == "__main__":
-    if "--peaked" in sys.argv:
+    if "--eigen" in sys.argv:
+        eigen()
+    elif "--peaked" in sys.argv:
         peaked()
     else:
         main()
