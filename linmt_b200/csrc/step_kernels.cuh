@@ -1058,6 +1058,16 @@ static __global__ void __launch_bounds__(128) finalize_kernel(FinalizeArgs a) {
   const int osent = a.orig[sent];
   for (int q = warp; q < a.nbest; q += 4) {
     const size_t ob = (size_t)osent * a.nbest + q;
+    // positions past the hypothesis (all of them when fewer than nbest passed the filter) read START / "no
+    // alignment", so that a result does not carry what an earlier decode left in the buffer
+    const int n_used = (q >= s_nb) ? 0 : ft[s_best[q]] + 2;
+    for (int j = n_used + lane; j < a.max_len; j += 32) {
+      a.out_tok[ob * a.max_len + j] = kStart;
+      if (a.out_vit) a.out_vit[ob * a.max_len + j] = -20;
+    }
+    if (a.out_align)
+      for (size_t j = (size_t)n_used * a.max_src + lane; j < (size_t)a.max_len * a.max_src; j += 32)
+        a.out_align[ob * a.max_len * a.max_src + j] = 0.f;
     if (q >= s_nb) {
       if (lane == 0) { a.out_len[ob] = 0; a.out_score[ob] = 0.f; }
       continue;

@@ -33,14 +33,21 @@ def partition(sents, world: int, batch: int) -> List[List[int]]:
 
 def gather_results(local: Dict[int, object], dst: int = 0):
     """One gather of the per-sentence results to rank ``dst`` (the only collective of a job)."""
-    import torch.distributed as dist
-    if not dist.is_initialized() or dist.get_world_size() == 1:
-        return dict(local)
-    out = [None] * dist.get_world_size() if dist.get_rank() == dst else None
-    dist.gather_object(local, out, dst=dst)
-    if dist.get_rank() != dst:
+    parts = gather_parts(local, dst)
+    if parts is None:
         return None
     merged = {}
-    for part in out:
+    for part in parts:
         merged.update(part)
     return merged
+
+
+def gather_parts(local, dst: int = 0):
+    """The same gather for any picklable per-rank result (e.g. a tuple of numpy arrays: sentence indices,
+    padded token rows, lengths, scores): the list of every rank's part on rank ``dst``, None elsewhere."""
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return [local]
+    out = [None] * dist.get_world_size() if dist.get_rank() == dst else None
+    dist.gather_object(local, out, dst=dst)
+    return out if dist.get_rank() == dst else None
