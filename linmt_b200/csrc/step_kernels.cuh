@@ -688,6 +688,8 @@ inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int k
 // Ensemble of up to 8 members for one row: out[v] = log(mean_m softmax(z_m)[v]) (mode 0, the
 // reference's rule, src/decoder.h:1913-1921 -- its renormalisation, :1923-1931, is the
 // log-softmax the next kernel applies to this row) or mean_m log softmax(z_m)[v] (mode 1).
+// Two sweeps over the members' rows (HBM-bound: each row of logits is read twice, the combined row
+// written once): running (max, sum of exponentials) per member, then the combination.
 // grid = rows, block = 256
 struct EnsembleRows {
   const float* logits[8];
@@ -696,43 +698,81 @@ struct EnsembleRows {
 static __global__ void __launch_bounds__(256) ensemble_combine_kernel(EnsembleRows er, int ld, int V, int mode, float* __restrict__ out) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
-  __shared__ float s_red[8];
+  __shared__ float s_m[8][8], s_s[8][8];   // [member][warp] partial (max, sum of exp relative to it)
   __shared__ float s_max[8], s_lse[8];
   const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int V4 = V & ~3;
+  // one sweep per member: running maximum and sum of exponentials relative to it (16-byte loads, two in flight)
   for (int m = 0; m < er.n; ++m) {
     const float* z = er.logits[m] + (size_t)r * ld;
-    float mx = -INFINITY;
-    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, z[i]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    mx = s_red[0];
-    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_red[w]);
-    __syncthreads();
-    float sum = 0.f;
-    for (int i = tid; i < V; i += 256) sum += expf(z[i] - mx);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) s_red[warp] = sum;
-    __syncthreads();
-    if (tid == 0) {
-      float t = 0.f;
-      for (int w = 0; w < 8; ++w) t += s_red[w];
-      s_max[m] = mx; s_lse[m] = logf(t);
+    float mx = -INFINITY, sum = 0.f;
+    auto take = [&](float x) {
+      if (x > mx) { sum = sum * __expf(mx - x) + 1.0f; mx = x; }
+      else sum += __expf(x - mx);
+    };
+    int i = tid * 4;
+    for (; i + 1024 < V4; i += 2048) {
+      const float4 q0 = *reinterpret_cast<const float4*>(z + i);
+      const float4 q1 = *reinterpret_cast<const float4*>(z + i + 1024);
+      take(q0.x); take(q0.y); take(q0.z); take(q0.w);
+      take(q1.x); take(q1.y); take(q1.z); take(q1.w);
     }
-    __syncthreads();
+    for (; i < V4; i += 1024) {
+      const float4 q = *reinterpret_cast<const float4*>(z + i);
+      take(q.x); take(q.y); take(q.z); take(q.w);
+    }
+    for (int j = V4 + tid; j < V; j += 256) take(z[j]);
+    // combine (max, sum) pairs in a fixed order: lanes by shuffle tree, then the warps one after the other
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+      const float os = __shfl_xor_sync(0xffffffffu, sum, o);
+      const float nm = fmaxf(mx, om);
+      sum = (nm == -INFINITY) ? 0.f : sum * __expf(mx - nm) + os * __expf(om - nm);
+      mx = nm;
+    }
+    if (lane == 0) { s_m[m][warp] = mx; s_s[m][warp] = sum; }
   }
+  __syncthreads();
+  if (tid < er.n) {
+    float mx = s_m[tid][0], sum = s_s[tid][0];
+    for (int w = 1; w < 8; ++w) {
+      const float om = s_m[tid][w], os = s_s[tid][w];
+      const float nm = fmaxf(mx, om);
+      sum = (nm == -INFINITY) ? 0.f : sum * __expf(mx - nm) + os * __expf(om - nm);
+      mx = nm;
+    }
+    s_max[tid] = mx; s_lse[tid] = logf(sum);
+  }
+  __syncthreads();
+  // second sweep: the members' probabilities (or log-probabilities) of four classes at a time, accumulated in
+  // double like the reference's loop (src/decoder.h:1913-1921)
   float* o = out + (size_t)r * ld;
-  for (int i = tid; i < V; i += 256) {
+  const float inv_n = 1.0f / er.n;
+  for (int i = tid * 4; i < V4; i += 1024) {
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    for (int m = 0; m < er.n; ++m) {
+      const float4 q = *reinterpret_cast<const float4*>(er.logits[m] + (size_t)r * ld + i);
+      const float c = s_max[m] + s_lse[m];
+      const float l0 = q.x - c, l1 = q.y - c, l2 = q.z - c, l3 = q.w - c;   // (z - max) - lse up to one rounding
+      if (mode == 0) { a0 += (double)expf(l0); a1 += (double)expf(l1); a2 += (double)expf(l2); a3 += (double)expf(l3); }
+      else { a0 += (double)l0; a1 += (double)l1; a2 += (double)l2; a3 += (double)l3; }
+    }
+    float4 w;
+    if (mode == 0) w = make_float4(logf((float)(a0 / er.n)), logf((float)(a1 / er.n)), logf((float)(a2 / er.n)), logf((float)(a3 / er.n)));
+    else w = make_float4((float)(a0 / er.n), (float)(a1 / er.n), (float)(a2 / er.n), (float)(a3 / er.n));
+    *reinterpret_cast<float4*>(o + i) = w;
+  }
+  for (int j = V4 + tid; j < V; j += 256) {
     double acc = 0.0;
     for (int m = 0; m < er.n; ++m) {
-      const float lp = (er.logits[m][(size_t)r * ld + i] - s_max[m]) - s_lse[m];
+      const float lp = er.logits[m][(size_t)r * ld + j] - (s_max[m] + s_lse[m]);
       acc += (mode == 0) ? (double)expf(lp) : (double)lp;
     }
     acc /= er.n;
-    o[i] = (mode == 0) ? logf((float)acc) : (float)acc;
+    o[j] = (mode == 0) ? logf((float)acc) : (float)acc;
   }
+  (void)inv_n;
 }
 
 // ---------------------------------------------------------------------------------------
