@@ -68,7 +68,9 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     tc::TcEpiF32 e{nullptr, dy.as<float>(), Np, 0};
     int bn = 0, splits = 1;
     const size_t ws_floats = (size_t)16 << 20;
-    tc::pick_shape(R, Np, Kp, nt, 148, ws_floats, 4096, &bn, &splits, fmt);
+    int n_sm = 148;
+    KCK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
+    tc::pick_shape(R, Np, Kp, nt, n_sm, ws_floats, 4096, &bn, &splits, fmt);
     DevBuf dws, dcnt;
     KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
     for (int t = 0; t < nt; ++t)
