@@ -1,6 +1,7 @@
 // engine_tc.cu -- the tensor-core path of the engine: operands as bf16 planes, every GEMM a
 // tcgen05/TMEM kernel fed by TMA, LSTM cell / tanh / bias fused into the epilogues.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "engine.h"
