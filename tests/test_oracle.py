@@ -129,3 +129,37 @@ def test_ensemble_modes(oracle, c1):
     for mode in ("prob_mean", "logprob_mean"):
         two = oracle.decode(c.desc, [blob, blob2], sents, beam=2, trace=True, ensemble=mode)
         assert two["len"][:, 0].min() >= 2
+
+
+@pytest.mark.parametrize("family,precision,fixture", [("peaked", "fp32", "c2_peaked_fp32.npz"), ("peaked", "bf16", "c2_peaked_bf16.npz"),
+                                                       ("flat", "fp32", "c2_batch64.npz")])
+def test_large_fixtures_spot_check(oracle, family, precision, fixture):
+    """The fixtures of the 4 x 1000, 30k-vocabulary configuration hold what the checker decodes today: two of
+    the 64 sentences decoded again (sentences are independent, and grouping rows changes no bit)."""
+    c = synth.configs()["C2"]
+    blob = c.blobs(family=family)[0]
+    pick = [1, 3]                                     # two of the shorter sentences: a few seconds of CPU
+    sents = c.sentences().subset(pick)
+    g = np.load(os.path.join(GOLD, fixture))
+    o = oracle.decode(c.desc, [blob], sents, beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta, precision=precision)
+    for j, i in enumerate(pick):
+        n = int(g["len"][i, 0])
+        assert int(o["len"][j, 0]) == n
+        assert (o["tok"][j, 0, :n] == g["tok"][i, 0, :n]).all()
+        assert o["score"][j, 0] == g["score"][i, 0]
+
+
+def test_second_cpu_build_agrees_to_rounding(oracle):
+    """The Eigen-GEMM build of the checker (another summation order, timing and fixtures only) against the
+    canonical build on the small configuration: same math, log-probabilities equal to fp32 rounding.  Skipped
+    where that build does not exist (it is made only next to the reference tree)."""
+    if oracle.eigen_lib() is None:
+        pytest.skip("no Eigen-GEMM build of the checker on this machine")
+    c = synth.configs()["C1"]
+    blob, sents = c.blobs()[0], c.sentences()
+    a = oracle.decode(c.desc, [blob], sents, beam=4, nbest=1, trace=True)
+    b = oracle.decode(c.desc, [blob], sents, beam=4, nbest=1, trace=True, gemm="eigen")
+    # first step of every sentence: no search decisions yet, the same candidates on both sides
+    np.testing.assert_allclose(a["cand_logp"][:, 0, 0], b["cand_logp"][:, 0, 0], rtol=2e-6, atol=2e-6)
+    same = sum(1 for i in range(sents.n) if list(a["tok"][i, 0, :a["len"][i, 0]]) == list(b["tok"][i, 0, :b["len"][i, 0]]))
+    assert same >= sents.n - 2
