@@ -155,11 +155,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   and the last one takes the vote: the position of the largest summed score, the search starting from
 //   "none, 0" (EnsembleFactory::EnsemblesModels, src/decoder.h:1934-1964).
 // grid = rows, block = 256, dynamic smem = (win + 8) floats.  The kernel is a chain of L2 round trips, not
-// of bytes: loads are issued in batches ahead of the arithmetic.  (Two forms that cut its L2 traffic were
-// tried and measured no faster: the window's states kept in shared memory between the score sweep and the
-// context sweep -- 86 KB per CTA costs the occupancy the halved traffic buys -- and one CTA per group of
-// beams of a sentence reading every state row once for all of them -- a quarter of the CTAs, the same
-// chain of round trips in each.)
+// of bytes.  (Three variations were tried and measured no faster: the window's states kept in shared memory
+// between the score sweep and the context sweep -- 86 KB per CTA costs the occupancy the halved traffic buys;
+// one CTA per group of beams of a sentence reading every state row once for all of them -- a quarter of the
+// CTAs, the same chain of round trips in each; and loads issued in batches of eight ahead of the arithmetic --
+// the registers cost more occupancy than the batching hides latency.)
 // Optional record of the attention centre p_t of every row of a forward (local attention): the parity tests
 // use it to tell a window that was cut on the other side of an integer apart from an error.
 struct AttTrace {
@@ -168,7 +168,7 @@ struct AttTrace {
   int T1;               // forwards per sentence in the record (longest step count + 1)
   int t;                // this forward
 };
-static __global__ void __launch_bounds__(256, 4) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+static __global__ void __launch_bounds__(256, 5) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
@@ -210,19 +210,10 @@ static __global__ void __launch_bounds__(256, 4) attention_kernel(const float* _
   for (int w = warp; w < W; w += nw) {
     const float* hrow = hsb + (size_t)(S - 1 - (lo + w)) * Hp;
     float acc = 0.f;
-    // loads first, four row segments at a time: the kernel is a chain of L2 round trips otherwise
-    for (int j0 = lane * 4; j0 < Hp; j0 += 4 * 128) {
-      float4 a[4], b[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int j = j0 + q * 128;
-        if (j < Hp) { a[q] = *reinterpret_cast<const float4*>(hrow + j); b[q] = *reinterpret_cast<const float4*>(u + j); }
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        if (j0 + q * 128 < Hp) {
-          acc = fmaf(a[q].x, b[q].x, acc); acc = fmaf(a[q].y, b[q].y, acc); acc = fmaf(a[q].z, b[q].z, acc); acc = fmaf(a[q].w, b[q].w, acc);
-        }
+    for (int j = lane * 4; j < Hp; j += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(hrow + j);
+      const float4 b = *reinterpret_cast<const float4*>(u + j);
+      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -291,17 +282,10 @@ static __global__ void __launch_bounds__(256, 4) attention_kernel(const float* _
   float* crow = ctx ? ctx + (size_t)r * Hp : nullptr;
   for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w0 = 0; w0 < W; w0 += 8) {   // eight state rows in flight, added in position order
-      float4 h4[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        if (w0 + q < W) h4[q] = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w0 + q)) * Hp + j);
-#pragma unroll
-      for (int q = 0; q < 8; ++q)
-        if (w0 + q < W) {
-          const float a = e[w0 + q];
-          acc.x += a * h4[q].x; acc.y += a * h4[q].y; acc.z += a * h4[q].z; acc.w += a * h4[q].w;
-        }
+    for (int w = 0; w < W; ++w) {
+      const float a = e[w];
+      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
+      acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
     }
     if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
     if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
@@ -570,27 +554,16 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
       const __half* w0 = rf.b0 + (size_t)v * rf.ldb;
       const __half* w1 = rf.b1 + (size_t)v * rf.ldb;
       float acc = 0.f;
-      // eight loads in flight per lane: the weight rows come from L2 or HBM and a lane has nothing else to do
-      for (int j0 = lane * 4; j0 < rf.K; j0 += 4 * 128) {
-        uint2 q0[4], q1[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * 128;
-          if (j < rf.K) { q0[u] = *reinterpret_cast<const uint2*>(w0 + j); q1[u] = *reinterpret_cast<const uint2*>(w1 + j); }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * 128;
-          if (j < rf.K) {
-            const __half2 h00 = *reinterpret_cast<const __half2*>(&q0[u].x), h01 = *reinterpret_cast<const __half2*>(&q0[u].y);
-            const __half2 h10 = *reinterpret_cast<const __half2*>(&q1[u].x), h11 = *reinterpret_cast<const __half2*>(&q1[u].y);
-            const float2 b00 = __half22float2(h00), b01 = __half22float2(h01), b10 = __half22float2(h10), b11 = __half22float2(h11);
-            acc = fmaf(s_a[j + 0], fmaf(b10.x, kPairInv, b00.x), acc);
-            acc = fmaf(s_a[j + 1], fmaf(b10.y, kPairInv, b00.y), acc);
-            acc = fmaf(s_a[j + 2], fmaf(b11.x, kPairInv, b01.x), acc);
-            acc = fmaf(s_a[j + 3], fmaf(b11.y, kPairInv, b01.y), acc);
-          }
-        }
+      for (int j = lane * 4; j < rf.K; j += 128) {
+        const uint2 q0 = *reinterpret_cast<const uint2*>(w0 + j);
+        const uint2 q1 = *reinterpret_cast<const uint2*>(w1 + j);
+        const __half2 h00 = *reinterpret_cast<const __half2*>(&q0.x), h01 = *reinterpret_cast<const __half2*>(&q0.y);
+        const __half2 h10 = *reinterpret_cast<const __half2*>(&q1.x), h11 = *reinterpret_cast<const __half2*>(&q1.y);
+        const float2 b00 = __half22float2(h00), b01 = __half22float2(h01), b10 = __half22float2(h10), b11 = __half22float2(h11);
+        acc = fmaf(s_a[j + 0], fmaf(b10.x, kPairInv, b00.x), acc);
+        acc = fmaf(s_a[j + 1], fmaf(b10.y, kPairInv, b00.y), acc);
+        acc = fmaf(s_a[j + 2], fmaf(b11.x, kPairInv, b01.x), acc);
+        acc = fmaf(s_a[j + 3], fmaf(b11.y, kPairInv, b01.y), acc);
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
