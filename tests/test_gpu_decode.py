@@ -495,3 +495,29 @@ def test_two_devices_in_one_process(oracle, cuda_lib):
     out1 = other.decode(sents)
     assert (out1["tok"] == ref["tok"]).all() and (out1["score"] == ref["score"]).all()
     one.close(); two.close(); other.close()
+
+
+@pytest.mark.skipif("__import__('torch').cuda.device_count() < 2")
+def test_file_mode_on_two_devices(cuda_lib, tmp_path):
+    """--devices "0 1" in the decoding config: file mode deals its batches to both GPUs and writes the same file
+    as one GPU does."""
+    from linmt_b200 import decoder, modelfile
+    d = synth.ModelDesc(2, 32, 60, 50, 1)
+    blob = synth.make_blob(d, 9)
+    mp = tmp_path / "model.nmt"
+    modelfile.write_model(str(mp), d, blob, binary=True)
+    src = modelfile.default_vocab(d.Vs, "src")
+    rng = np.random.default_rng(8)
+    lines = [" ".join(src[i] for i in rng.integers(1, d.Vs, size=int(n))) for n in rng.integers(2, 20, size=23)]
+    (tmp_path / "in.txt").write_text("\n".join(lines) + "\n")
+    outs = []
+    for name, extra in (("one", {}), ("two", {"devices": "0 1"})):
+        cp = tmp_path / f"{name}.config"
+        modelfile.write_config(str(cp), [str(mp)], beam_size=3, nbest=2, longest_sent=20, lp_alpha=0.65, cp_beta=0.2,
+                               print_decoding_info=1, batch_size=4, **extra)
+        ds = decoder.DecoderSentence()
+        ds.Init(str(cp))
+        ds.DecodeFile(str(tmp_path / "in.txt"), str(tmp_path / f"{name}.out"))
+        ds.close()
+        outs.append((tmp_path / f"{name}.out").read_text())
+    assert outs[0] == outs[1] and outs[0].count("================") == len(lines)
