@@ -60,7 +60,7 @@ WORKLOADS = {
 }
 
 
-def workload(name: str, rank: int, world: int, precision=None):
+def workload(name: str, rank: int, world: int, precision=None, n_sentences=None):
     """Returns (config, list of per-rank batches).  C1/C2 are weak-scaled (every rank decodes its
     own batch of the named distribution); C3-C5 are the named fixed jobs, length-bucketed and
     dealt to the ranks (strong scaling)."""
@@ -72,7 +72,7 @@ def workload(name: str, rank: int, world: int, precision=None):
     if scaling == "weak":
         sents = synth.make_sentences(c.n_sent, c.len_lo, c.len_hi, c.desc.Vs, c.zipf_s, c.seeds[0] + 7919 * rank, c.step_rule)
         return c, [sents]
-    allsents = c.sentences()
+    allsents = c.sentences(n_sentences)   # None = the configuration's own job size
     mine = shard.partition(allsents, world, batch)[rank]
     sub = allsents.subset(mine)
     batches = [sub.subset(b) for b in shard.batches_by_length(sub, batch)]
@@ -235,7 +235,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     name = args.workload
-    c, batches = workload(name, rank, world, args.precision)
+    c, batches = workload(name, rank, world, args.precision, args.sentences)
     blobs = c.blobs()
     max_src = max(int(b.lengths().max()) for b in batches)
     Tm = max(int(b.steps.max()) for b in batches)
@@ -520,6 +520,7 @@ def main():
     ap.add_argument("--precision", default=None, choices=["fp32", "bf16"], help="override the workload's precision")
     ap.add_argument("--no-strong-c3", action="store_true", help="skip the strong-scaled C3 job reported beside the headline")
     ap.add_argument("--c3-sentences", type=int, default=4096)
+    ap.add_argument("--sentences", type=int, default=None, help="cut a fixed job (C3-C5) down to its first N sentences (profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
