@@ -919,25 +919,28 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, 
     }
     __syncthreads();
     if (s_last && warp >= 2 && warp < kIssue2Warp) {
-      const int q = warp & 3, half = (warp - 2) >> 2;
-      const int row = m0 + q * 32 + lane;
-      if (row < M) {
-        const size_t zstride = (size_t)gridDim.x * BM * (size_t)N;
-        const float* p0 = ws + (size_t)row * (size_t)N + n0;
-        for (int c0 = half * 16; c0 < BN && n0 + c0 < N; c0 += 16 * (kEpiWarps / 4)) {
-          float v[16];
+      // (row, 16-column chunk) items dealt to all epilogue threads: a tile with few valid rows (late decoder
+      // steps) still spreads its chunks over every warp instead of walking them one after the other
+      const int mrows = (M - m0) < BM ? (M - m0) : BM;
+      const int ncols = (N - n0) < BN ? (N - n0) : BN;
+      const int nch = (ncols + 15) >> 4;
+      const size_t zstride = (size_t)gridDim.x * BM * (size_t)N;
+      for (int it = (int)threadIdx.x - 64; it < mrows * nch; it += kEpiWarps * 32) {
+        const int ch = it / mrows, r = it - ch * mrows;
+        const int row = m0 + r, c0 = ch * 16;
+        const float* p0 = ws + (size_t)row * (size_t)N + n0 + c0;
+        float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0.f;
-          for (int z = 0; z < splits; ++z) {
-            const float4* src = reinterpret_cast<const float4*>(p0 + (size_t)z * zstride + c0);
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        for (int z = 0; z < splits; ++z) {
+          const float4* src = reinterpret_cast<const float4*>(p0 + (size_t)z * zstride);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 t = __ldcg(src + i);
-              v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
-            }
+          for (int i = 0; i < 4; ++i) {
+            const float4 t = __ldcg(src + i);
+            v[4 * i] += t.x; v[4 * i + 1] += t.y; v[4 * i + 2] += t.z; v[4 * i + 3] += t.w;
           }
-          epi(row, n0 + c0, v);
         }
+        epi(row, n0 + c0, v);
       }
     }
   }
