@@ -208,6 +208,7 @@ typedef struct linmt_stats {
   float last_rec_gemm_ms;         /* time inside them */
   float last_host_issue_ms;       /* host time spent issuing the decoder steps of the last device batch */
   double last_rec_gemm_flops;     /* their algorithmic flops: 2 * rows * 4H * K per launch */
+  int64_t pair_launches;          /* GEMM launches, of kernel_launches, that ran on CTA pairs (tcgen05 cta_group::2) */
 } linmt_stats;
 int linmt_get_stats(const linmt_engine* e, linmt_stats* out);
 /* 1 = put a CUDA event before every kernel of the decoder steps (for roofline measurements).  The events

@@ -31,7 +31,7 @@ class StatsC(C.Structure):
     _fields_ = [("kernel_launches", C.c_int64), ("decoder_row_steps", C.c_int64), ("sentence_steps", C.c_int64),
                 ("last_decode_ms", C.c_float), ("last_gemm_ms", C.c_float), ("last_gemm_launches", C.c_int32),
                 ("last_rec_gemm_launches", C.c_int32), ("last_rec_gemm_ms", C.c_float), ("last_host_issue_ms", C.c_float),
-                ("last_rec_gemm_flops", C.c_double)]
+                ("last_rec_gemm_flops", C.c_double), ("pair_launches", C.c_int64)]
 
 
 EXPORTS = ["python_decoder_init", "python_decoder_do_job", "linmt_default_options", "linmt_blob_floats",

@@ -264,6 +264,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_ATT_MERGE"); att_merge_ = use_tc_ && !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
+  { const char* pe = std::getenv("LINMT_TC_PAIR"); pair_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
   // fp32 weights on the tensor cores: the f16 pair by default (3 partial products), bf16 planes on request
   fmt_ = (o.precision == LINMT_PREC_FP32 && (o.gemm_path == LINMT_GEMM_AUTO || o.gemm_path == LINMT_GEMM_TENSOR || o.gemm_path == LINMT_GEMM_TENSOR_V16 ||
@@ -946,6 +947,7 @@ int linmt_get_stats(const linmt_engine* e, linmt_stats* out) {
   *out = e->eng.stats;
   for (const auto& r : e->replicas) {   // launches and forwards of every device
     out->kernel_launches += r->stats.kernel_launches;
+    out->pair_launches += r->stats.pair_launches;
     out->decoder_row_steps += r->stats.decoder_row_steps;
     out->sentence_steps += r->stats.sentence_steps;
   }

@@ -129,6 +129,7 @@ class Engine {
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
   bool att_merge_ = false; // tensor path: W_c2 . h_top computed with the attention projections (LINMT_ATT_MERGE=0: test knob)
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
+  bool pair_ = true;       // CTA pairs for the GEMM shapes that are down to two stages (LINMT_TC_PAIR=0: test knob)
   bool persist_ = true;    // persistent kernel for the many-wave vocabulary GEMM (LINMT_TC_PERSIST=0: test knob)
   bool pdl_gemm_ = false;  // true while the decoder step issues its GEMMs (the encoder's wavefront does not take part)
   int fmt_ = 0;       // plane format of every operand: 0 = bf16 planes, 1 = f16 pair

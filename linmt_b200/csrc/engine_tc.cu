@@ -6,6 +6,7 @@
 
 #include "engine.h"
 #include "gemm_tc.cuh"
+#include "gemm_tc_pair.cuh"
 #include "step_kernels.cuh"
 
 namespace linmt {
@@ -117,13 +118,19 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   // (vocabulary GEMM: 143 us against 149 us)
   int bk = (nt == 1) ? 64 : 32;
   if (fmt_ == 1 && nt == 2 && K % 64 == 0) bk = (bn >= 240 && (size_t)N * K * 4 > ((size_t)96 << 20)) ? 32 : 64;
+  // CTA pairs (gemm_tc_pair.cuh) where the one-tile shape has room for two stages only: an even number of row
+  // tiles (an odd one is rounded up, which must still fit one wave), split operands, 64-deep stages, K not split
+  const int mt = (M + tc::BM - 1) / tc::BM;
+  const long ntile_cols = (N + bn - 1) / bn;
+  const bool pair = pair_ && fmt_ == 1 && nt == 2 && bk == 64 && splits == 1 && mt >= 2 && bn % 16 == 0 &&
+                    tc::make_shape(bn, nt, bk, fmt_).stages < 3 && (long)((mt + 1) & ~1) * ntile_cols <= n_sm_ && ws_parts_ == 1;
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K, bk);
-  const CUtensorMap* bm = b_maps(W, N, K, bn, bk);
+  const CUtensorMap* bm = b_maps(W, N, K, pair ? bn / 2 : bn, bk);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
   tc::TmapSet tm;
   std::memcpy(tm.a, am, sizeof(tm.a));
   std::memcpy(tm.b, bm, sizeof(tm.b));
-  tc::Shape sh = tc::make_shape(bn, nt, bk, fmt_);
+  tc::Shape sh = pair ? tc::make_shape_pair(bn, nt, bk, fmt_) : tc::make_shape(bn, nt, bk, fmt_);
   sh.splits = splits;
   if (drain > 0) sh.drain = drain;
   sh.pdl = (pdl_ && pdl_gemm_) ? 1 : 0;
@@ -146,6 +153,12 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
     }
     CK(tc::launch_gemm_tc_persist(tm, M, N, K, sh, e, d_tc_err_, stream, n_sm_));
     LAUNCHED();
+    return LINMT_OK;
+  }
+  if (pair) {
+    CK((tc::launch_gemm_tc_pair<2, 64, 1, Epi>(tm, M, N, K, sh, e, d_tc_err_, stream, nullptr, nullptr)));
+    LAUNCHED();
+    ++stats.pair_launches;
     return LINMT_OK;
   }
   CK(tc::launch_gemm_tc(tm, M, N, K, sh, e, d_tc_err_, stream, d_splitk_ws_ + (size_t)ws_part_ * ws_floats,

@@ -424,6 +424,35 @@ def test_launch_variants_give_identical_bits(cuda_lib):
                 assert abs(o["score"][i, 0] - outs[0]["score"][i, 0]) <= 1e-4 * abs(outs[0]["score"][i, 0])
 
 
+def test_cta_pairs_give_the_same_bits(cuda_lib):
+    """At full width (64 sentences x 12 beams = 768 rows = six row tiles) the gate products run on CTA pairs
+    (tcgen05 cta_group::2: each CTA loads half of the weight tile).  The same products accumulate in the same
+    order, so hypotheses and scores must be bit-identical to the one-tile launches (LINMT_TC_PAIR=0)."""
+    from linmt_b200 import decoder
+    c = synth.configs()["C2"]
+    blob = c.blobs()[0]
+    sents = c.sentences()
+    outs, pairs = [], []
+    for env in ({}, {"LINMT_TC_PAIR": "0"}):
+        old = {k: os.environ.get(k) for k in env}
+        os.environ.update(env)
+        try:
+            dec = decoder.Decoder(c.desc, [blob], beam=c.beam, nbest=1, lp_alpha=c.lp_alpha, cp_beta=c.cp_beta,
+                                  max_batch=64, max_src_len=64, max_steps=100)
+            outs.append(dec.decode(sents))
+            pairs.append(dec.stats()["pair_launches"])
+            dec.close()
+        finally:
+            for k, v in old.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+    assert pairs[0] > 0 and pairs[1] == 0, pairs
+    assert (outs[0]["tok"] == outs[1]["tok"]).all() and (outs[0]["len"] == outs[1]["len"]).all()
+    assert (outs[0]["score"] == outs[1]["score"]).all()
+
+
 @pytest.mark.parametrize("L,H,V,Vs,beam,att", [
     (1, 100, 999, 777, 7, "local_p_general"),       # one layer, sizes that are multiples of nothing
     (3, 250, 5003, 4001, 20, "local_p_general"),    # wide beam
