@@ -121,9 +121,19 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   // CTA pairs (gemm_tc_pair.cuh) where the one-tile shape has room for two stages only: an even number of row
   // tiles (an odd one is rounded up, which must still fit one wave), split operands, 64-deep stages, K not split
   const int mt = (M + tc::BM - 1) / tc::BM;
+  // The many-wave one-plane logits GEMM has a persistent pair form as well: worth it for an even number of row tiles
+  // (measured at N = 30016, K = 1024: 56.2 against 61.7 us at 768 rows, 24.5 against 27.7 at 192; an odd number of
+  // row tiles wastes half a pair and loses), with 208-wide tiles.
+  const bool one_plane_logits = nt == 1 && Epi::kHasPmax;   // the fp32-output GEMMs: vocabulary projection
+  bool ppair = false;
+  if (pair_ && persist_ && one_plane_logits && splits == 1 && bk == 64 && mt % 2 == 0 && ws_parts_ == 1 &&
+      (long)mt * ((N + bn - 1) / bn) > n_sm_ && (long)(mt / 2) * ((N + 207) / 208) > n_sm_ / 2) {
+    ppair = true;
+    bn = 208;
+  }
   const long ntile_cols = (N + bn - 1) / bn;
-  const bool pair = pair_ && fmt_ == 1 && nt == 2 && bk == 64 && splits == 1 && mt >= 2 && bn % 16 == 0 &&
-                    tc::make_shape(bn, nt, bk, fmt_).stages < 3 && (long)((mt + 1) & ~1) * ntile_cols <= n_sm_ && ws_parts_ == 1;
+  const bool pair = ppair || (pair_ && fmt_ == 1 && nt == 2 && bk == 64 && splits == 1 && mt >= 2 && bn % 16 == 0 &&
+                    tc::make_shape(bn, nt, bk, fmt_).stages < 3 && (long)((mt + 1) & ~1) * ntile_cols <= n_sm_ && ws_parts_ == 1);
   const CUtensorMap* am = a_maps(A, a_col0, a_rows_cap, K, bk);
   const CUtensorMap* bm = b_maps(W, N, K, pair ? bn / 2 : bn, bk);
   if (!am || !bm) return fail(LINMT_ECUDA, "cuTensorMapEncodeTiled failed");
@@ -144,7 +154,16 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   }
   // many waves of tiles whose leading product is one chain: one persistent CTA per SM
   const long tiles = (long)((M + tc::BM - 1) / tc::BM) * ((N + bn - 1) / bn);
-  const bool one_plane_logits = nt == 1 && Epi::kHasPmax;   // the fp32-output GEMMs: vocabulary projection
+  if (ppair) {
+    const int pdl = sh.pdl;
+    sh = tc::make_shape_persist_pair(bn, nt, bk, fmt_);
+    sh.pdl = pdl;
+    if (fmt_ == 1) CK((tc::launch_gemm_tc_persist_pair<1, 64, 1, Epi>(tm, M, N, K, sh, e, d_tc_err_, stream, n_sm_)));
+    else CK((tc::launch_gemm_tc_persist_pair<1, 64, 0, Epi>(tm, M, N, K, sh, e, d_tc_err_, stream, n_sm_)));
+    LAUNCHED();
+    ++stats.pair_launches;
+    return LINMT_OK;
+  }
   if (persist_ && splits == 1 && tiles > n_sm_ && ((nt == 2 && drain >= K / 32) || one_plane_logits)) {
     if (nt == 1) {
       const int pdl = sh.pdl;

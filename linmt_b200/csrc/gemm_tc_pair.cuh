@@ -356,5 +356,231 @@ inline cudaError_t launch_gemm_tc_pair(const TmapSet& tm, int M, int N, int K, c
                             splits > 1 ? ws : (float*)nullptr, counters);
 }
 
+// ---- persistent form on CTA pairs (many-wave GEMMs: the vocabulary projection) ---------------------------
+// gemm_tc_persist_kernel with every SM pair walking over 256 x BN tiles: pair p takes pair tiles p, p + pairs, ...
+// (row pair fastest); CTA `rank` of the pair owns row tile 2 * (row pair) + rank of each.  Loads, barriers and
+// TMEM hand-over as in gemm_tc_pair_kernel; the tensor core may start the next tile once the epilogue warps of
+// BOTH CTAs have copied their accumulator rows out (they arrive on the leader's barrier).
+inline Shape make_shape_persist_pair(int bn, int nt, int bk, int fmt) {
+  Shape s = make_shape_pair(bn, nt, bk, fmt);
+  if (nt == 1) {
+    const int stg = kEpiWarps * 32 * kPersistStageStride * 4;
+    s.stages = (SMEM_BUDGET - stg) / s.stage_bytes;
+    if (s.stages > kMaxStages) s.stages = kMaxStages;
+    s.smem_bytes = s.stages * s.stage_bytes + stg + 1024 + 256;
+  }
+  return s;
+}
+
+template <int NT, int BKT, int FMT, class Epi>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_persist_pair_kernel(const __grid_constant__ TmapSet tm, int M, int N, int K, int BN, int STAGES, Epi epi,
+                            int* __restrict__ err_flag, int stage_stride) {
+  constexpr int PC = product_code(NT, FMT);
+  constexpr int NP = num_products(PC);
+  constexpr int A_BYTES = BM * BKT * 2;
+  constexpr int BK = BKT;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const int BH = BN >> 1;
+  const int B_BYTES = BH * BK * 2;
+  const int STAGE_BYTES = NT * (A_BYTES + B_BYTES);
+  const int STG_WARP = 32 * stage_stride * 4;
+  const int RING = (stage_stride > 0 ? STAGES * STAGE_BYTES : ring_bytes(STAGES, STAGE_BYTES));
+  const int PRE = RING + kEpiWarps * STG_WARP;
+  const uint32_t bars = base + PRE;   // full[STAGES], empty[STAGES], accum_full, tmem_free
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + PRE + 8 * (2 * STAGES + 3));
+  __shared__ int s_abort;
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int mt = (M + BM - 1) / BM;
+  const int mt2 = (mt + 1) >> 1;                       // row pairs
+  const int ntile = mt2 * ((N + BN - 1) / BN);        // pair tiles
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int nkb = K / BK;
+  const uint32_t accum_full = bars + 8u * (2 * STAGES);
+  const uint32_t tmem_free = accum_full + 8u;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bars + 8u * s, 1); mbar_init(bars + 8u * (STAGES + s), 1); }
+    mbar_init(accum_full, 1);
+    mbar_init(tmem_free, 2 * kEpiWarps);   // both CTAs' epilogue warps (the leader's copy is the one waited on)
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32((const void*)tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    const bool is_a = lane < NT;
+    const int t = is_a ? lane : lane - NT;
+    const CUtensorMap* map = reinterpret_cast<const CUtensorMap*>(&tm) + (is_a ? (t < 3 ? t : 0) : 3 + (t < 3 ? t : 0));
+    const uint32_t dst_off = is_a ? (uint32_t)(t * A_BYTES) : (uint32_t)(NT * A_BYTES + t * B_BYTES);
+    const uint32_t full0 = cluster_map(bars, 0u);
+    const uint32_t tx_bytes = 2u * (uint32_t)STAGE_BYTES;
+    int s = 0; uint32_t ph = 0;
+    pdl_wait();
+    bool live = true;
+    for (int tile = pair; tile < ntile && live; tile += npairs) {
+      const int ycoord = is_a ? ((tile % mt2) * 2 + (int)rank) * BM : (tile / mt2) * BN + (int)rank * BH;
+      for (int kb = 0; kb < nkb; ++kb) {
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(bars + 8u * (STAGES + s), ph ^ 1u, &s_abort) ? 1 : 0;
+          if (ok && leader) mbar_expect_tx(bars + 8u * s, tx_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { live = false; break; }
+        if (lane < 2 * NT) tma_load_2d_pair(base + s * STAGE_BYTES + dst_off, map, kb * BK, ycoord, full0 + 8u * s);
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc(2 * BM, BN, FMT);
+      const uint32_t acc1 = tmem_acc + (uint32_t)acc_stride(BN);
+      const uint64_t bstep = (uint64_t)(B_BYTES >> 4);
+      int s = 0; uint32_t ph = 0;
+      bool live = true;
+      int it = 0;
+      for (int tile = pair; tile < ntile && live; tile += npairs, ++it) {
+        if (it > 0) {
+          if (!mbar_wait(tmem_free, (uint32_t)((it - 1) & 1), &s_abort)) break;
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < nkb; ++kb) {
+          const uint32_t st = base + s * STAGE_BYTES;
+          if (!mbar_wait(bars + 8u * s, ph, &s_abort)) { live = false; break; }
+          tc_fence_after();
+          const uint64_t a0 = make_desc<BKT>(st);
+          const uint64_t b0 = make_desc<BKT>(st + NT * A_BYTES);
+          if (NP > 1) {
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+#pragma unroll
+              for (int p = 0; p < NP - 1; ++p) {
+                const uint64_t ad = a0 + (uint64_t)(((prod_a(PC, p) * A_BYTES) >> 4) + ks * 2);
+                const uint64_t bd = b0 + (uint64_t)prod_b(PC, p) * bstep + (uint64_t)(ks * 2);
+                umma_f16_pair(acc1, ad, bd, idesc, (kb | ks | p) ? 1u : 0u);
+              }
+            }
+          }
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks)
+            umma_f16_pair(tmem_acc, a0 + (uint64_t)(ks * 2), b0 + (uint64_t)(ks * 2), idesc, (kb | ks) ? 1u : 0u);
+          umma_commit_pair(bars + 8u * (STAGES + s));
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (live) umma_commit_pair(accum_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    constexpr int kParts = kEpiWarps / 4;
+    constexpr int kChunks = kEpiBlockChunks;
+    const int part = (warp - 2) >> 2;
+    const int nchunks = BN >> 4;
+    const int cpw = (nchunks + kParts - 1) / kParts;
+    const int ch0 = part * cpw;
+    const uint32_t astride = (uint32_t)acc_stride(BN);
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(ch0 * 16);
+    float* sbuf = reinterpret_cast<float*>(base_ptr + (warp - 2) * kEpiScratchBytes);
+    const uint32_t tmem_free_leader = cluster_map(tmem_free, 0u);
+    pdl_wait();
+    int it = 0;
+    for (int tile = pair; tile < ntile; tile += npairs, ++it) {
+      const int m0 = ((tile % mt2) * 2 + (int)rank) * BM, n0 = (tile / mt2) * BN;
+      const int row0 = m0 + q * 32;
+      int nmine = nchunks - ch0; nmine = nmine < 0 ? 0 : (nmine > cpw ? cpw : nmine);
+      {
+        const int left = (N - (n0 + ch0 * 16) + 15) >> 4;
+        if (left < nmine) nmine = left < 0 ? 0 : left;
+      }
+      if (!mbar_wait_sleepy(accum_full, (uint32_t)(it & 1), &s_abort)) break;
+      tc_fence_after();
+      float macc[kChunks][16];
+#pragma unroll
+      for (int ci = 0; ci < kChunks; ++ci) {
+        if (ci < nmine) {
+          tmem_ld16(lane_base + (uint32_t)(ci * 16), macc[ci]);
+          if (NP > 1) {
+            float sm[16];
+            tmem_ld16(lane_base + astride + (uint32_t)(ci * 16), sm);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) macc[ci][i] += FMT ? sm[i] * kF16PairInvScale : sm[i];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tmem_free_leader);   // the pair's tensor cores may start the next tile
+      const bool last = tile + npairs >= ntile;
+      const int slot = (tile / mt2) * kParts + part;
+      if constexpr (Epi::kHasPmax) {
+        if (stage_stride > 0) {
+          float* own = reinterpret_cast<float*>(base_ptr + RING + (warp - 2) * STG_WARP);
+          float m = -INFINITY;
+#pragma unroll
+          for (int c0 = 0; c0 < kChunks; c0 += 2) {
+            if (c0 < nmine) {
+              const int nc = nmine - c0 < 2 ? nmine - c0 : 2;
+              m = fmaxf(m, epi.stage_store(row0, lane, M, n0 + (ch0 + c0) * 16, nc, macc + c0, own, stage_stride));
+            }
+          }
+          epi.pmax_store(row0 + lane, M, slot, m);
+          continue;
+        }
+      }
+      if (last && Epi::kHasBlock) {
+        // the last tile's accumulators are complete, so neither tensor core reads a ring any more
+        if (nmine > 0) epi.block(row0, lane, M, n0 + ch0 * 16, nmine, macc, sbuf, slot);
+        else if constexpr (Epi::kHasPmax) epi.pmax_store(row0 + lane, M, slot, -INFINITY);
+      } else if constexpr (Epi::kHasPmax) {
+        epi.direct_block(row0 + lane, M, n0 + ch0 * 16, nmine, macc, slot);
+      } else if (row0 + lane < M) {
+#pragma unroll
+        for (int ci = 0; ci < kChunks; ++ci)
+          if (ci < nmine) epi(row0 + lane, n0 + (ch0 + ci) * 16, macc[ci]);
+      }
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc_pair(tmem_acc, TMEM_COLS);
+  if (threadIdx.x == 0 && s_abort) atomicExch(err_flag, 1);
+}
+
+// One cluster of two CTAs per SM pair (at most n_sm / 2 pairs); B tensor maps with a box of bn / 2 rows.
+template <int NT, int BKT, int FMT, class Epi>
+inline cudaError_t launch_gemm_tc_persist_pair(const TmapSet& tm, int M, int N, int K, const Shape& sh, const Epi& epi, int* err_flag,
+                                               cudaStream_t st, int n_sm) {
+  if (K % sh.bk || sh.stages < 2 || sh.bn % 16) return cudaErrorInvalidValue;
+  static bool optin_done[kMaxDevices] = {};
+  if (cudaError_t e = ensure_smem_optin(gemm_tc_persist_pair_kernel<NT, BKT, FMT, Epi>, optin_done); e != cudaSuccess) return e;
+  const int mt2 = ((M + BM - 1) / BM + 1) / 2;
+  const int tiles = mt2 * ((N + sh.bn - 1) / sh.bn);
+  const int pairs = tiles < n_sm / 2 ? tiles : n_sm / 2;
+  const int stride = sh.nt == 1 ? kPersistStageStride : 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = (size_t)sh.smem_bytes; cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = sh.pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_persist_pair_kernel<NT, BKT, FMT, Epi>, tm, M, N, K, sh.bn, sh.stages, epi, err_flag, stride);
+}
+
 }  // namespace tc
 }  // namespace linmt
