@@ -38,8 +38,8 @@ FALLBACK_HBM_GBS = 6650.0
 # ncu captures of this benchmark's own C2 decode (dram__bytes_read.sum + dram__bytes_write.sum of one launch; the
 # summaries with the capture commands are committed with the profiles).  None = no capture for that class.
 C2_TRAFFIC_BYTES = {
-    "lstm_gemm": 43.3e6,        # first layer 45.04 MB (with input-term table rows), the others 42.77 MB
-    "vocab_gemm": 105.8e6,      # 63.45 MB read (the weights) + 42.31 MB written (half of the logits still in L2)
+    "lstm_gemm": 43.5e6,        # first layer 45.74 MB (with input-term table rows), the others 42.72 MB
+    "vocab_gemm": 109.8e6,      # 63.44 MB read (the weights) + 46.33 MB written (half of the logits still in L2)
     "attn_proj_gemm": 15.8e6, "attn_out_gemm": 10.56e6,
     "softmax_topk": 104.8e6,    # the logits once + candidates' weight rows
     "gather": 9.8e6, "attention": 11.36e6, "beam_select": 0.11e6,
