@@ -241,6 +241,8 @@ int Engine::alloc_state(DevState& s) {
   DA(s.proj, 3 * rh); DA(s.ctx, rh);
   DA(s.logits, (size_t)R * Vp);
   DA(s.hs, (size_t)B * opt.max_src_len * Hp);
+  CK(cudaMemset(s.hs, 0, sizeof(float) * (size_t)B * opt.max_src_len * Hp));   // rows past a sentence's end are never written, but read as GEMM operand rows by the fold
+  if (att_fold_) DA(s.hs_wc1, (size_t)B * opt.max_src_len * Hp);
   DA(s.enc_x, (size_t)B * Hp);
   for (int i = 0; i < 2; ++i) {
     s.enc_h[i].resize(L); s.enc_c[i].resize(L);
@@ -263,6 +265,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   { const char* pe = std::getenv("LINMT_XW"); xw_table_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_XW=0: test knob
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_ATT_MERGE"); att_merge_ = use_tc_ && !(pe && std::atoi(pe) == 0); }
+  { const char* pe = std::getenv("LINMT_ATT_FOLD"); att_fold_ = att_merge_ && !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PAIR"); pair_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
@@ -456,16 +459,18 @@ int Engine::run_decoder_step(int mi, int t, int rows) {
 
 // Attention of one decoder forward (both GEMM families).
 int Engine::launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
-                             float* ra, int32_t* rl, int32_t* rv) {
+                             float* ra, int32_t* rl, int32_t* rv, bool fold) {
   // the record of member mi: [n][Tm+1][k] at pt + mi * (sentences of this device batch's record) * (Tm+1) * k
   const AttTrace at{trace_dev_.pt ? trace_dev_.pt + (size_t)mi * trace_pt_member_stride_ : nullptr, d_orig_, trace_dev_.Tm + 1, t};
   DevModel& m = models_[mi];
   DevState& s = states_[mi];
   const int ldp = att_merge_ ? 3 * Hp : 2 * Hp;
   const size_t smem = sizeof(float) * (win + 8);
+  // fold: the weighted sum runs over W_c1 . hs and the kernel writes htilde (ctx_planes = the htilde panel)
+  const AttFold af = fold ? AttFold{s.hs_wc1, s.proj + 2 * Hp, 3 * Hp, m.att_bout} : AttFold{nullptr, nullptr, 0, nullptr};
   CK(tc::launch_k(pdl_, attention_kernel, dim3(rows), dim3(256), smem, stream, (const float*)s.proj, ldp, u_alt, Hp, (const float*)m.vp,
                   (const float*)s.hs, (const int32_t*)d_len_, ctx, H, Hp, k, (int)opt.max_src_len, (int)opt.attention_mode,
-                  (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens_member_code(mi), at));
+                  (int)opt.attention_d, win, ra, rl, rv, ctx_planes, nt, rec_win, ens_member_code(mi), at, af));
   LAUNCHED();
   return LINMT_OK;
 }

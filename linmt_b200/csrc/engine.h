@@ -47,6 +47,7 @@ struct TcState {
   std::vector<tc::Planes> panel;     // l = 1..L-1: [R][2Hp]  h_cur(l-1) | h_prev(l)
   tc::Planes panel_top{};            // [R][2Hp]  ctx | h_cur(L-1)
   tc::Planes panel_ht{};             // [R][Hp]   htilde
+  tc::Planes hs_planes{};            // [B * max_src][Hp]  the encoder's top states as operand planes (attention fold)
   std::vector<tc::Planes> encp[2];   // [L] x [B][2Hp]  below | h_prev, double buffered over positions
 };
 
@@ -57,6 +58,7 @@ struct DevState {
   float *proj = nullptr, *ctx = nullptr;             // [R][2Hp or 3Hp], [R][Hp]
   float* logits = nullptr;                           // [R][Vp]
   float* hs = nullptr;                               // [B][max_src][Hp]
+  float* hs_wc1 = nullptr;                           // [B][max_src][Hp]  W_c1 . hs (tensor path with the attention fold)
   float* enc_x = nullptr;                            // [B][Hp]
   std::vector<float*> enc_h[2], enc_c[2];            // [L] x [B][Hp], double buffered
 };
@@ -108,7 +110,7 @@ class Engine {
   int run_decoder_step_tc(int mi, int t, int rows);
   int step_tail(int t, int rows);
   int launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
-                       float* rec_align, int32_t* rec_lo, int32_t* rec_vit);
+                       float* rec_align, int32_t* rec_lo, int32_t* rec_vit, bool fold = false);
   int alloc_state_tc(TcState& s);
   int build_xw_tables();   // dec_xw of every model (tensor path, xw_table_)
   int alloc_planes(tc::Planes& p, size_t rows, int ld);
@@ -127,6 +129,7 @@ class Engine {
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
   bool xw_table_ = false;  // first decoder layer: embedding term from a per-vocabulary table instead of the GEMM
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
+  bool att_fold_ = false;  // tensor path: W_c1 applied to the encoder states once per batch, attention writes htilde (LINMT_ATT_FOLD=0: test knob)
   bool att_merge_ = false; // tensor path: W_c2 . h_top computed with the attention projections (LINMT_ATT_MERGE=0: test knob)
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)
   bool pair_ = true;       // CTA pairs for the GEMM shapes that are down to two stages (LINMT_TC_PAIR=0: test knob)

@@ -65,6 +65,7 @@ int Engine::alloc_state_tc(TcState& s) {
     if ((rc = alloc_planes(s.panel[l], R, 2 * Hp))) return rc;
   if ((rc = alloc_planes(s.panel_top, R, 2 * Hp))) return rc;
   if ((rc = alloc_planes(s.panel_ht, R, Hp))) return rc;
+  if (att_fold_ && (rc = alloc_planes(s.hs_planes, (size_t)B * opt.max_src_len, Hp))) return rc;
   for (int i = 0; i < 2; ++i) {
     s.encp[i].resize(L);
     for (int l = 0; l < L; ++l)
@@ -273,6 +274,16 @@ int Engine::run_encoder_tc(int n, int Smax) {
     for (int l = 0; l < L; ++l)
       if (Smax > 0) CK(cudaStreamWaitEvent(main_stream, enc_events_[l][(Smax - 1) % kRing], 0));
     if (rc != LINMT_OK) return rc;
+    if (att_fold_) {
+      // W_c1 applied to every encoder state of the batch, once: the decoder's attention then sums these rows and
+      // needs no output GEMM of its own (see AttFold in step_kernels.cuh).  Rows past a sentence's length hold
+      // whatever an earlier batch left there; nothing reads their products.
+      const size_t rows_all = (size_t)n * opt.max_src_len;
+      tc::split_planes_kernel<<<1024, 256, 0, main_stream>>>(s.hs, ts.hs_planes, nt_, rows_all * Hp);
+      LAUNCHED();
+      tc::TcEpiF32 e{nullptr, s.hs_wc1, Hp, 0};
+      if ((rc = tc_gemm(ts.hs_planes, 0, B * (int)opt.max_src_len, m.p_att_out_w, (int)rows_all, Hp, Hp, e))) return rc;
+    }
   }
   return LINMT_OK;
 }
@@ -375,10 +386,10 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
     int32_t* rl = d_rec_lo_ ? d_rec_lo_ + (size_t)t * R : nullptr;
     int32_t* rv = d_rec_vit_ ? d_rec_vit_ + (size_t)t * R : nullptr;
     if (int rc = kt(KC_ATTENTION)) return rc;
-    if (int rc = launch_attention(mi, t, rows, u_alt, nullptr, ts.panel_top, nt_, ra, rl, rv)) return rc;
+    if (int rc = launch_attention(mi, t, rows, u_alt, nullptr, att_fold_ ? ts.panel_ht : ts.panel_top, nt_, ra, rl, rv, att_fold_)) return rc;
   }
-  // 5. htilde = tanh(W_c1 ctx + W_c2 h + b)
-  {
+  // 5. htilde = tanh(W_c1 ctx + W_c2 h + b) (with the fold the attention kernel has written it already)
+  if (!att_fold_) {
     tc::TcEpiBiasTanh e{m.att_bout, ts.panel_ht, 0, nt_};
     if (int rc0 = kt(KC_ATTOUT)) return rc0;
     int rc;

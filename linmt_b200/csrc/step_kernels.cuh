@@ -168,12 +168,22 @@ struct AttTrace {
   int T1;               // forwards per sentence in the record (longest step count + 1)
   int t;                // this forward
 };
+// Optional fold of the attention output layer into this kernel.  htilde = tanh(W_c1 ctx + W_c2 h + b) and
+// ctx = sum_j a_j hs_j, so W_c1 ctx = sum_j a_j (W_c1 hs_j): with `cs` = the encoder states already multiplied by
+// W_c1 (once per batch), the weighted sum IS the first term, `add` carries the row's W_c2 h (computed with the
+// attention projections) and the kernel writes the attentional state itself -- a dependent GEMM launch less per
+// step.  cs == nullptr: plain context.
+struct AttFold {
+  const float* cs;      // [B][max_src][Hp] like hs
+  const float* add; int ld_add;   // element (row, j) at add[row * ld_add + j]
+  const float* bias;    // [Hp]
+};
 static __global__ void __launch_bounds__(256, 5) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
                                  int32_t* __restrict__ rec_lo, int32_t* __restrict__ rec_vit, tc::Planes ctx_planes, int nt,
-                                 int rec_win, int ens, AttTrace at) {
+                                 int rec_win, int ens, AttTrace at, AttFold fold) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   extern __shared__ float sm[];
@@ -280,12 +290,20 @@ static __global__ void __launch_bounds__(256, 5) attention_kernel(const float* _
   }
   // context: CreateCTKernel, deep_rnn_kernel.h:1250-1260 (sum over window positions in order)
   float* crow = ctx ? ctx + (size_t)r * Hp : nullptr;
+  const float* csb = fold.cs ? fold.cs + (size_t)sent * max_src * Hp : hsb;
   for (int j = threadIdx.x * 4; j < Hp; j += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int w = 0; w < W; ++w) {
       const float a = e[w];
-      const float4 h4 = *reinterpret_cast<const float4*>(hsb + (size_t)(S - 1 - (lo + w)) * Hp + j);
+      const float4 h4 = *reinterpret_cast<const float4*>(csb + (size_t)(S - 1 - (lo + w)) * Hp + j);
       acc.x += a * h4.x; acc.y += a * h4.y; acc.z += a * h4.z; acc.w += a * h4.w;
+    }
+    if (fold.cs) {
+      // the attentional state: the sums of TcEpiBiasTanh in its order, (W_c1 ctx + W_c2 h) + b
+      const float4 g = *reinterpret_cast<const float4*>(fold.add + (size_t)r * fold.ld_add + j);
+      const float4 b = *reinterpret_cast<const float4*>(fold.bias + j);
+      acc.x = tc::tanh_fast((acc.x + g.x) + b.x); acc.y = tc::tanh_fast((acc.y + g.y) + b.y);
+      acc.z = tc::tanh_fast((acc.z + g.z) + b.z); acc.w = tc::tanh_fast((acc.w + g.w) + b.w);
     }
     if (crow) *reinterpret_cast<float4*>(crow + j) = acc;
     if (ctx_planes.p[0]) {  // tensor-core path: the context goes straight into its operand panel
