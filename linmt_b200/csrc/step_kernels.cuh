@@ -498,15 +498,19 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
           }
       }
     };
-    int i = tid * 4;
-    for (; i + 3 * 1024 < V4; i += 4 * 1024) {
+    // From the last column block down: the GEMM that wrote the logits walked the column tiles upwards, so the
+    // highest columns of every row are the ones still in L2 (all rows are swept at the same time).
+    const int top = V4 & ~1023;                       // start of the last, possibly partial, block of 1024
+    if (top + tid * 4 < V4) group(*reinterpret_cast<const float4*>(z + top + tid * 4), top + tid * 4);
+    int i = top - 1024 + tid * 4;
+    for (; i - 3 * 1024 >= 0; i -= 4 * 1024) {
       const float4 q0 = *reinterpret_cast<const float4*>(z + i);
-      const float4 q1 = *reinterpret_cast<const float4*>(z + i + 1024);
-      const float4 q2 = *reinterpret_cast<const float4*>(z + i + 2048);
-      const float4 q3 = *reinterpret_cast<const float4*>(z + i + 3072);
-      group(q0, i); group(q1, i + 1024); group(q2, i + 2048); group(q3, i + 3072);
+      const float4 q1 = *reinterpret_cast<const float4*>(z + i - 1024);
+      const float4 q2 = *reinterpret_cast<const float4*>(z + i - 2048);
+      const float4 q3 = *reinterpret_cast<const float4*>(z + i - 3072);
+      group(q0, i); group(q1, i - 1024); group(q2, i - 2048); group(q3, i - 3072);
     }
-    for (; i < V4; i += 1024) group(*reinterpret_cast<const float4*>(z + i), i);
+    for (; i >= 0; i -= 1024) group(*reinterpret_cast<const float4*>(z + i), i);
   }
   for (int i = V4 + tid; i < V; i += 256) visit(z[i], i);
 #pragma unroll
