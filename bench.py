@@ -41,8 +41,8 @@ C2_TRAFFIC_BYTES = {
     "lstm_gemm": 43.5e6,        # first layer 45.74 MB (with input-term table rows), the others 42.72 MB
     "vocab_gemm": 109.8e6,      # 63.44 MB read (the weights) + 46.33 MB written (half of the logits still in L2)
     "attn_proj_gemm": 15.8e6, "attn_out_gemm": 10.56e6,
-    "softmax_topk": 104.8e6,    # the logits once + candidates' weight rows
-    "gather": 9.8e6, "attention": 11.36e6, "beam_select": 0.11e6,
+    "softmax_topk": 107.1e6,    # the logits once + candidates' weight rows (cold-cache capture)
+    "gather": 9.8e6, "attention": 19.55e6, "beam_select": 0.11e6,
 }
 
 
@@ -387,8 +387,8 @@ def run_ours(args):
             roof("ensemble_combine", "ensemble combination of the members' distributions", "hbm", rs * V * 4.0 * (M + 1)),
             roof("gather", "beam reordering of the recurrent state (h planes of every layer, attentional state)", "hbm",
                  rs * (L + 1) * nt * Hp * 2.0 * 2 * M),
-            roof("attention", "attention: p_t, window scores, softmax x Gaussian, context", "hbm",
-                 (ss * 21 * Hp * 4.0 + rs * (3 * Hp * 4.0 + nt * Hp * 2.0)) * M),
+            roof("attention", "attention: p_t, window scores, softmax x Gaussian, weighted sum of W_c1-mapped states, tanh -> attentional state", "hbm",
+                 (ss * 2 * 21 * Hp * 4.0 + rs * (3 * Hp * 4.0 + nt * Hp * 2.0)) * M),
             roof("beam_select", "beam selection (k(k+1) candidates per sentence)", "hbm", rs * (c.beam + 1) * 8.0),
         ]
         blocks = [b_ for b_ in blocks if b_]
