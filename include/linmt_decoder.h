@@ -216,7 +216,8 @@ int linmt_get_stats(const linmt_engine* e, linmt_stats* out);
 int linmt_set_kernel_timing(linmt_engine* e, int32_t on);
 /* Device time and launch count per kernel class of the last timed device batch (first device of the handle).
  * Classes in launch order: 0 state gather, 1 LSTM gate GEMMs, 2 attention projections GEMM, 3 attention,
- * 4 attention output GEMM, 5 vocabulary GEMM, 6 ensemble combine, 7 softmax / top-k, 8 beam selection.
+ * 4 attention output GEMM (no launches on the tensor-core path: that layer is applied to the encoder states once per
+ * batch and finished inside the attention kernel), 5 vocabulary GEMM, 6 ensemble combine, 7 softmax / top-k, 8 beam selection.
  * `ms` and `launches` hold n >= 9 entries. */
 int linmt_kernel_times(const linmt_engine* e, float* ms, int32_t* launches, int32_t n);
 

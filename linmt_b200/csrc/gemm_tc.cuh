@@ -28,7 +28,8 @@
 // epilogue warps sleep between polls.  A ring of shared-memory stages is handed back and forth with
 // mbarriers; every wait is bounded and reports through an error flag instead of hanging.  All kernels
 // take part in programmatic dependent launch (see pdl_wait below).  A persistent variant
-// (gemm_tc_persist_kernel) serves the many-wave vocabulary GEMM.
+// (gemm_tc_persist_kernel) serves the many-wave vocabulary GEMM; gemm_tc_pair.cuh holds the forms of both kernels
+// that run on CTA pairs (tcgen05 cta_group::2), used where a launch is wide enough for them to pay.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
