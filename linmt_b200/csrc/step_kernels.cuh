@@ -178,7 +178,8 @@ struct AttFold {
   const float* add; int ld_add;   // element (row, j) at add[row * ld_add + j]
   const float* bias;    // [Hp]
 };
-static __global__ void __launch_bounds__(256, 5) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
+// (six CTAs per SM: 888 resident CTAs hold the 768 rows of a full step in one wave; at five, 28 rows ran as a second wave)
+static __global__ void __launch_bounds__(256, 6) attention_kernel(const float* __restrict__ proj, int ldp, const float* __restrict__ u_alt, int ldu,
                                  const float* __restrict__ vp, const float* __restrict__ hs,
                                  const int32_t* __restrict__ src_len, float* __restrict__ ctx, int H, int Hp,
                                  int k, int max_src, int mode, int D, int win, float* __restrict__ rec_align,
