@@ -311,6 +311,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
     DA(d_splitk_ws_, kSplitKWsFloats);
     DA(d_splitk_counters_, kSplitKMaxTiles);
     CK(cudaMemset(d_splitk_counters_, 0, sizeof(int) * kSplitKMaxTiles));
+    if (pair_ && !pairs_available()) pair_ = false;   // (a device that cannot co-schedule two such CTAs keeps the one-tile kernels)
   }
   models_.resize(nm); states_.resize(nm); tc_states_.resize(nm);
   for (int i = 0; i < nm; ++i) {

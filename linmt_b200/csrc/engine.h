@@ -109,6 +109,7 @@ class Engine {
   int run_encoder_tc(int n, int Smax);
   int run_decoder_step_tc(int mi, int t, int rows);
   int step_tail(int t, int rows);
+  bool pairs_available();   // clusters of two GEMM CTAs can be scheduled on the current device (engine_tc.cu)
   int launch_attention(int mi, int t, int rows, const float* u_alt, float* ctx, const tc::Planes& ctx_planes, int nt,
                        float* rec_align, int32_t* rec_lo, int32_t* rec_vit, bool fold = false);
   int alloc_state_tc(TcState& s);

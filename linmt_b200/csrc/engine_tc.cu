@@ -187,6 +187,8 @@ int Engine::tc_gemm(const tc::Planes& A, int a_col0, int a_rows_cap, const tc::P
   return LINMT_OK;
 }
 
+bool Engine::pairs_available() { return tc::max_resident_pairs<2, 64, 1, tc::TcEpiLstm>() > 0; }
+
 static tc::Planes no_planes() { return tc::Planes{}; }
 
 // Input-term table of the first decoder layer: dec_xw[v][:] = W_x . embedding(v) for every target word, computed
@@ -326,7 +328,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
       for (int p = 0; p < nt_; ++p)
         add(m.p_emb_tgt.p[p], (long long)m.p_emb_tgt.ld * 2, ts.panel1.p[p], (long long)ts.panel1.ld * 2, Hp * 2, 1);
     jobs.n = nj;
-    dim3 grid(rows, nj);
+    dim3 grid(rows, (nj + kGatherJobsPerBlock - 1) / kGatherJobsPerBlock);
     if (int rc = kt(KC_GATHER)) return rc;
     CK(tc::launch_k(pdl_, row_gather_kernel, grid, dim3(128), 0, stream, jobs, (const int32_t*)d_parent_, (const int32_t*)d_tok_, V, k, t == 0 ? 1 : 0));
     LAUNCHED();

@@ -582,5 +582,22 @@ inline cudaError_t launch_gemm_tc_persist_pair(const TmapSet& tm, int M, int N, 
   return cudaLaunchKernelEx(&cfg, gemm_tc_persist_pair_kernel<NT, BKT, FMT, Epi>, tm, M, N, K, sh.bn, sh.stages, epi, err_flag, stride);
 }
 
+// How many CTA pairs of the one-tile pair kernel the current device holds at once (0: clusters of two such CTAs
+// cannot be scheduled here, e.g. on a partitioned device, and the host must keep to the one-tile kernels).
+template <int NT, int BKT, int FMT, class Epi>
+inline int max_resident_pairs() {
+  static bool optin_done[kMaxDevices] = {};
+  if (ensure_smem_optin(gemm_tc_pair_kernel<NT, BKT, FMT, Epi>, optin_done) != cudaSuccess) { cudaGetLastError(); return 0; }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2, 1, 1); cfg.blockDim = dim3(kThreadsMain); cfg.dynamicSmemBytes = (size_t)(SMEM_BUDGET + 1280);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<NT, BKT, FMT, Epi>, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
 }  // namespace tc
 }  // namespace linmt

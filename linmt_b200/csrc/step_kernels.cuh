@@ -85,24 +85,46 @@ struct GatherJobs {
   GatherJob j[32];
   int n;
 };
+constexpr int kGatherJobsPerBlock = 4;   // a full step (768 rows x 10 jobs) is then 2304 blocks: one wave of resident CTAs
 static __global__ void row_gather_kernel(GatherJobs jobs, const int32_t* __restrict__ parent, const int32_t* __restrict__ tok,
                                          int vocab, int k, int src_per_sentence) {
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
   const int r = blockIdx.x;
-  const GatherJob& jb = jobs.j[blockIdx.y];
-  long long srow;
-  if (jb.kind == 1) {
-    int t = tok[r];
-    if (t < 0 || t >= vocab) t = kUnk;
-    srow = t;
-  } else {
-    const int sent = r / k;
-    srow = src_per_sentence ? sent : sent * k + parent[r];
+  const int j0 = blockIdx.y * kGatherJobsPerBlock;
+  const int sent = r / k;
+  const long long prow = src_per_sentence ? sent : sent * k + parent[r];
+  // every thread moves 16 bytes of up to four jobs at a time: all loads first, then the stores
+  const unsigned char* src[kGatherJobsPerBlock];
+  unsigned char* dst[kGatherJobsPerBlock];
+  int nchunk[kGatherJobsPerBlock];
+  int most = 0;
+#pragma unroll
+  for (int q = 0; q < kGatherJobsPerBlock; ++q) {
+    nchunk[q] = 0; src[q] = nullptr; dst[q] = nullptr;
+    if (j0 + q < jobs.n) {
+      const GatherJob& jb = jobs.j[j0 + q];
+      long long srow = prow;
+      if (jb.kind == 1) {
+        int t = tok[r];
+        if (t < 0 || t >= vocab) t = kUnk;
+        srow = t;
+      }
+      src[q] = jb.src + srow * jb.src_stride;
+      dst[q] = jb.dst + (long long)r * jb.dst_stride;
+      nchunk[q] = jb.row_bytes / 16;
+      most = nchunk[q] > most ? nchunk[q] : most;
+    }
   }
-  const uint4* src = reinterpret_cast<const uint4*>(jb.src + srow * jb.src_stride);
-  uint4* dst = reinterpret_cast<uint4*>(jb.dst + (long long)r * jb.dst_stride);
-  for (int i = threadIdx.x; i < jb.row_bytes / 16; i += blockDim.x) dst[i] = src[i];
+  for (int c = threadIdx.x; c < most; c += blockDim.x) {
+    uint4 v[kGatherJobsPerBlock];
+#pragma unroll
+    for (int q = 0; q < kGatherJobsPerBlock; ++q)
+      if (c < nchunk[q]) v[q] = reinterpret_cast<const uint4*>(src[q])[c];
+#pragma unroll
+    for (int q = 0; q < kGatherJobsPerBlock; ++q)
+      if (c < nchunk[q]) reinterpret_cast<uint4*>(dst[q])[c] = v[q];
+  }
 }
 
 // Encoder input for the tensor-core path: embedding planes of the token at reversed position
