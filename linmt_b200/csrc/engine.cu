@@ -240,6 +240,7 @@ int Engine::alloc_state(DevState& s) {
   DA(s.htilde, rh); DA(s.htilde_prev, rh);
   DA(s.proj, 3 * rh); DA(s.ctx, rh);
   DA(s.logits, (size_t)R * Vp);
+  if (logits16_) DA(s.logits16, (size_t)R * Vp);
   DA(s.hs, (size_t)B * opt.max_src_len * Hp);
   CK(cudaMemset(s.hs, 0, sizeof(float) * (size_t)B * opt.max_src_len * Hp));   // rows past a sentence's end are never written, but read as GEMM operand rows by the fold
   if (att_fold_) DA(s.hs_wc1, (size_t)B * opt.max_src_len * Hp);
@@ -282,6 +283,7 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   const bool v16x = o.gemm_path == LINMT_GEMM_TENSOR_V16X || o.gemm_path == LINMT_GEMM_AUTO;
   if (fmt_ == 1 && (o.gemm_path == LINMT_GEMM_TENSOR_V16 || (v16x && nm == 1))) nt_vocab_ = 1;
   refine_ = fmt_ == 1 && v16x && nm == 1;
+  { const char* pe = std::getenv("LINMT_LOGITS16"); logits16_ = refine_ && !(pe && std::atoi(pe) == 0); }
   if (linmt_blob_floats(&d) != blob_floats) return fail(LINMT_EINVAL, "weight blob size does not match the model dimensions");
   if (o.beam <= 0) return fail(LINMT_EINVAL, "--beam-size cannot be <= 0");
   if (o.penalty < 0) return fail(LINMT_EINVAL, "--penalty cannot be < 0");
@@ -499,7 +501,8 @@ int Engine::step_tail(int t, int rows) {
         rf.eps_coef = 1.1f * (1.0f / 1024.0f) * m0.voc_wnorm_max;
       }
       if (refine_) trace_dev_.rf = rf;
-      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_, refine_ ? &rf : nullptr));
+      CK(launch_softmax_topk(s.logits, Vp, V, kk, rows, o, 1, stream, pdl_, d_pmax_, pmax_ld_, pmax_slots_, refine_ ? &rf : nullptr,
+                             logits16_ ? s.logits16 : nullptr));
     } else {
       // EnsembleFactory::EnsemblesModels (src/decoder.h:1910-1931): mean of the members'
       // probabilities, renormalised -- written as log(mean p) so that the log-softmax of the

@@ -57,6 +57,7 @@ struct DevState {
   float *htilde = nullptr, *htilde_prev = nullptr;   // [R][Hp]
   float *proj = nullptr, *ctx = nullptr;             // [R][2Hp or 3Hp], [R][Hp]
   float* logits = nullptr;                           // [R][Vp]
+  __half* logits16 = nullptr;                        // [R][Vp]  the same in fp16 (one-product logits whose candidates are recomputed)
   float* hs = nullptr;                               // [B][max_src][Hp]
   float* hs_wc1 = nullptr;                           // [B][max_src][Hp]  W_c1 . hs (tensor path with the attention fold)
   float* enc_x = nullptr;                            // [B][Hp]
@@ -130,6 +131,7 @@ class Engine {
   bool pdl_ = false;  // decoder-step kernels launched with programmatic stream serialization (tensor path)
   bool xw_table_ = false;  // first decoder layer: embedding term from a per-vocabulary table instead of the GEMM
   bool refine_ = false;    // one-product vocabulary GEMM + accurate recomputation of the candidates in the softmax kernel
+  bool logits16_ = false;  // one-product logits stored as fp16 (only with the accurate recomputation of the candidates; LINMT_LOGITS16=0: test knob)
   bool att_fold_ = false;  // tensor path: W_c1 applied to the encoder states once per batch, attention writes htilde (LINMT_ATT_FOLD=0: test knob)
   bool att_merge_ = false; // tensor path: W_c2 . h_top computed with the attention projections (LINMT_ATT_MERGE=0: test knob)
   bool pmax_on_ = true;    // vocabulary GEMM hands block maxima to the softmax (LINMT_PMAX=0: test knob)

@@ -407,6 +407,7 @@ int Engine::run_decoder_step_tc(int mi, int t, int rows) {
   // 6. logits
   {
     tc::TcEpiF32 e{m.voc_b, s.logits, Vp, 0};
+    if (logits16_) e.out16 = s.logits16;   // the softmax of this step is their only reader
     pmax_slots_ = 0;
     if (n_models == 1 && pmax_on_) { e.pmax = d_pmax_; e.pmax_ld = pmax_ld_; e.n_valid = V; }
     if (int rc = kt(KC_VOCAB)) return rc;

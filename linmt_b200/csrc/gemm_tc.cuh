@@ -529,18 +529,36 @@ struct TcEpiF32 {
   // 64 columns (tile column block `slot`) of every row, over columns < n_valid, at pmax[row * pmax_ld + slot].
   // The softmax kernel then needs no first sweep over the row for its maximum and its top-k threshold.
   float* pmax = nullptr; int pmax_ld = 0; int n_valid = 0;
-  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
-    float* o = out + (size_t)row * ld + col0;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float4 r = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      if (bias) {
-        const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
-        r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
-      }
-      if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
-      *reinterpret_cast<float4*>(o + 4 * q) = r;
+  // Optional half-precision output (out16 set: `out` is not written): logits whose few values that matter one by one
+  // are recomputed by their consumer and which otherwise only enter a sum of exponentials go out as fp16, half
+  // the bytes to write and to sweep.  The block maxima are then those of the ROUNDED values (elements of the row).
+  __half* out16 = nullptr;
+  __device__ __forceinline__ float4 finish4(float4 r, int col0) const {
+    if (bias) {
+      const float4 b = *reinterpret_cast<const float4*>(bias + col0);
+      r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
     }
+    if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
+    if (out16) {
+      r.x = __half2float(__float2half_rn(r.x)); r.y = __half2float(__float2half_rn(r.y));
+      r.z = __half2float(__float2half_rn(r.z)); r.w = __half2float(__float2half_rn(r.w));
+    }
+    return r;
+  }
+  // four consecutive finished values to row-major element index idx (a multiple of 4)
+  __device__ __forceinline__ void store4(size_t idx, const float4& r) const {
+    if (out16) {
+      const __half2 lo = __floats2half2_rn(r.x, r.y), hi = __floats2half2_rn(r.z, r.w);
+      *reinterpret_cast<uint2*>(out16 + idx) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+      *reinterpret_cast<float4*>(out + idx) = r;
+    }
+  }
+  __device__ __forceinline__ void operator()(int row, int col0, const float* v) const {
+    const size_t o = (size_t)row * ld + col0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      store4(o + 4 * q, finish4(make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]), col0 + 4 * q));
   }
   // Block form (see TcEpiLstm::block): bias / tanh in registers, the block of up to 64 columns
   // staged per row, then stored with a row's 16 float4 on consecutive lanes.
@@ -548,6 +566,13 @@ struct TcEpiF32 {
   static constexpr bool kHasPmax = true;
   __device__ __forceinline__ void pmax_store(int row, int M, int slot, float m) const {
     if (pmax && row < M) pmax[(size_t)row * pmax_ld + slot] = m;
+  }
+  __device__ __forceinline__ float max4(float m, const float4& r, int c) const {
+    if (c + 0 < n_valid) m = fmaxf(m, r.x);
+    if (c + 1 < n_valid) m = fmaxf(m, r.y);
+    if (c + 2 < n_valid) m = fmaxf(m, r.z);
+    if (c + 3 < n_valid) m = fmaxf(m, r.w);
+    return m;
   }
   // the same block without staging (row-per-lane stores), for callers whose staging area is busy
   __device__ __forceinline__ void direct_block(int row, int M, int col_first, int nch, float (*v)[16], int slot) const {
@@ -557,21 +582,11 @@ struct TcEpiF32 {
       for (int ci = 0; ci < kEpiBlockChunks; ++ci) {
         if (ci < nch) {
           const int col0 = col_first + 16 * ci;
-          float* o = out + (size_t)row * ld + col0;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            float4 r = make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]);
-            if (bias) {
-              const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
-              r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
-            }
-            if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
-            *reinterpret_cast<float4*>(o + 4 * q) = r;
-            const int c = col0 + 4 * q;
-            if (c + 0 < n_valid) m = fmaxf(m, r.x);
-            if (c + 1 < n_valid) m = fmaxf(m, r.y);
-            if (c + 2 < n_valid) m = fmaxf(m, r.z);
-            if (c + 3 < n_valid) m = fmaxf(m, r.w);
+            const float4 r = finish4(make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]), col0 + 4 * q);
+            store4((size_t)row * ld + col0 + 4 * q, r);
+            m = max4(m, r, col0 + 4 * q);
           }
         }
       }
@@ -590,18 +605,9 @@ struct TcEpiF32 {
         const int col0 = col_first + 16 * ci;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          float4 r = make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]);
-          if (bias) {
-            const float4 b = *reinterpret_cast<const float4*>(bias + col0 + 4 * q);
-            r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
-          }
-          if (col0 < split) { r.x = tanh_fast(r.x); r.y = tanh_fast(r.y); r.z = tanh_fast(r.z); r.w = tanh_fast(r.w); }
+          const float4 r = finish4(make_float4(v[ci][4 * q], v[ci][4 * q + 1], v[ci][4 * q + 2], v[ci][4 * q + 3]), col0 + 4 * q);
           *reinterpret_cast<float4*>(sbuf + lane * stride + 16 * ci + 4 * q) = r;
-          const int c = col0 + 4 * q;
-          if (c + 0 < n_valid) m = fmaxf(m, r.x);
-          if (c + 1 < n_valid) m = fmaxf(m, r.y);
-          if (c + 2 < n_valid) m = fmaxf(m, r.z);
-          if (c + 3 < n_valid) m = fmaxf(m, r.w);
+          m = max4(m, r, col0 + 4 * q);
         }
       }
     }
@@ -609,9 +615,7 @@ struct TcEpiF32 {
     const int nq = 4 * nch;   // float4 per row
     for (int s = lane; s < 32 * nq; s += 32) {
       const int r = s / nq, g = s - r * nq;
-      if (row0 + r < M)
-        *reinterpret_cast<float4*>(out + (size_t)(row0 + r) * ld + col_first + 4 * g) =
-            *reinterpret_cast<const float4*>(sbuf + r * stride + 4 * g);
+      if (row0 + r < M) store4((size_t)(row0 + r) * ld + col_first + 4 * g, *reinterpret_cast<const float4*>(sbuf + r * stride + 4 * g));
     }
     __syncwarp();
     return m;

@@ -373,7 +373,8 @@ constexpr float kPairInv = 1.0f / 2048.0f;
 // (e.g. a row of equal logits) the block falls back to kk exact arg-best sweeps.
 constexpr int kTopkCap = 1024;
 static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float* __restrict__ logits, int ld, int V, int kk, TopkOut out,
-                                                                  int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots, TopkRefine rf) {
+                                                                  int normalise, const float* __restrict__ pmax, int pmax_ld, int n_slots, TopkRefine rf,
+                                                                  const __half* __restrict__ logits16) {
   extern __shared__ float s_a[];   // [rf.K] the row's activations in fp32 (refinement only)
   tc::pdl_launch_dependents();   // see gemm_tc.cuh: the next kernel of the step may start its prologue
   tc::pdl_wait();                // nothing below runs before the previous kernel's results are visible
@@ -389,12 +390,17 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
   const int r = blockIdx.x, tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const float* z = logits + (size_t)r * ld;
+  // fp16 logits (refinement mode only: the candidates' values are recomputed, the rest only enter the sum)
+  const __half* zh = logits16 ? logits16 + (size_t)r * ld : nullptr;
+  auto zat = [&](int i) { return zh ? __half2float(zh[i]) : z[i]; };
   const int V4 = V & ~3;
   // ---- pass 1: maxima (four independent 16-byte loads in flight per thread) -- or, when the GEMM that
   // produced the logits left the maxima of disjoint column blocks of every row (pmax), just those ----
   float m = -INFINITY;
   if (pmax) {
     for (int s = tid; s < n_slots; s += 256) m = fmaxf(m, pmax[(size_t)r * pmax_ld + s]);
+  } else if (zh) {
+    for (int i = tid; i < V; i += 256) m = fmaxf(m, __half2float(zh[i]));
   } else {
     float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
     int i = tid * 4;
@@ -494,6 +500,7 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
     float tot = 0.f;
     for (int w = 0; w < 8; ++w) tot += s_red[w];
     tau -= 2.0f * (rf.eps_coef * sqrtf(tot) + 1e-5f);   // + fp16 subnormals and the accumulator's own rounding
+    if (zh) tau -= 2.0f * 4.9e-4f * fmaxf(fabsf(rmax), fabsf(tau));   // and the rounding of the stored value (2^-11 relative)
     __syncthreads();
   }
   // ---- pass 2: sum of exponentials, candidates ----
@@ -521,6 +528,28 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
           }
       }
     };
+    if (zh) {
+      // eight values per 16-byte load, blocks of 2048 columns, from the last one down
+      auto group8 = [&](const uint4& q, int i) {
+        const __half2* h = reinterpret_cast<const __half2*>(&q);
+        const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), c = __half22float2(h[2]), d = __half22float2(h[3]);
+        group(make_float4(a.x, a.y, b.x, b.y), i);
+        group(make_float4(c.x, c.y, d.x, d.y), i + 4);
+      };
+      const int V8 = V & ~7;
+      const int top8 = V8 & ~2047;
+      if (top8 + tid * 8 < V8) group8(*reinterpret_cast<const uint4*>(zh + top8 + tid * 8), top8 + tid * 8);
+      int i = top8 - 2048 + tid * 8;
+      for (; i - 3 * 2048 >= 0; i -= 4 * 2048) {
+        const uint4 q0 = *reinterpret_cast<const uint4*>(zh + i);
+        const uint4 q1 = *reinterpret_cast<const uint4*>(zh + i - 2048);
+        const uint4 q2 = *reinterpret_cast<const uint4*>(zh + i - 4096);
+        const uint4 q3 = *reinterpret_cast<const uint4*>(zh + i - 6144);
+        group8(q0, i); group8(q1, i - 2048); group8(q2, i - 4096); group8(q3, i - 6144);
+      }
+      for (; i >= 0; i -= 2048) group8(*reinterpret_cast<const uint4*>(zh + i), i);
+      for (int j = V8 + tid; j < V; j += 256) visit(__half2float(zh[j]), j);
+    } else {
     // From the last column block down: the GEMM that wrote the logits walked the column tiles upwards, so the
     // highest columns of every row are the ones still in L2 (all rows are swept at the same time).
     const int top = V4 & ~1023;                       // start of the last, possibly partial, block of 1024
@@ -534,8 +563,9 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
       group(q0, i); group(q1, i - 1024); group(q2, i - 2048); group(q3, i - 3072);
     }
     for (; i >= 0; i -= 1024) group(*reinterpret_cast<const float4*>(z + i), i);
+    for (int j = V4 + tid; j < V; j += 256) visit(z[j], j);
+    }
   }
-  for (int i = V4 + tid; i < V; i += 256) visit(z[i], i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
   if (lane == 0) s_red[warp] = ssum;
@@ -546,7 +576,7 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
     s_sum = bs;
     s_lse = normalise ? logf(bs) : -rmax;   // normalise = 0: the row already holds log-probabilities
     if (!rf.a0) {
-      if (out.eos_logp) out.eos_logp[r] = (z[kEos] - rmax) - s_lse;
+      if (out.eos_logp) out.eos_logp[r] = (zat(kEos) - rmax) - s_lse;
       if (out.row_stats) { out.row_stats[2 * r] = rmax; out.row_stats[2 * r + 1] = s_lse; }
     }
   }
@@ -563,7 +593,7 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
       float bv = -INFINITY;
       int bi = 0x7fffffff;
       for (int i = tid; i < V; i += 256) {
-        const float v = z[i];
+        const float v = zat(i);
         const bool after = (v < last_v) || (v == last_v && i > last_i);
         if (after && better(v, i, bv, bi)) { bv = v; bi = i; }
       }
@@ -614,7 +644,7 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
       for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (lane == 0) {
         const float zv = acc + (rf.bias ? rf.bias[v] : 0.f);
-        const float za = (c < nc) ? s_cv[c] : z[kEos];
+        const float za = (c < nc) ? s_cv[c] : zat(kEos);
         const float delta = __expf(zv - rmax) - __expf(za - rmax);
         if (c < nc) { s_cv[c] = zv; s_cd[c] = delta; }
         else { s_eos = zv; s_eos_delta = delta; }
@@ -668,7 +698,7 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = tid; i < V; i += 256) {
-      const float v = z[i];
+      const float v = zat(i);
       const bool after = (v < last_v) || (v == last_v && i > last_i);
       if (after && better(v, i, bv, bi)) { bv = v; bi = i; }
     }
@@ -694,12 +724,12 @@ static __global__ void __launch_bounds__(256, 6) softmax_topk_kernel(const float
 
 inline cudaError_t launch_softmax_topk(const float* logits, int ld, int V, int kk, int rows, const TopkOut& out, int normalise,
                                        cudaStream_t st, bool pdl = false, const float* pmax = nullptr, int pmax_ld = 0, int n_slots = 0,
-                                       const TopkRefine* refine = nullptr) {
+                                       const TopkRefine* refine = nullptr, const __half* logits16 = nullptr) {
   if (n_slots <= 0) pmax = nullptr;
   TopkRefine rf{};
   if (refine) rf = *refine;
   const size_t smem = rf.a0 ? sizeof(float) * (size_t)rf.K : 0;
-  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), smem, st, logits, ld, V, kk, out, normalise, pmax, pmax_ld, n_slots, rf);
+  return tc::launch_k(pdl, softmax_topk_kernel, dim3(rows), dim3(256), smem, st, logits, ld, V, kk, out, normalise, pmax, pmax_ld, n_slots, rf, refine ? logits16 : (const __half*)nullptr);
 }
 
 // ---------------------------------------------------------------------------------------

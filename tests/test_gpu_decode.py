@@ -391,14 +391,14 @@ def test_launch_variants_give_identical_bits(cuda_lib):
     maxima, so that another set of candidates is recomputed accurately; the first decoder layer's
     embedding term inside the GEMM instead of from its table; the attention output product as one GEMM
     instead of two halves; that product per step on the context instead of once per batch on the encoder
-    states): scores equal to fp32 rounding, and a near-tie may resolve differently in a
+    states; the one-product logits stored as fp32 instead of fp16): scores equal to fp32 rounding, and a near-tie may resolve differently in a
     sentence or two."""
     from linmt_b200 import decoder
     c = synth.configs()["C2"]
     blob = c.blobs()[0]
     sents = c.sentences().subset(range(24))   # 288 rows: several waves of vocabulary tiles -> persistent kernel
     same_bits = ({"LINMT_PDL": "0"}, {"LINMT_TC_PERSIST": "0"})
-    same_sums = ({"LINMT_PMAX": "0"}, {"LINMT_XW": "0"}, {"LINMT_ATT_MERGE": "0"}, {"LINMT_ATT_FOLD": "0"})
+    same_sums = ({"LINMT_PMAX": "0"}, {"LINMT_XW": "0"}, {"LINMT_ATT_MERGE": "0"}, {"LINMT_ATT_FOLD": "0"}, {"LINMT_LOGITS16": "0"})
     outs = []
     for env in ({},) + same_bits + same_sums:
         old = {k: os.environ.get(k) for k in env}
