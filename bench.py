@@ -39,10 +39,10 @@ FALLBACK_HBM_GBS = 6650.0
 # summaries with the capture commands are committed with the profiles).  None = no capture for that class.
 C2_TRAFFIC_BYTES = {
     "lstm_gemm": 43.5e6,        # first layer 45.74 MB (with input-term table rows), the others 42.72 MB
-    "vocab_gemm": 109.8e6,      # 63.44 MB read (the weights) + 46.33 MB written (half of the logits still in L2)
+    "vocab_gemm": 77.2e6,       # 63.40 MB read (the weights) + 13.82 MB written (fp16 logits, most of them still in L2)
     "attn_proj_gemm": 15.8e6, "attn_out_gemm": 10.56e6,
-    "softmax_topk": 107.1e6,    # the logits once + candidates' weight rows (cold-cache capture)
-    "gather": 9.8e6, "attention": 19.55e6, "beam_select": 0.11e6,
+    "softmax_topk": 56.0e6,     # the fp16 logits once + candidates' weight rows (cold-cache capture)
+    "gather": 10.66e6, "attention": 19.55e6, "beam_select": 0.11e6,
 }
 
 
@@ -359,6 +359,8 @@ def run_ours(args):
                 "fp32 tensor path every product is computed as `products_per_product` 16-bit partial products, which is "
                 "what tensor_pipe_* counts")
         total_cls_ms = sum(v[0] for v in cls.values()) or 1.0
+        # one-product logits of a single fp32 model go out as fp16 (the library's default; LINMT_LOGITS16=0 keeps fp32)
+        logits16 = tensor and fp32 and M == 1 and args.gemm_path in ("auto", "tensor_v16x") and os.environ.get("LINMT_LOGITS16", "1") != "0"
 
         def roof(key, kernel, bound, work, products=0):
             """Roofline block of one kernel class: algorithmic flops (tensor) or bytes (hbm) of the timed pass over
@@ -383,7 +385,8 @@ def run_ours(args):
             roof("vocab_gemm", f"vocabulary GEMM [rows,H]x[H,V] ({args.gemm_path} path)", "tensor", 2.0 * rs * H * V * M, voc_products),
             roof("attn_proj_gemm", "attention projections GEMM [rows,H]x[H,3H] (W_p | W_a^T | W_c2)", "tensor", 2.0 * rs * H * 3 * H * M, gate_products),
             roof("attn_out_gemm", "attention output GEMM [rows,H]x[H,H] (W_c1) + tanh", "tensor", 2.0 * rs * H * H * M, gate_products),
-            roof("softmax_topk", "log-softmax statistics + per-row top-(k+1), one pass over the logits", "hbm", rs * V * 4.0),
+            roof("softmax_topk", "log-softmax statistics + per-row top-(k+1), one pass over the logits" + (" (fp16)" if logits16 else ""), "hbm",
+                 rs * V * (2.0 if logits16 else 4.0)),
             roof("ensemble_combine", "ensemble combination of the members' distributions", "hbm", rs * V * 4.0 * (M + 1)),
             roof("gather", "beam reordering of the recurrent state (h planes of every layer, attentional state)", "hbm",
                  rs * (L + 1) * nt * Hp * 2.0 * 2 * M),
