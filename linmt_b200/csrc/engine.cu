@@ -266,7 +266,8 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   { const char* pe = std::getenv("LINMT_XW"); xw_table_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_XW=0: test knob
   { const char* pe = std::getenv("LINMT_PMAX"); pmax_on_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_ATT_MERGE"); att_merge_ = use_tc_ && !(pe && std::atoi(pe) == 0); }
-  { const char* pe = std::getenv("LINMT_ATT_FOLD"); att_fold_ = att_merge_ && !(pe && std::atoi(pe) == 0); }
+  // (local attention only: over a whole sentence the second window costs the attention kernel more than the GEMM it replaces)
+  { const char* pe = std::getenv("LINMT_ATT_FOLD"); att_fold_ = att_merge_ && o.attention_mode == LINMT_ATT_LOCAL_P_GENERAL && !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PERSIST"); persist_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_TC_PAIR"); pair_ = !(pe && std::atoi(pe) == 0); }
   { const char* pe = std::getenv("LINMT_PDL"); pdl_ = use_tc_ && !(pe && std::atoi(pe) == 0); }   // LINMT_PDL=0: test knob
