@@ -7,6 +7,7 @@
 #include "engine.h"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_tc_pair.cuh"
 #include "step_kernels.cuh"
 
 namespace {
@@ -73,11 +74,19 @@ int linmt_k_gemm(const float* X, const float* W, float* Y, int32_t R, int32_t K,
     tc::pick_shape(R, Np, Kp, nt, n_sm, ws_floats, 4096, &bn, &splits, fmt);
     DevBuf dws, dcnt;
     KCK(dws.alloc(ws_floats * 4)); KCK(dcnt.alloc(4096 * 4)); KCK(cudaMemset(dcnt.p, 0, 4096 * 4));
+    // the engine's rule for CTA pairs: split operands, 64-deep stages, K not split, a shape that is down to two
+    // stages as one tile, the row tiles (rounded up to even) in one wave; LINMT_TC_PAIR=0 keeps the one-tile kernel
+    const char* pair_env = std::getenv("LINMT_TC_PAIR");
+    const int mt = (R + tc::BM - 1) / tc::BM;
+    const bool pair = !(pair_env && std::atoi(pair_env) == 0) && fmt == 1 && nt == 2 && bk == 64 && splits == 1 && mt >= 2 && bn % 16 == 0 &&
+                      tc::make_shape(bn, nt, bk, fmt).stages < 3 && (long)((mt + 1) & ~1) * ((Np + bn - 1) / bn) <= n_sm &&
+                      tc::max_resident_pairs<2, 64, 1, tc::TcEpiF32>() > 0;
     for (int t = 0; t < nt; ++t)
-      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, bn, bk)) return LINMT_ECUDA;
-    tc::Shape sh = tc::make_shape(bn, nt, bk, fmt);
+      if (!tc::make_tmap(&tm.b[t], B.p[t], Np, Kp, Kp, pair ? bn / 2 : bn, bk)) return LINMT_ECUDA;
+    tc::Shape sh = pair ? tc::make_shape_pair(bn, nt, bk, fmt) : tc::make_shape(bn, nt, bk, fmt);
     sh.splits = splits;
-    cudaError_t le = tc::launch_gemm_tc(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>());
+    cudaError_t le = pair ? tc::launch_gemm_tc_pair<2, 64, 1, tc::TcEpiF32>(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, nullptr, nullptr)
+                          : tc::launch_gemm_tc(tm, R, Np, Kp, sh, e, derr.as<int>(), 0, dws.as<float>(), dcnt.as<int>());
     KCK(le);
     KCK(cudaDeviceSynchronize());
     int herr = 0;

@@ -60,3 +60,33 @@ def test_gemm_tensor_vs_checker(oracle, cuda_lib, R, K, N, path, prec, tol):
     ref = X.astype(np.float64) @ W.astype(np.float64)
     scale = np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64)
     assert (np.abs(Y - ref) <= tol * scale + 1e-7).all(), float((np.abs(Y - ref) / scale).max())
+
+
+def test_gemm_on_cta_pairs_vs_float64_and_one_tile(cuda_lib):
+    """The decoder's gate product at full width (768 x 2048 times 2048 x 4096) picks 176-wide tiles, which as one
+    tile per CTA leave room for two stages only: the library then runs CTA pairs (tcgen05 cta_group::2, each CTA
+    loading half of the weight tile).  Against a float64 product the error is that of an fp32 FMA loop, and the
+    bits are those of the one-tile kernel (LINMT_TC_PAIR=0): the same products accumulate in the same order."""
+    import os
+    from linmt_b200 import decoder
+    rng = np.random.default_rng(11)
+    R, K, N = 768, 2048, 4096
+    X = rng.uniform(-1, 1, (R, K)).astype(np.float32)
+    W = rng.uniform(-0.08, 0.08, (K, N)).astype(np.float32)
+    Y = decoder.k_gemm(X, W, "tensor", "fp32")
+    ref = X.astype(np.float64) @ W.astype(np.float64)
+    scale = np.abs(X).astype(np.float64) @ np.abs(W).astype(np.float64)
+    assert (np.abs(Y - ref) <= 1e-6 * scale + 1e-7).all(), float((np.abs(Y - ref) / scale).max())
+    old = os.environ.get("LINMT_TC_PAIR")
+    os.environ["LINMT_TC_PAIR"] = "0"
+    try:
+        Y1 = decoder.k_gemm(X, W, "tensor", "fp32")
+    finally:
+        if old is None:
+            os.environ.pop("LINMT_TC_PAIR", None)
+        else:
+            os.environ["LINMT_TC_PAIR"] = old
+    assert np.array_equal(Y, Y1)
+    # a last row tile that is partly empty (700 = 5 x 128 + 60 rows)
+    Y5 = decoder.k_gemm(X[:700], W, "tensor", "fp32")
+    assert (np.abs(Y5 - ref[:700]) <= 1e-6 * scale[:700] + 1e-7).all()
