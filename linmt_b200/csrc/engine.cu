@@ -228,6 +228,7 @@ int Engine::pack_model(const float* blob, DevModel& m) {
   if ((rc = store(&m.voc_w, &m.p_voc_w, (size_t)Vp, Hp))) return rc;
   host.assign(Vp, 0.f);
   std::memcpy(host.data(), bv.bd, sizeof(float) * V);
+  for (int v = 0; v < V; ++v) m.voc_babs_max = std::max(m.voc_babs_max, std::fabs(host[v]));
   if ((rc = upload(&m.voc_b, host.size()))) return rc;
   return LINMT_OK;
 }
@@ -320,6 +321,9 @@ int Engine::init(const linmt_model_desc& d, const float* const* blobs, int nm, s
   for (int i = 0; i < nm; ++i) {
     int rc = pack_model(blobs[i], models_[i]);
     if (rc) return rc;
+    // fp16 storage of the logits needs them inside fp16's range with room to spare: |z| <= |w_row| |htilde| + |b| and
+    // every component of htilde is below 1 in magnitude
+    if (logits16_ && !(models_[i].voc_wnorm_max * std::sqrt((float)H) + models_[i].voc_babs_max < 3.0e4f)) logits16_ = false;
     if ((rc = alloc_state(states_[i]))) return rc;
     if (use_tc_ && (rc = alloc_state_tc(tc_states_[i]))) return rc;
   }

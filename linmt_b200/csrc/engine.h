@@ -35,6 +35,7 @@ struct DevModel {
   float* voc_b = nullptr;                // [Vp]
   float* dec_xw = nullptr;               // [V][4Hp] W_x . embedding(v) of the first decoder layer (tensor path, optional)
   float voc_wnorm_max = 0.f;             // largest 2-norm of a vocabulary weight row
+  float voc_babs_max = 0.f;              // largest magnitude of a vocabulary bias
   // the same operands as bf16 planes for the tensor-core path (fp32 copies are then not kept)
   tc::Planes p_emb_src{}, p_emb_tgt{}, p_att_proj_w{}, p_att_out_w{}, p_voc_w{};
   std::vector<tc::Planes> p_enc_w, p_dec_w;
