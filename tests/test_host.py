@@ -193,3 +193,26 @@ def test_multi_device_job_order_and_errors(cuda_lib):
     rc = cuda_lib.linmt_create_from_weights_on(C.byref(d), arr, 1, blob.size, C.byref(o), devs.ctypes.data_as(C.c_void_p), 3, C.byref(h))
     assert rc == 1 and b"twice" in cuda_lib.linmt_last_error(None)
     assert cuda_lib.linmt_device_count(None) == 0
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU restatement in the reference's loop shape and
+    prints ONE JSON line with the same metric, unit and direction as the main arm, marked `impl: reference`, with
+    a `cpu_baseline` that describes the run and an `e2e` that repeats the value with no copies."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "C1",
+                          "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1, lines
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["unit"] == "tokens/s" and d["higher_is_better"] is True
+    assert d["metric"].startswith("decoded target tokens/sec") and d["value"] > 0 and d["gpu_launches"] == 0
+    cb = d["cpu_baseline"]
+    assert cb["kind"] in ("port", "reference") and cb["cores"] >= 1 and cb["sample"] and cb["value"] == d["value"]
+    e = d["e2e"]
+    assert e["value"] == d["value"] and e["unit"] == d["unit"] and e["h2d_bytes_per_step"] == 0 and e["d2h_bytes_per_step"] == 0
+    assert d["config"]["workload"].startswith("C1")
